@@ -1,0 +1,427 @@
+#!/usr/bin/env python
+"""Benchmark of the fused INT4/INT8 dequantise + matmul operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the operator over every projection of the workload (for the
+default workload: the Qwen2.5-7B decode MLP, fused gate+up GEMV then down GEMV, int4
+group 128, M=1).  Inputs are seeded synthetic tensors with the model's shapes.
+
+  value   weight GB/s with everything resident in HBM: (packed weights + scales + zeros
+          read per step) x steps / device time, CUDA events around exactly K steps.  The
+          K steps are replayed from one CUDA graph so that the device, not the Python
+          launch loop, sets the pace; each step reads a different copy of the weights
+          (copies x bytes > 2 x L2), so no step finds its weights in L2.
+  e2e     the same metric through the public call, metal_native._C.dequant_matmul, with
+          the activations in pinned host memory: every step copies them to the device,
+          runs the operator and copies the result back to pinned host memory, then
+          waits.  Weights stay resident (they are model state, loaded once).
+  roofline  the dominant kernel (the largest projection's GEMV) timed alone with CUDA
+          events, algorithmic bytes / duration against the measured HBM copy peak.
+  cpu_baseline  the reference's CPU dequantise-then-matmul path (the oracle port of
+          tests/cpp/test_dequant_matmul.mm:119-213) on the host cores, same workload.
+
+With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the workload is
+the Llama-3-70B int8 per-channel layers column-sharded over N, each step ending in an
+all-gather of the output slices; the value is the whole-job aggregate.
+
+--impl reference times the CPU path only (rank 0), as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT / "metal-native_b200"), str(ROOT)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+FALLBACK_HBM_GBS = 6650.0   # used only if MEASURED_PEAKS.json is absent ("of fallback")
+METRIC = "int4 dequant-GEMV weight GB/s"
+UNIT = "GB/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto",
+                    help="auto | qwen7b-decode | llama8b-decode-m{4,16,32} | qwen7b-prefill | "
+                         "llama70b-int8-m{1,64}")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    return ap.parse_args()
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured", d
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback", {}
+
+
+def workload_name(args, world):
+    if args.workload != "auto":
+        return args.workload
+    return "qwen7b-decode" if world == 1 else "llama70b-int8-m1"
+
+
+def build_layers(name, world, rank):
+    """Returns (layers, description).  CPU tensors; identical on every call."""
+    from metal_native import workloads
+    if name == "qwen7b-decode":
+        return workloads.config1(), "Qwen2.5-7B decode MLP: gate+up [1,3584]x[37888,3584]^T then down [1,18944]x[3584,18944]^T, int4 g128 asym, fp16"
+    if name.startswith("llama8b-decode-m"):
+        M = int(name.rsplit("m", 1)[1])
+        return workloads.config2(M), f"Llama-3-8B batched decode M={M}: K=4096,N=14336 and K=14336,N=4096, int4 g128 sym, bf16"
+    if name == "qwen7b-prefill":
+        return workloads.config3(), "Qwen2.5-7B prefill M=512: K=3584,N=18944 and K=18944,N=3584, int4 g128 asym, fp16"
+    if name.startswith("llama70b-int8-m"):
+        M = int(name.rsplit("m", 1)[1])
+        return (workloads.config4(M, world_size=world, rank=rank),
+                f"Llama-3-70B M={M}: K=8192,N=57344 and K=28672,N=8192, int8 per-channel, bf16, "
+                f"column-sharded over {world} GPU(s)")
+    raise SystemExit(f"unknown workload {name}")
+
+
+# --------------------------------------------------------------------------- CPU arm
+
+def cpu_path_time(layers, seconds, max_steps=None):
+    """Times the oracle port of the reference CPU path on all host threads.  Returns
+    (seconds per step, steps run, threads)."""
+    import numpy as np
+    from oracle import oracle
+    from tests import helpers as H
+    threads = oracle.host_threads()
+    prepared = []
+    for L in layers:
+        s = H.f32(L.scales)
+        prepared.append((H.f32(L.x), L.wq.contiguous().numpy(), s,
+                         H.f32(L.zeros) if L.zeros is not None else None, L.group_size, L.quant_type,
+                         np.empty((L.N, L.K), np.float32)))
+    times = []
+    t_end = time.perf_counter() + seconds
+    while True:
+        t0 = time.perf_counter()
+        for (x, wq, s, z, g, qt, scratch) in prepared:
+            oracle.dequant_matmul(x, wq, s, z, g, qt, threads=threads, scratch=scratch)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() >= t_end or (max_steps and len(times) >= max_steps):
+            break
+    return times, threads
+
+
+def cpu_sample_layers(layers, budget_macs=4e9):
+    """Bounds the CPU work of one step: if a layer needs more than `budget_macs`
+    multiply-adds, keep only its first rows n (a contiguous block of output columns) and
+    say so.  Throughput in weight GB/s is unaffected by the cut."""
+    from metal_native.workloads import Layer
+    out, notes = [], []
+    for L in layers:
+        macs = L.M * L.N * L.K
+        if macs <= budget_macs:
+            out.append(L)
+            continue
+        n_keep = max(16, int(L.N * budget_macs / macs) // 16 * 16)
+        out.append(Layer(L.name, L.quant_type, L.M, L.K, n_keep, L.group_size, L.x, L.wq[:n_keep].contiguous(),
+                         L.scales[:n_keep].contiguous(), None if L.zeros is None else L.zeros[:n_keep].contiguous()))
+        notes.append(f"{L.name}: first {n_keep} of {L.N} output columns")
+    return out, notes
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    name = workload_name(args, world)
+    layers, desc = build_layers(name, 1, 0)
+    sample, notes = cpu_sample_layers(layers)
+    wbytes = sum(L.weight_bytes for L in sample)
+    times, threads = cpu_path_time(sample, 1e9, max_steps=args.warmup)          # warm-up steps
+    times, threads = cpu_path_time(sample, 1e9, max_steps=max(1, args.steps))   # exactly K steps
+    total = sum(times)
+    value = wbytes * len(times) / total / 1e9
+    sample_desc = "whole workload per step" if not notes else "; ".join(notes)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": total / len(times) * 1e3,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "description": desc, "arm": "CPU oracle port of the reference's "
+                   "dequantise-then-matmul helpers (tests/cpp/test_dequant_matmul.mm:119-213), "
+                   "N split over host threads"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()   # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.split(",") for r in Path(self.file.name).read_text().strip().splitlines() if r.strip()]
+        os.unlink(self.file.name)
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                r = [c.strip() for c in r]
+                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
+                for nme, val in zip(names, r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nme)
+            except (ValueError, IndexError):
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load: power above the midpoint between idle and peak draw
+        thr = (min(pw) + max(pw)) / 2 if max(pw) - min(pw) > 50 else -1
+        loaded = sorted(s for s, p in zip(sm, pw) if p >= thr) or sorted(sm)
+        return {"sm_mhz": loaded[len(loaded) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "samples_under_load": len(loaded), "power_w_max": max(pw)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import metal_native
+    from metal_native import _C
+
+    name = workload_name(args, world)
+    layers_cpu, desc = build_layers(name, world, rank)
+    sampler = ClockSampler(local) if rank == 0 else None
+
+    # ---- resident copies of the weights: copies x bytes > 2 x L2 -------------------
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    wbytes_rank = sum(L.weight_bytes for L in layers_cpu)
+    copies = max(2, -(-2 * l2 // wbytes_rank) + 1)
+    copies = min(copies, 16)
+    dev_layers = []
+    for c in range(copies):
+        dev_layers.append([L.to(dev) if c == 0 else
+                           type(L)(L.name, L.quant_type, L.M, L.K, L.N, L.group_size, dev_layers[0][i].x,
+                                   dev_layers[0][i].wq.clone(), dev_layers[0][i].scales.clone(),
+                                   None if L.zeros is None else dev_layers[0][i].zeros.clone())
+                           for i, L in enumerate(layers_cpu)])
+    outs = [torch.empty((L.M, L.N), dtype=L.x.dtype, device=dev) for L in layers_cpu]
+    gathered = None
+    if world > 1:
+        from metal_native import sharded
+        gathered = [sharded.GatherBuffer(L.M, L.N, world, L.x.dtype, dev) for L in layers_cpu]
+
+    def step(i):
+        for j, L in enumerate(dev_layers[i % copies]):
+            _C.dequant_matmul(L.x, L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs[j])
+            if world > 1:
+                gathered[j].all_gather(outs[j])
+
+    kernels_per_step = len(layers_cpu)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up, graph capture ------------------------------------------------------
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(args.steps):
+                step(i)
+        graph.replay()     # untimed: uploads the graph
+        torch.cuda.synchronize()
+
+        # ---- timed region: exactly K steps ------------------------------------------
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    total_wbytes = wbytes_rank * world
+    value = total_wbytes * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- roofline: the dominant kernel alone -------------------------------------------
+    dom = max(range(len(layers_cpu)), key=lambda j: layers_cpu[j].weight_bytes)
+    Ld = layers_cpu[dom]
+    reps = max(50, min(args.steps, 400))
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(g2, stream=stream):
+            for i in range(reps):
+                L = dev_layers[i % copies][dom]
+                _C.dequant_matmul(L.x, L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs[dom])
+        g2.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        g2.replay()
+        k1.record(stream)
+        torch.cuda.synchronize()
+        dom_us = k0.elapsed_time(k1) * 1e3 / reps
+    peak, peak_kind, peaks = hbm_peak()
+    algo_bytes = Ld.total_bytes
+    achieved = algo_bytes / (dom_us * 1e-6) / 1e9
+    traffic = None
+    tr_file = ROOT / "profiles" / "traffic.json"
+    if tr_file.exists():
+        try:
+            traffic = json.loads(tr_file.read_text()).get(f"{name}:{Ld.name}")
+        except Exception:
+            traffic = None
+    roofline = {"bound": "hbm", "kernel": f"gemv ({Ld.name})", "achieved": achieved, "peak": peak,
+                "peak_source": f"{peak_kind} HBM copy bandwidth", "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": traffic,
+                "algorithmic_bytes_per_launch": algo_bytes, "weight_bytes_per_launch": Ld.weight_bytes,
+                "weight_GBps": Ld.weight_bytes / (dom_us * 1e-6) / 1e9, "us_per_launch": dom_us}
+
+    # ---- end to end through the public call, host buffers ------------------------------
+    xs_host = [L.x.pin_memory() for L in layers_cpu]
+    full_N = [L.N * (world if world > 1 else 1) for L in layers_cpu]
+    outs_host = [torch.empty((L.M, n), dtype=L.x.dtype).pin_memory() for L, n in zip(layers_cpu, full_N)]
+    xs_dev = [torch.empty_like(L.x, device=dev) for L in layers_cpu]
+
+    def e2e_step(i):
+        for j, L in enumerate(dev_layers[i % copies]):
+            xs_dev[j].copy_(xs_host[j], non_blocking=True)
+            o = _C.dequant_matmul(xs_dev[j], L.wq, L.scales, L.zeros, L.group_size, L.quant_type)
+            if world > 1:
+                o = gathered[j].all_gather(o)
+            outs_host[j].copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 400)
+    for i in range(5):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    c1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(c0.elapsed_time(c1), (time.perf_counter() - t0) * 1e3)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": total_wbytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in xs_host),
+           "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs_host),
+           "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+           "call": "metal_native._C.dequant_matmul per projection, eager; weights resident"}
+
+    # ---- keep the load on for the clock sampler, then read it ----------------------------
+    if rank == 0:
+        t_end = time.perf_counter() + 1.0
+        while time.perf_counter() < t_end:
+            graph.replay()
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+
+    # ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample, notes = cpu_sample_layers(layers_cpu)
+        times, threads = cpu_path_time(sample, args.cpu_seconds)
+        best = sorted(times)[len(times) // 2]
+        cpu = {"value": sum(L.weight_bytes for L in sample) / best / 1e9, "unit": UNIT, "cores": threads,
+               "kind": "port", "ms_per_step": best * 1e3,
+               "sample": (f"{len(times)} whole steps" if not notes else f"{len(times)} steps of: " + "; ".join(notes))
+               + f", median, {threads} threads splitting N"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f16" if layers_cpu[0].x.dtype == torch.float16 else "bf16", "data": "synthetic",
+            "config": {"workload": name, "description": desc, "weight_copies": copies,
+                       "l2_policy": f"inputs larger than L2: {copies} weight copies x {wbytes_rank / 1e6:.1f} MB "
+                                    f"rotate, L2 = {l2 / 1e6:.0f} MB",
+                       "launch": f"{args.steps} steps replayed from one CUDA graph",
+                       "weight_bytes_per_step": total_wbytes,
+                       "frac_of_measured_hbm": value / (peak * world), "frac_of_nominal_8TBs": value / (8000.0 * world)},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": kernels_per_step * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,154 @@
+/*
+ * mnq.h -- C ABI of libmnq.so: B200 (sm_100a) kernels for MetalNative's fused
+ * INT4/INT8 dequantise + matmul operator.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the
+ * CUDA stream it is given and returns without synchronising.  The caller owns all
+ * buffers (inputs, output and workspace); unless an entry point says otherwise
+ * the library allocates nothing.  No C++ exception crosses this boundary: each
+ * call returns an mnq_status and, on failure, mnq_last_error() gives the message
+ * for the calling thread.  Validation runs on the host before any launch.
+ *
+ * Data layouts are the reference's (shaders/matmul_dequant_kernel.metal:55-72):
+ *   activations    [M, K]        fp16 or bf16, row-major, leading dimension lda
+ *   weights_packed [N, K/2]      uint8, two 4-bit values per byte, element k in
+ *                                the low nibble for even k, high nibble for odd k
+ *                  [N, K]        int8
+ *   scales, zeros  [N, ceil(K/group_size)]   fp16 or bf16
+ *   out            [M, N]        dtype of the activations, leading dimension ldc
+ * with  w[n,k] = (q - 8) * s - z  (int4, q the unsigned nibble)
+ *       w[n,k] =  q      * s - z  (int8, q signed)
+ * and   out[m,n] = sum_k activations[m,k] * w[n,k], accumulated in fp32.
+ */
+#ifndef MNQ_H
+#define MNQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MNQ_API __attribute__((visibility("default")))
+#else
+#define MNQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: the values of the reference's MetalNativeError enum
+ * (include/metal_native/core/error.h:21-31). */
+typedef enum mnq_status {
+    MNQ_SUCCESS = 0,
+    MNQ_DEVICE_NOT_FOUND = 1,
+    MNQ_ALLOCATION_FAILED = 2,
+    MNQ_KERNEL_COMPILATION_FAILED = 3,
+    MNQ_INVALID_ARGUMENT = 4,
+    MNQ_OUT_OF_MEMORY = 5,
+    MNQ_TIMEOUT_ERROR = 6,
+    MNQ_INTERNAL_ERROR = 7,
+    MNQ_NOT_IMPLEMENTED = 8
+} mnq_status;
+
+/* Replaces enum class QuantType {INT4, INT8}
+ * (include/metal_native/ops/matmul.h:59-63). */
+typedef enum mnq_quant { MNQ_INT4 = 0, MNQ_INT8 = 1 } mnq_quant;
+
+/* Element types that cross the boundary. */
+typedef enum mnq_dtype { MNQ_FP16 = 0, MNQ_BF16 = 1, MNQ_FP32 = 2 } mnq_dtype;
+
+/* Kernel families the dispatcher chooses from (mnq_dequant_matmul_ex). */
+typedef enum mnq_path {
+    MNQ_PATH_AUTO = 0,
+    MNQ_PATH_GEMV = 1,    /* M <= 32: streams packed rows, unpacks in registers */
+    MNQ_PATH_GEMM = 2,    /* tcgen05 / TMEM tensor-core tiles */
+    MNQ_PATH_GENERIC = 3  /* any shape or alignment; guarded scalar loads */
+} mnq_path;
+
+/* Optional overrides for mnq_dequant_matmul_ex.  Zero in a field means "let the
+ * library decide"; a zero-filled struct behaves like passing NULL. */
+typedef struct mnq_tuning {
+    int32_t path;           /* mnq_path */
+    int32_t split_k;        /* number of K chunks (GEMV) */
+    int32_t warps_per_cta;  /* GEMV: 16 output rows per warp */
+    int32_t reserved[5];
+} mnq_tuning;
+
+/* Name of a status code ("Success", "InvalidArgument", ...): the strings of the
+ * reference's error_to_string (src/core/error.cpp:14-26). */
+MNQ_API const char* mnq_status_name(int status);
+
+/* Message of the last failed call made by this thread ("" if none).  The text
+ * after the "<StatusName>: " prefix the reference puts in MNException::what()
+ * (src/core/error.cpp:60-63). */
+MNQ_API const char* mnq_last_error(void);
+
+/* Workspace the fused operator may need for the given problem, in bytes (it
+ * depends only on the arguments, never on device state).  The workspace holds
+ * split-K partial sums and arrival counters.  It must be zero-filled once before
+ * its first use; every call leaves it zero-filled again, so one buffer can be
+ * reused by successive calls on the same stream.  Calls that may run
+ * concurrently need separate workspaces. */
+MNQ_API size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type);
+
+/* Fused dequantise + matmul.  Replaces
+ *   MNTensor dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant_type)
+ * (include/metal_native/ops/matmul.h:77-82; host side src/ops/matmul.mm:903-1029).
+ *
+ * Differences from the reference's host function, all at the boundary:
+ *   - the caller passes `out` (the reference allocates and returns it);
+ *   - act_dtype may be MNQ_BF16 as well as MNQ_FP16 (out has the same dtype);
+ *     scale_dtype is the dtype of scales and zeros and may differ from it;
+ *   - group_size may be any positive multiple of 32, or any value >= K for one
+ *     scale per output row ("per-channel"); the reference accepts 32, 64, 128;
+ *   - zeros may be NULL, meaning all zero;
+ *   - every row m < M is computed (the reference's M <= 8 kernels write row 0 only).
+ * K must be even for int4.  lda >= K, ldc >= N, in elements.
+ * `workspace` may be NULL when workspace_bytes is 0; if the workspace is smaller
+ * than mnq_workspace_bytes() the call still succeeds with less K-parallelism. */
+MNQ_API int mnq_dequant_matmul(const void* activations, const void* weights_packed, const void* scales,
+                       const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                       int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same, with overrides (tests and tuning).  `tuning` may be NULL. */
+MNQ_API int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, const void* scales,
+                          const void* zeros, void* out, int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldc, int32_t group_size, int32_t quant_type,
+                          int32_t act_dtype, int32_t scale_dtype, void* workspace,
+                          size_t workspace_bytes, void* stream, const mnq_tuning* tuning);
+
+/* Which kernel family mnq_dequant_matmul would run for these arguments
+ * (an mnq_path value other than AUTO), or a negative mnq_status on bad arguments.
+ * Pure host logic: usable without a GPU.  The reference's counterpart is the
+ * `use_vecmat = (M <= 8)` choice in src/ops/matmul.mm:946-956. */
+MNQ_API int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size,
+                    int32_t quant_type, int32_t act_dtype, const void* activations,
+                    const void* weights_packed, const void* scales, const void* zeros);
+
+/* Dequantise a whole weight matrix with the fused operator's formula (scale and
+ * zero, [N, ceil(K/g)] indexing): out[n,k] = (q-8)*s - z  or  q*s - z, evaluated
+ * as one fp32 fused multiply-add, then rounded to nearest even if out_dtype is
+ * fp16 or bf16.  The fp32 output is bit-identical to the reference's CPU helpers
+ * dequant_reference_int4 / dequant_reference_int8
+ * (tests/cpp/test_dequant_matmul.mm:119-188).  out is [N, K] row-major. */
+MNQ_API int mnq_dequantize(const void* weights_packed, const void* scales, const void* zeros, void* out,
+                   int64_t N, int64_t K, int32_t group_size, int32_t quant_type,
+                   int32_t scale_dtype, int32_t out_dtype, void* stream);
+
+/* The reference's standalone dequantise kernels
+ *   dequantize_int8_to_fp16[_vec]  (shaders/dequantize_kernel.metal:9-22, 58-96)
+ *   dequantize_int4_to_fp16[_vec]  (shaders/dequantize_kernel.metal:26-54, 100-163)
+ * as launched by QuantWeightCache::get_dequantized
+ * (src/memory/quant_weight_cache.mm:65-153): scale only, no zero-point, flat
+ * group index i / group_size, fp16 scales, fp16 output of num_elements values. */
+MNQ_API int mnq_dequantize_flat(const void* input, const void* scales_fp16, void* out_fp16,
+                        int64_t num_elements, int32_t group_size, int32_t quant_type, void* stream);
+
+/* Library version, "major.minor.patch". */
+MNQ_API const char* mnq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MNQ_H */

@@ -1,0 +1,259 @@
+// C ABI of libmnq.so (declared in include/mnq.h): argument validation, kernel
+// selection and error reporting.  Mirrors the host side of the reference operator,
+// src/ops/matmul.mm:903-1029: the same checks in the same order with the same
+// messages, followed by the checks the reference leaves out (scales/zeros presence,
+// leading dimensions, even K for int4), all before any launch.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "mnq_common.cuh"
+
+namespace mnq {
+
+int launch_dequantize_matrix(const void* wq, const void* scales, const void* zeros, void* out,
+                             int64_t N, int64_t K, int32_t group_size, int32_t G, int32_t quant,
+                             int32_t scale_dtype, int32_t out_dtype, int sm_count, cudaStream_t stream);
+int launch_dequantize_flat(const void* in, const void* scales, void* out, int64_t num_elements,
+                           int32_t group_size, int32_t quant, int sm_count, cudaStream_t stream);
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+int fail(int status, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int check_cuda(cudaError_t e, const char* what)
+{
+    if (e == cudaSuccess) return MNQ_SUCCESS;
+    const int status = (e == cudaErrorMemoryAllocation) ? MNQ_OUT_OF_MEMORY
+                     : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) ? MNQ_DEVICE_NOT_FOUND
+                     : MNQ_INTERNAL_ERROR;
+    return fail(status, "%s: %s", what, cudaGetErrorString(e));
+}
+
+namespace {
+
+// SM count of the current device; one attribute query per device per process.
+int current_sm_count(int* out)
+{
+    static int cached[64];
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) { *out = cached[dev]; return MNQ_SUCCESS; }
+    int sms = 0;
+    rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev),
+                    "cudaDeviceGetAttribute(MultiProcessorCount)");
+    if (rc) return rc;
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    *out = sms;
+    return MNQ_SUCCESS;
+}
+
+// Host-only validation shared by mnq_dequant_matmul_ex and mnq_select_path.
+int validate_matmul(const void* x, const void* wq, const void* scales, const void* out, bool need_out,
+                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldc, int32_t group_size,
+                    int32_t quant, int32_t act_dtype, int32_t scale_dtype)
+{
+    // src/ops/matmul.mm:913-915 (Float16 only there; bf16 is this library's extension)
+    if (act_dtype != MNQ_FP16 && act_dtype != MNQ_BF16)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: activations must be Float16 or BFloat16");
+    // src/ops/matmul.mm:916-918 accepts 32, 64, 128; here any multiple of 32, or >= K for one
+    // scale per output row
+    if (group_size <= 0 || (group_size < K && group_size % 32 != 0))
+        return fail(MNQ_INVALID_ARGUMENT,
+                    "dequant_matmul: group_size must be a positive multiple of 32 (32, 64, 128, ...) or >= K");
+    if (quant != MNQ_INT4 && quant != MNQ_INT8)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: quant_type must be INT4 or INT8");
+    if (scale_dtype != MNQ_FP16 && scale_dtype != MNQ_BF16)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: scales must be Float16 or BFloat16");
+    if (M < 0 || N < 0 || K < 0)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: negative dimension");
+    // src/ops/matmul.mm:926-934 checks weights_packed.shape[1] == K/2; an odd K would make the
+    // kernels' (K+1)/2 row stride disagree with that, so it is rejected outright
+    if (quant == MNQ_INT4 && (K & 1))
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: INT4 weights must be [N, K/2] (K must be even)");
+    if (lda < K) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: lda must be >= K");
+    if (ldc < N) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: ldc must be >= N");
+    if (M > 0 && N > 0) {
+        if (K > 0 && (!x || !wq || !scales))
+            return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: null activations, weights_packed or scales");
+        if (need_out && !out) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: null output");
+    }
+    return MNQ_SUCCESS;
+}
+
+void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales, const void* zeros,
+               void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldc, int32_t group_size,
+               int32_t quant, int32_t act_dtype, int32_t scale_dtype, void* workspace,
+               size_t workspace_bytes, void* stream)
+{
+    a.x = x; a.wq = wq; a.scales = scales; a.zeros = zeros; a.out = out;
+    a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldc = ldc;
+    a.group_size = group_size;
+    a.G = (K <= 0) ? 0 : static_cast<int32_t>((K + group_size - 1) / group_size);
+    a.quant = quant; a.act_dtype = act_dtype; a.scale_dtype = scale_dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace ? workspace_bytes : 0;
+    a.stream = static_cast<cudaStream_t>(stream);
+    a.sm_count = 148;
+}
+
+int choose_path(const MatmulArgs& a)
+{
+    if (a.M <= 32 && gemv_supported(a)) return MNQ_PATH_GEMV;
+    if (a.M > 32 && gemm_supported(a)) return MNQ_PATH_GEMM;
+    return MNQ_PATH_GENERIC;
+}
+
+template <typename T>
+__global__ void zero_rows_kernel(T* out, int64_t M, int64_t N, int64_t ldc)
+{
+    const int64_t total = M * N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[(i / N) * ldc + (i % N)] = T(0);
+}
+
+}  // namespace
+}  // namespace mnq
+
+using namespace mnq;
+
+extern "C" {
+
+const char* mnq_status_name(int status)
+{
+    switch (status) {
+        case MNQ_SUCCESS: return "Success";
+        case MNQ_DEVICE_NOT_FOUND: return "DeviceNotFound";
+        case MNQ_ALLOCATION_FAILED: return "AllocationFailed";
+        case MNQ_KERNEL_COMPILATION_FAILED: return "KernelCompilationFailed";
+        case MNQ_INVALID_ARGUMENT: return "InvalidArgument";
+        case MNQ_OUT_OF_MEMORY: return "OutOfMemory";
+        case MNQ_TIMEOUT_ERROR: return "TimeoutError";
+        case MNQ_INTERNAL_ERROR: return "InternalError";
+        case MNQ_NOT_IMPLEMENTED: return "NotImplemented";
+        default: return "Unknown";
+    }
+}
+
+const char* mnq_last_error(void) { return g_error; }
+
+const char* mnq_version(void) { return "0.1.0"; }
+
+size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
+{
+    return gemv_workspace_bytes(M, N, K, group_size, quant_type);
+}
+
+int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size, int32_t quant_type,
+                    int32_t act_dtype, const void* activations, const void* weights_packed,
+                    const void* scales, const void* zeros)
+{
+    const int rc = validate_matmul(activations, weights_packed, scales, nullptr, false, M, N, K, lda, N,
+                                   group_size, quant_type, act_dtype, MNQ_FP16);
+    if (rc) return -rc;
+    MatmulArgs a;
+    fill_args(a, activations, weights_packed, scales, zeros, nullptr, M, N, K, lda, N, group_size,
+              quant_type, act_dtype, MNQ_FP16, nullptr, 0, nullptr);
+    // the answer must not depend on how much workspace a later call brings
+    a.workspace = reinterpret_cast<void*>(uintptr_t(256));
+    a.workspace_bytes = gemv_workspace_bytes(M, N, K, group_size, quant_type);
+    return choose_path(a);
+}
+
+int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, const void* scales,
+                          const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                          int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                          const mnq_tuning* tuning)
+{
+    int rc = validate_matmul(activations, weights_packed, scales, out, true, M, N, K, lda, ldc, group_size,
+                             quant_type, act_dtype, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return MNQ_SUCCESS;  // empty output: nothing to launch
+
+    MatmulArgs a;
+    fill_args(a, activations, weights_packed, scales, zeros, out, M, N, K, lda, ldc, group_size, quant_type,
+              act_dtype, scale_dtype, workspace, workspace_bytes, stream);
+    rc = current_sm_count(&a.sm_count);
+    if (rc) return rc;
+
+    if (K == 0) {  // empty reduction: the sum over no terms
+        const int64_t total = M * N;
+        const int grid = static_cast<int>(total / 256 + 1 > 1024 ? 1024 : total / 256 + 1);
+        if (act_dtype == MNQ_FP16)
+            zero_rows_kernel<<<grid, 256, 0, a.stream>>>(static_cast<__half*>(out), M, N, ldc);
+        else
+            zero_rows_kernel<<<grid, 256, 0, a.stream>>>(static_cast<__nv_bfloat16*>(out), M, N, ldc);
+        return check_cuda(cudaGetLastError(), "zero-fill launch");
+    }
+
+    int path = (tuning && tuning->path != MNQ_PATH_AUTO) ? tuning->path : choose_path(a);
+    switch (path) {
+        case MNQ_PATH_GEMV: return launch_gemv(a, tuning);
+        case MNQ_PATH_GEMM: return launch_gemm(a, tuning);
+        case MNQ_PATH_GENERIC: return launch_generic(a);
+        default: return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: unknown path %d", path);
+    }
+}
+
+int mnq_dequant_matmul(const void* activations, const void* weights_packed, const void* scales,
+                       const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                       int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return mnq_dequant_matmul_ex(activations, weights_packed, scales, zeros, out, M, N, K, lda, ldc,
+                                 group_size, quant_type, act_dtype, scale_dtype, workspace,
+                                 workspace_bytes, stream, nullptr);
+}
+
+int mnq_dequantize(const void* weights_packed, const void* scales, const void* zeros, void* out, int64_t N,
+                   int64_t K, int32_t group_size, int32_t quant_type, int32_t scale_dtype,
+                   int32_t out_dtype, void* stream)
+{
+    if (quant_type != MNQ_INT4 && quant_type != MNQ_INT8)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize: quant_type must be INT4 or INT8");
+    if (scale_dtype != MNQ_FP16 && scale_dtype != MNQ_BF16)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize: scales must be Float16 or BFloat16");
+    if (out_dtype != MNQ_FP16 && out_dtype != MNQ_BF16 && out_dtype != MNQ_FP32)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize: output must be Float32, Float16 or BFloat16");
+    if (N < 0 || K < 0 || group_size <= 0)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize: bad dimensions or group_size");
+    if (N == 0 || K == 0) return MNQ_SUCCESS;
+    if (!weights_packed || !scales || !out)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize: null weights_packed, scales or output");
+    int sms = 148;
+    const int rc = current_sm_count(&sms);
+    if (rc) return rc;
+    const int32_t G = static_cast<int32_t>((K + group_size - 1) / group_size);
+    return launch_dequantize_matrix(weights_packed, scales, zeros, out, N, K, group_size, G, quant_type,
+                                    scale_dtype, out_dtype, sms, static_cast<cudaStream_t>(stream));
+}
+
+int mnq_dequantize_flat(const void* input, const void* scales_fp16, void* out_fp16, int64_t num_elements,
+                        int32_t group_size, int32_t quant_type, void* stream)
+{
+    if (quant_type != MNQ_INT4 && quant_type != MNQ_INT8)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize_flat: quant_type must be INT4 or INT8");
+    if (num_elements < 0 || group_size <= 0)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize_flat: bad num_elements or group_size");
+    if (num_elements == 0) return MNQ_SUCCESS;
+    if (!input || !scales_fp16 || !out_fp16)
+        return fail(MNQ_INVALID_ARGUMENT, "dequantize_flat: null input, scales or output");
+    int sms = 148;
+    const int rc = current_sm_count(&sms);
+    if (rc) return rc;
+    return launch_dequantize_flat(input, scales_fp16, out_fp16, num_elements, group_size, quant_type, sms,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

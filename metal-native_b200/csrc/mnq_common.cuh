@@ -1,0 +1,225 @@
+// Shared device helpers: dtype traits, cache-hinted loads, exact integer -> fp16/bf16
+// unpacking of packed INT4 / INT8 weights, warp-level mma wrappers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mnq.h"
+
+namespace mnq {
+
+// ---------------------------------------------------------------------------
+// Host-side error plumbing (defined in api.cu)
+// ---------------------------------------------------------------------------
+int fail(int status, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+
+// ---------------------------------------------------------------------------
+// 16-bit float traits
+// ---------------------------------------------------------------------------
+template <typename T> struct F16Traits;
+
+template <> struct F16Traits<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
+};
+template <> struct F16Traits<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+// scales / zeros arrive as fp16 or bf16 bits; widening to fp32 is exact.
+__device__ __forceinline__ float widen16(const void* base, size_t idx, int dtype)
+{
+    const uint16_t bits = __ldg(reinterpret_cast<const uint16_t*>(base) + idx);
+    if (dtype == MNQ_BF16) return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    return __half2float(__ushort_as_half(bits));
+}
+
+// ---------------------------------------------------------------------------
+// Loads
+// ---------------------------------------------------------------------------
+// Weights are read exactly once: keep them out of L1 so the activations and scales
+// staged through L1/shared memory are not evicted.
+__device__ __forceinline__ uint4 ldg_stream_16(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_8(const void* p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_4(const void* p)
+{
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Bit tricks
+// ---------------------------------------------------------------------------
+template <int LUT>
+__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(r) : "r"(a), "r"(b), "r"(c), "n"(LUT));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+__device__ __forceinline__ uint32_t b2_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 u32_as_b2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+
+// ---------------------------------------------------------------------------
+// INT4: one 32-bit word = 8 nibbles n0..n7 (element k in nibble k).
+// Produces (q - 8) as exact 16-bit floats, paired (n0,n4) (n1,n5) (n2,n6) (n3,n7):
+// the pairing that costs no shifts for the even nibbles.  The activations are
+// staged in the same order, so the pairing never has to be undone.
+// ---------------------------------------------------------------------------
+template <typename T> struct UnpackInt4;
+
+template <> struct UnpackInt4<__half> {
+    // 0x6400 = 1024.0h: OR-ing a nibble into the low mantissa bits gives 1024 + n
+    // exactly; OR-ing it 4 bits higher gives 1024 + 16 n.
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&out)[4])
+    {
+        constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
+        const uint32_t w8 = w >> 8;
+        const __half2 lo0 = u32_as_h2(lop3<0xEA>(w, LO, MAGIC));
+        const __half2 hi0 = u32_as_h2(lop3<0xEA>(w, HI, MAGIC));
+        const __half2 lo1 = u32_as_h2(lop3<0xEA>(w8, LO, MAGIC));
+        const __half2 hi1 = u32_as_h2(lop3<0xEA>(w8, HI, MAGIC));
+        const __half2 c1032 = __half2half2(__ushort_as_half(0x6408));  // 1032
+        const __half2 sixteenth = __half2half2(__ushort_as_half(0x2C00));  // 1/16
+        const __half2 m72 = __half2half2(__ushort_as_half(0xD480));  // -72
+        out[0] = h2_as_u32(__hsub2(lo0, c1032));           // (n0-8, n4-8)
+        out[1] = h2_as_u32(__hfma2(hi0, sixteenth, m72));  // (n1-8, n5-8): 64 + n - 72
+        out[2] = h2_as_u32(__hsub2(lo1, c1032));           // (n2-8, n6-8)
+        out[3] = h2_as_u32(__hfma2(hi1, sixteenth, m72));  // (n3-8, n7-8)
+    }
+};
+
+template <> struct UnpackInt4<__nv_bfloat16> {
+    // 0x4300 = 128.0bf16 (7 mantissa bits): 128 + n is exact for n < 128.
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&out)[4])
+    {
+        constexpr uint32_t LO = 0x000F000Fu, MAGIC = 0x43004300u;
+        const __nv_bfloat162 c136 = __bfloat162bfloat162(__ushort_as_bfloat16(0x4308));  // 136
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 v = u32_as_b2(lop3<0xEA>(w >> (4 * i), LO, MAGIC));
+            out[i] = b2_as_u32(__hsub2(v, c136));
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// INT8: one 32-bit word = 4 signed bytes b0..b3.  Produces q as exact 16-bit
+// floats, paired (b0,b1) (b2,b3).
+// ---------------------------------------------------------------------------
+template <typename T> struct UnpackInt8;
+
+template <> struct UnpackInt8<__half> {
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&out)[2])
+    {
+        const uint32_t u = w ^ 0x80808080u;  // b + 128 in 0..255
+        const __half2 c1152 = __half2half2(__ushort_as_half(0x6480));  // 1024 + 128
+        out[0] = h2_as_u32(__hsub2(u32_as_h2(prmt(u, 0x64646464u, 0x4140u)), c1152));
+        out[1] = h2_as_u32(__hsub2(u32_as_h2(prmt(u, 0x64646464u, 0x4342u)), c1152));
+    }
+};
+
+template <> struct UnpackInt8<__nv_bfloat16> {
+    // bf16 has too few mantissa bits for 128 + (0..255); go through fp32:
+    // 0x4B0000uu = 2^23 + u, minus (2^23 + 128) = q exactly; q needs <= 8
+    // significant bits, so the top half of the fp32 is the exact bf16.
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&out)[2])
+    {
+        const uint32_t u = w ^ 0x80808080u;
+        constexpr float BIAS = 8388736.0f;  // 2^23 + 128
+        const float f0 = __uint_as_float(prmt(u, 0x4B000000u, 0x7440u)) - BIAS;
+        const float f1 = __uint_as_float(prmt(u, 0x4B000000u, 0x7441u)) - BIAS;
+        const float f2 = __uint_as_float(prmt(u, 0x4B000000u, 0x7442u)) - BIAS;
+        const float f3 = __uint_as_float(prmt(u, 0x4B000000u, 0x7443u)) - BIAS;
+        out[0] = prmt(__float_as_uint(f0), __float_as_uint(f1), 0x7632u);
+        out[1] = prmt(__float_as_uint(f2), __float_as_uint(f3), 0x7632u);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Warp-level tensor-core step used by the decode path: D[16x8] += A[16x16] B[16x8],
+// fp32 accumulate.  A = 16 weight rows, B = up to 8 activation rows (tokens).
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma_16x8x16<__half>(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                    uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16x8x16<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                           uint32_t a2, uint32_t a3, uint32_t b0,
+                                                           uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------
+// Launch-argument bundles
+// ---------------------------------------------------------------------------
+struct MatmulArgs {
+    const void* x;        // [M, K] act dtype
+    const void* wq;       // packed weights
+    const void* scales;   // [N, G]
+    const void* zeros;    // [N, G] or null
+    void* out;            // [M, N] act dtype
+    int64_t M, N, K, lda, ldc;
+    int32_t group_size;   // clamped to >= 1; >= K means one group per row
+    int32_t G;            // groups per row = ceil(K / group_size)
+    int32_t quant;        // mnq_quant
+    int32_t act_dtype;    // mnq_dtype
+    int32_t scale_dtype;  // mnq_dtype
+    void* workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+    int32_t sm_count;
+};
+
+// Launchers (each returns an mnq_status)
+int launch_generic(const MatmulArgs& a);
+bool gemv_supported(const MatmulArgs& a);
+int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
+size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
+bool gemm_supported(const MatmulArgs& a);
+int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning);
+
+}  // namespace mnq

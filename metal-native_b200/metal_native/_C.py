@@ -1,0 +1,321 @@
+"""``metal_native._C`` -- the operator bindings, over torch CUDA tensors.
+
+The reference's ``_C`` is a pybind11 module (``bindings/bind_ops.cpp``); this one binds
+the same operator to ``libmnq.so`` through ctypes: tensors cross as raw device pointers,
+the current torch CUDA stream is the queue, and errors come back as status codes that
+are re-raised as :class:`MetalNativeError` with the reference's ``"<Code>: <message>"``
+text (``src/core/error.cpp:60-63``).
+
+There is no CPU path: importing this module without the built library, or calling an
+operator with CPU tensors, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmnq.so"
+
+INT4, INT8 = 0, 1
+FP16, BF16, FP32 = 0, 1, 2
+PATH_AUTO, PATH_GEMV, PATH_GEMM, PATH_GENERIC = 0, 1, 2, 3
+_PATH_NAMES = {PATH_GEMV: "gemv", PATH_GEMM: "gemm", PATH_GENERIC: "generic"}
+
+
+class MetalNativeError(RuntimeError):
+    """Counterpart of the exception pybind11 raises for ``MNException``
+    (``bindings/bind_core.cpp:347``).  ``code`` is the ``MetalNativeError`` enum value
+    (``include/metal_native/core/error.h:21-31``)."""
+
+    def __init__(self, code: int, message: str):
+        self.code = int(code)
+        self.code_name = _status_name(code)
+        super().__init__(f"{self.code_name}: {message}")
+
+
+class Tuning(ctypes.Structure):
+    """``mnq_tuning`` of include/mnq.h."""
+    _fields_ = [("path", ctypes.c_int32), ("split_k", ctypes.c_int32),
+                ("warps_per_cta", ctypes.c_int32), ("reserved", ctypes.c_int32 * 5)]
+
+
+def _load() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python metal-native_b200/build.py` "
+            "(needs nvcc; there is no CPU fallback)")
+    L = ctypes.CDLL(str(_LIB_PATH))
+    i32, i64, vp, sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+    L.mnq_status_name.restype = ctypes.c_char_p
+    L.mnq_status_name.argtypes = [ctypes.c_int]
+    L.mnq_last_error.restype = ctypes.c_char_p
+    L.mnq_last_error.argtypes = []
+    L.mnq_version.restype = ctypes.c_char_p
+    L.mnq_version.argtypes = []
+    L.mnq_workspace_bytes.restype = sz
+    L.mnq_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
+    mm = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
+    L.mnq_dequant_matmul.restype = ctypes.c_int
+    L.mnq_dequant_matmul.argtypes = mm
+    L.mnq_dequant_matmul_ex.restype = ctypes.c_int
+    L.mnq_dequant_matmul_ex.argtypes = mm + [ctypes.POINTER(Tuning)]
+    L.mnq_select_path.restype = ctypes.c_int
+    L.mnq_select_path.argtypes = [i64, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]
+    L.mnq_dequantize.restype = ctypes.c_int
+    L.mnq_dequantize.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp]
+    L.mnq_dequantize_flat.restype = ctypes.c_int
+    L.mnq_dequantize_flat.argtypes = [vp, vp, vp, i64, i32, i32, vp]
+    return L
+
+
+_lib = _load()
+
+
+def _status_name(code: int) -> str:
+    return _lib.mnq_status_name(int(code)).decode()
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise MetalNativeError(rc, _lib.mnq_last_error().decode())
+
+
+def _invalid(msg: str) -> MetalNativeError:
+    return MetalNativeError(4, msg)
+
+
+_DT = {torch.float16: FP16, torch.bfloat16: BF16, torch.float32: FP32}
+
+
+def _quant_code(quant_type: str) -> int:
+    # The reference maps "int4" to INT4 and *every other string* to INT8
+    # (bindings/bind_ops.cpp:373); unknown strings are rejected here instead.
+    if quant_type == "int4":
+        return INT4
+    if quant_type == "int8":
+        return INT8
+    raise _invalid(f"dequant_matmul: quant_type must be 'int4' or 'int8', got {quant_type!r}")
+
+
+def _require_cuda(name: str, t: torch.Tensor, device=None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise _invalid(f"dequant_matmul: {name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise _invalid(f"dequant_matmul: {name} must be a CUDA tensor (there is no CPU path)")
+    if device is not None and t.device != device:
+        raise _invalid(f"dequant_matmul: {name} is on {t.device}, expected {device}")
+
+
+def _weights_as_bytes(weights_packed: torch.Tensor, quant: int) -> torch.Tensor:
+    """uint8 [N, K/2] (int4) or int8 [N, K]; int4 may also arrive as 32-bit words
+    [N, K/8], nibble i of a word at bits 4i -- the same bytes on a little-endian host."""
+    w = weights_packed
+    if w.dim() != 2:
+        raise _invalid("dequant_matmul: weights_packed must be 2D")
+    if not w.is_contiguous():
+        raise _invalid("dequant_matmul: weights_packed must be contiguous")
+    if quant == INT4:
+        if w.dtype in (torch.int32, torch.uint32):
+            return w.view(torch.uint8)
+        if w.dtype in (torch.uint8, torch.int8):
+            return w
+        raise _invalid("dequant_matmul: INT4 weights must be uint8 [N, K/2] (or 32-bit words [N, K/8])")
+    if w.dtype in (torch.int8, torch.uint8):
+        return w
+    raise _invalid("dequant_matmul: INT8 weights must be int8 [N, K]")
+
+
+# one zero-filled workspace per (device, stream); the kernels leave it zero-filled
+_ws_lock = threading.Lock()
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor | None:
+    if nbytes == 0:
+        return None
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        with _ws_lock:
+            ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
+    return ws
+
+
+def _prepare(activations, weights_packed, scales, zeros, group_size, quant_type):
+    q = _quant_code(quant_type)
+    _require_cuda("activations", activations)
+    dev = activations.device
+    _require_cuda("weights_packed", weights_packed, dev)
+    _require_cuda("scales", scales, dev)
+    if zeros is not None:
+        _require_cuda("zeros", zeros, dev)
+    # src/ops/matmul.mm:910-915
+    if activations.dim() != 2:
+        raise _invalid("dequant_matmul: activations must be 2D [M, K]")
+    if activations.dtype not in (torch.float16, torch.bfloat16):
+        raise _invalid("dequant_matmul: activations must be Float16 or BFloat16")
+    if activations.stride(1) != 1 and activations.shape[1] > 1:
+        activations = activations.contiguous()
+    M, K = activations.shape
+    lda = activations.stride(0) if M > 1 else max(K, 1)
+    if lda < K:
+        activations = activations.contiguous()
+        lda = K
+    w = _weights_as_bytes(weights_packed, q)
+    N = w.shape[0]
+    # src/ops/matmul.mm:926-934
+    if q == INT4 and w.shape[1] * 2 != K:
+        raise _invalid("dequant_matmul: INT4 weights must be [N, K/2]")
+    if q == INT8 and w.shape[1] != K:
+        raise _invalid("dequant_matmul: INT8 weights must be [N, K]")
+    group_size = int(group_size)
+    # src/ops/matmul.mm:916-918 accepts 32, 64, 128; any multiple of 32, or >= K, here
+    if group_size <= 0 or (group_size < K and group_size % 32 != 0):
+        raise _invalid("dequant_matmul: group_size must be a positive multiple of 32 (32, 64, 128, ...) or >= K")
+    G = (K + group_size - 1) // group_size if K > 0 else 0
+    # the reference never validates scales / zeros (src/ops/matmul.mm:903-934); a wrong
+    # shape there reads out of bounds, so it is checked here
+    if scales.dtype not in (torch.float16, torch.bfloat16):
+        raise _invalid("dequant_matmul: scales must be Float16 or BFloat16")
+    if scales.numel() != N * G or not scales.is_contiguous():
+        raise _invalid(f"dequant_matmul: scales must be contiguous [N, ceil(K/group_size)] = [{N}, {G}]")
+    if zeros is not None:
+        if zeros.dtype != scales.dtype:
+            raise _invalid("dequant_matmul: zeros must have the dtype of scales")
+        if zeros.numel() != N * G or not zeros.is_contiguous():
+            raise _invalid(f"dequant_matmul: zeros must be contiguous [N, ceil(K/group_size)] = [{N}, {G}]")
+    return activations, w, scales, zeros, M, N, K, lda, group_size, q
+
+
+def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant_type,
+                   *, out=None, tuning: Tuning | None = None):
+    """Fused dequantization + matrix multiplication.
+
+    Same parameters, in the same order, as the reference binding
+    (``bindings/bind_ops.cpp:366-382``): ``activations`` [M, K] fp16 (bf16 also
+    accepted), ``weights_packed`` [N, K/2] uint8 for ``"int4"`` or [N, K] int8 for
+    ``"int8"``, ``scales`` / ``zeros`` [N, K/group_size], returning [M, N] in the dtype of
+    ``activations``.  ``zeros`` may be ``None`` (symmetric quantisation).  The work is
+    enqueued on the current CUDA stream; like the reference op it returns before the
+    GPU has finished (``synchronize()`` or any torch sync waits for it).
+    """
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=dev)
+    else:
+        _require_cuda("out", out, dev)
+        if out.shape != (M, N) or out.dtype != x.dtype or out.stride(1) != 1:
+            raise _invalid("dequant_matmul: out must be [M, N] in the dtype of activations")
+    ldc = out.stride(0) if M > 1 else max(N, 1)
+    if torch.cuda.current_device() != dev.index:
+        with torch.cuda.device(dev):
+            return dequant_matmul(x, weights_packed, s, z, g, quant_type, out=out, tuning=tuning)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nbytes = _lib.mnq_workspace_bytes(M, N, K, g, q)
+    ws = _workspace(dev, stream, nbytes)
+    args = (x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None,
+            out.data_ptr(), M, N, K, lda, ldc, g, q, _DT[x.dtype], _DT[s.dtype],
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
+    if tuning is None:
+        _check(_lib.mnq_dequant_matmul(*args))
+    else:
+        _check(_lib.mnq_dequant_matmul_ex(*args, ctypes.byref(tuning)))
+    return out
+
+
+def select_path(M, N, K, group_size, quant_type, dtype=torch.float16, lda=None, alignment=256) -> str:
+    """Kernel family the library picks for a problem: 'gemv', 'gemm' or 'generic'.
+    Host logic only (works without a GPU); ``alignment`` is the assumed alignment of the
+    buffers' base addresses."""
+    q = _quant_code(quant_type)
+    fake = ctypes.c_void_p(alignment * 4096)
+    rc = _lib.mnq_select_path(M, N, K, lda if lda is not None else K, int(group_size), q, _DT[dtype],
+                              fake, fake, fake, fake)
+    if rc < 0:
+        raise MetalNativeError(-rc, _lib.mnq_last_error().decode())
+    return _PATH_NAMES[rc]
+
+
+def dequantize(weights_packed, scales, zeros, group_size, quant_type, out_dtype=torch.float32):
+    """Dequantise a whole weight matrix with the fused operator's formula,
+    ``w = (q-8)*s - z`` / ``q*s - z``; returns [N, K].  With ``out_dtype=torch.float32``
+    the result is bit-identical to the reference's CPU helpers
+    (``tests/cpp/test_dequant_matmul.mm:119-188``)."""
+    q = _quant_code(quant_type)
+    _require_cuda("weights_packed", weights_packed)
+    dev = weights_packed.device
+    _require_cuda("scales", scales, dev)
+    w = _weights_as_bytes(weights_packed, q)
+    N = w.shape[0]
+    K = w.shape[1] * (2 if q == INT4 else 1)
+    g = int(group_size)
+    if g <= 0:
+        raise _invalid("dequantize: group_size must be positive")
+    G = (K + g - 1) // g if K > 0 else 0
+    if scales.dtype not in (torch.float16, torch.bfloat16) or scales.numel() != N * G or not scales.is_contiguous():
+        raise _invalid(f"dequantize: scales must be contiguous fp16/bf16 [{N}, {G}]")
+    if zeros is not None:
+        _require_cuda("zeros", zeros, dev)
+        if zeros.dtype != scales.dtype or zeros.numel() != N * G or not zeros.is_contiguous():
+            raise _invalid(f"dequantize: zeros must match scales ([{N}, {G}], {scales.dtype})")
+    if out_dtype not in _DT:
+        raise _invalid("dequantize: out_dtype must be float32, float16 or bfloat16")
+    out = torch.empty((N, K), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _check(_lib.mnq_dequantize(w.data_ptr(), scales.data_ptr(),
+                                   zeros.data_ptr() if zeros is not None else None, out.data_ptr(),
+                                   N, K, g, q, _DT[scales.dtype], _DT[out_dtype], stream))
+    return out
+
+
+def dequantize_flat(quantized, scales, group_size, quant_type, num_elements=None):
+    """The reference's standalone ``dequantize_int{4,8}_to_fp16`` kernels
+    (``shaders/dequantize_kernel.metal``): ``out[i] = half(q_i) * scales[i // group_size]``
+    (int4: ``q_i - 8``), no zero-point, fp16 in and out, flat indexing."""
+    q = _quant_code(quant_type)
+    _require_cuda("quantized", quantized)
+    dev = quantized.device
+    _require_cuda("scales", scales, dev)
+    if scales.dtype != torch.float16 or not scales.is_contiguous():
+        raise _invalid("dequantize_flat: scales must be contiguous Float16")
+    if not quantized.is_contiguous():
+        raise _invalid("dequantize_flat: quantized must be contiguous")
+    nbytes = quantized.numel() * quantized.element_size()
+    full = nbytes * 2 if q == INT4 else nbytes
+    n = full if num_elements is None else int(num_elements)
+    if n < 0 or n > full:
+        raise _invalid("dequantize_flat: num_elements exceeds the input")
+    g = int(group_size)
+    if g <= 0 or (n + g - 1) // g > scales.numel():
+        raise _invalid("dequantize_flat: scales has fewer than ceil(num_elements / group_size) entries")
+    out = torch.empty(n, dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _check(_lib.mnq_dequantize_flat(quantized.data_ptr(), scales.data_ptr(), out.data_ptr(), n, g, q, stream))
+    return out
+
+
+def synchronize() -> None:
+    """Wait for all enqueued work (reference: ``_C.synchronize``, ``bindings/bind_core.cpp:407-409``)."""
+    torch.cuda.synchronize()
+
+
+def version() -> str:
+    return _lib.mnq_version().decode()
+
+
+def library_path() -> str:
+    return str(_LIB_PATH)
+
+
+def exported_symbols() -> list[str]:
+    """Entry points declared in include/mnq.h that this module binds."""
+    return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
+            "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
+            "mnq_dequantize_flat"]
