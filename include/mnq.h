@@ -68,10 +68,14 @@ typedef enum mnq_path {
 /* Optional overrides for mnq_dequant_matmul_ex.  Zero in a field means "let the
  * library decide"; a zero-filled struct behaves like passing NULL. */
 typedef struct mnq_tuning {
-    int32_t path;           /* mnq_path */
-    int32_t split_k;        /* number of K chunks (GEMV) */
-    int32_t warps_per_cta;  /* GEMV: 16 output rows per warp */
-    int32_t reserved[5];
+    int32_t path;                /* mnq_path */
+    int32_t split_k;             /* GEMV: number of K chunks */
+    int32_t warps_per_cta;       /* GEMV: 16 output rows per warp at a time */
+    int32_t gemv_variant;        /* 0 auto, 1 register-prefetch kernel, 2 shared-memory streaming kernel */
+    int32_t piece_bytes;         /* streaming GEMV: packed bytes per row per stage (multiple of 64) */
+    int32_t stages;              /* streaming GEMV: stages per warp (2..8) */
+    int32_t ctas_per_sm;         /* streaming GEMV: resident CTAs per SM the plan assumes */
+    int32_t row_blocks_per_warp; /* streaming GEMV: consecutive 16-row blocks per warp */
 } mnq_tuning;
 
 /* Name of a status code ("Success", "InvalidArgument", ...): the strings of the
@@ -85,9 +89,10 @@ MNQ_API const char* mnq_last_error(void);
 
 /* Workspace the fused operator may need for the given problem, in bytes (it
  * depends only on the arguments, never on device state).  The workspace holds
- * split-K partial sums and arrival counters.  It must be zero-filled once before
- * its first use; every call leaves it zero-filled again, so one buffer can be
- * reused by successive calls on the same stream.  Calls that may run
+ * arrival counters (its first 64 KiB) followed by split-K partial sums.  It must be
+ * zero-filled once before its first use; every call leaves the counters at zero
+ * again, so one buffer can be reused by successive calls, of any shapes, on the
+ * same stream.  Calls that may run
  * concurrently need separate workspaces. */
 MNQ_API size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type);
 
@@ -128,7 +133,7 @@ MNQ_API int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_
 
 /* Dequantise a whole weight matrix with the fused operator's formula (scale and
  * zero, [N, ceil(K/g)] indexing): out[n,k] = (q-8)*s - z  or  q*s - z, evaluated
- * as one fp32 fused multiply-add, then rounded to nearest even if out_dtype is
+ * in fp32 as a product then a subtraction (the product is exact), then rounded to nearest even if out_dtype is
  * fp16 or bf16.  The fp32 output is bit-identical to the reference's CPU helpers
  * dequant_reference_int4 / dequant_reference_int8
  * (tests/cpp/test_dequant_matmul.mm:119-188).  out is [N, K] row-major. */
@@ -144,6 +149,13 @@ MNQ_API int mnq_dequantize(const void* weights_packed, const void* scales, const
  * group index i / group_size, fp16 scales, fp16 output of num_elements values. */
 MNQ_API int mnq_dequantize_flat(const void* input, const void* scales_fp16, void* out_fp16,
                         int64_t num_elements, int32_t group_size, int32_t quant_type, void* stream);
+
+/* Reads (and, if `clear` is non-zero, resets) the device-side status word of the
+ * current device; synchronises the device.  Bit 0: a kernel gave up a bounded wait
+ * for an asynchronous copy and left its output incomplete (reported by the shim as
+ * TimeoutError, the reference's MetalNativeError::TimeoutError,
+ * include/metal_native/core/error.h:28).  No counterpart call in the reference. */
+MNQ_API int mnq_device_status(uint32_t* status, int32_t clear);
 
 /* Library version, "major.minor.patch". */
 MNQ_API const char* mnq_version(void);

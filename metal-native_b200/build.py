@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "metal_native" / "lib"
 LIB = LIB_DIR / "libmnq.so"
-SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemm_tcgen05.cu", "sharded.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemv_stream.cu", "gemm_tcgen05.cu", "sharded.cu", "no_alloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -69,7 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if failed:
         raise RuntimeError("nvcc failed")
     tmp = LIB.with_suffix(".so.tmp")
-    link = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(tmp), *map(str, objs), "-lcudart", "-lcuda"]
+    link = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"]
     subprocess.run(link, check=True)
     os.replace(tmp, LIB)
     return LIB

@@ -149,6 +149,16 @@ const char* mnq_last_error(void) { return g_error; }
 
 const char* mnq_version(void) { return "0.1.0"; }
 
+int mnq_device_status(uint32_t* status, int32_t clear)
+{
+    if (!status) return fail(MNQ_INVALID_ARGUMENT, "device_status: null status pointer");
+    unsigned int v = 0;
+    const int rc = read_device_status(&v, clear != 0);
+    if (rc) return rc;
+    *status = v;
+    return MNQ_SUCCESS;
+}
+
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
     return gemv_workspace_bytes(M, N, K, group_size, quant_type);

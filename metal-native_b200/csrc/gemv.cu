@@ -450,7 +450,7 @@ bool plan_gemv(const MatmulArgs& a, const mnq_tuning* tuning, int lw, size_t wor
     }
     if (chunks > kMaxSplitK) chunks = kMaxSplitK;
     if (chunks > pl.total_steps) chunks = pl.total_steps;
-    if (chunks < 1) chunks = 1;
+    if (chunks < 1 || row_tiles > kMaxCounters) chunks = 1;
 
     const bool has_zero = a.zeros != nullptr;
     for (;; ) {
@@ -465,8 +465,7 @@ bool plan_gemv(const MatmulArgs& a, const mnq_tuning* tuning, int lw, size_t wor
                   (has_zero ? static_cast<size_t>(pl.segs) * pl.nt * 8 * 4 : 0);
         size_t need_ws = 0;
         if (pl.num_chunks > 1)
-            need_ws = 256 + ((static_cast<size_t>(row_tiles) * 4 + 255) / 256) * 256 +
-                      static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
+            need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
         const bool smem_ok = pl.smem <= kMaxSmemBytes;
         const bool ws_ok = need_ws <= workspace_bytes;
         if (smem_ok && ws_ok) break;
@@ -523,6 +522,7 @@ int launch_lw(const GemvParams& p, int lw, int nt, dim3 grid, int threads, size_
 
 bool gemv_supported(const MatmulArgs& a)
 {
+    if (gemv_stream_supported(a, nullptr)) return true;
     const int lw = pick_lane_width(a);
     if (!lw) return false;
     GemvPlan pl;
@@ -545,12 +545,15 @@ size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size,
     if (chunks < by_smem) chunks = by_smem;
     if (chunks < 2) chunks = 2;  // lets a caller force a 2-way split for testing
     if (chunks > kMaxSplitK) chunks = kMaxSplitK;
-    return 256 + ((static_cast<size_t>(row_blocks) * 4 + 255) / 256) * 256 +
-           static_cast<size_t>(chunks) * M * N * 4;
+    return kCounterBytes + static_cast<size_t>(chunks) * M * N * 4;
 }
 
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning)
 {
+    const int variant = tuning ? tuning->gemv_variant : 0;
+    if (variant != 1 && gemv_stream_supported(a, tuning)) return launch_gemv_stream(a, tuning);
+    if (variant == 2)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: the streaming GEMV kernel cannot take this problem");
     const int lw = pick_lane_width(a);
     if (!lw) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: shape/alignment not supported by the GEMV kernels");
     GemvPlan pl;
@@ -576,8 +579,7 @@ int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning)
     if (pl.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);
-        const size_t counters_bytes = 256 + ((static_cast<size_t>(row_tiles) * 4 + 255) / 256) * 256;
-        p.partial = reinterpret_cast<float*>(ws + counters_bytes);
+        p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
     dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;

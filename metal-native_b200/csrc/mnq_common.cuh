@@ -214,10 +214,21 @@ struct MatmulArgs {
     int32_t sm_count;
 };
 
+// Split-K workspace layout, the same for every kernel and every problem shape: arrival
+// counters (always left at zero by the kernel that used them) in the first kCounterBytes,
+// fp32 partial sums (left dirty) after them.  Keeping the counter region fixed means a
+// later call with another shape never finds stale partial sums where it expects zeroed
+// counters.
+constexpr size_t kCounterBytes = 64 * 1024;
+constexpr int64_t kMaxCounters = kCounterBytes / 4;
+
 // Launchers (each returns an mnq_status)
 int launch_generic(const MatmulArgs& a);
 bool gemv_supported(const MatmulArgs& a);
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
+bool gemv_stream_supported(const MatmulArgs& a, const mnq_tuning* tuning);
+int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning);
+int read_device_status(unsigned int* out, bool clear);
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
 bool gemm_supported(const MatmulArgs& a);
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning);

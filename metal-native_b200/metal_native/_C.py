@@ -38,8 +38,9 @@ class MetalNativeError(RuntimeError):
 
 class Tuning(ctypes.Structure):
     """``mnq_tuning`` of include/mnq.h."""
-    _fields_ = [("path", ctypes.c_int32), ("split_k", ctypes.c_int32),
-                ("warps_per_cta", ctypes.c_int32), ("reserved", ctypes.c_int32 * 5)]
+    _fields_ = [("path", ctypes.c_int32), ("split_k", ctypes.c_int32), ("warps_per_cta", ctypes.c_int32),
+                ("gemv_variant", ctypes.c_int32), ("piece_bytes", ctypes.c_int32), ("stages", ctypes.c_int32),
+                ("ctas_per_sm", ctypes.c_int32), ("row_blocks_per_warp", ctypes.c_int32)]
 
 
 def _load() -> ctypes.CDLL:
@@ -68,6 +69,8 @@ def _load() -> ctypes.CDLL:
     L.mnq_dequantize.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp]
     L.mnq_dequantize_flat.restype = ctypes.c_int
     L.mnq_dequantize_flat.argtypes = [vp, vp, vp, i64, i32, i32, vp]
+    L.mnq_device_status.restype = ctypes.c_int
+    L.mnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), i32]
     return L
 
 
@@ -306,6 +309,21 @@ def synchronize() -> None:
     torch.cuda.synchronize()
 
 
+def device_status(clear: bool = True) -> int:
+    """Status word of the current device (synchronises).  Non-zero means a kernel gave up a
+    bounded wait and left its output incomplete."""
+    v = ctypes.c_uint32(0)
+    _check(_lib.mnq_device_status(ctypes.byref(v), 1 if clear else 0))
+    return int(v.value)
+
+
+def check_device_status() -> None:
+    """Raise ``MetalNativeError`` (TimeoutError) if a kernel gave up a bounded wait."""
+    v = device_status(clear=True)
+    if v:
+        raise MetalNativeError(6, f"a kernel gave up waiting for an asynchronous copy (status {v:#x})")
+
+
 def version() -> str:
     return _lib.mnq_version().decode()
 
@@ -318,4 +336,4 @@ def exported_symbols() -> list[str]:
     """Entry points declared in include/mnq.h that this module binds."""
     return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
-            "mnq_dequantize_flat"]
+            "mnq_dequantize_flat", "mnq_device_status"]

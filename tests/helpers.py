@@ -54,7 +54,8 @@ def assert_close_to_oracle(out: torch.Tensor, ref: np.ndarray, what: str = ""):
     bf16 outputs cannot meet that gate whatever the kernel does (rounding the exact result
     to bf16 already costs ~1.6e-3 rel-L2), so they are held to the rounding floor instead:
     the error against the fp32 oracle may exceed the error of RN_bf16(oracle) by at most
-    5 %, and every element must be within one bf16 ulp of RN_bf16(oracle)."""
+    5 %, and every element must be within one bf16 ulp (2^-7 relative) of the oracle value,
+    plus 1e-4 of the output RMS for outputs that nearly cancel."""
     got = out.detach().to("cpu", torch.float32).numpy()
     assert got.shape == ref.shape, (got.shape, ref.shape)
     assert np.isfinite(got).all(), f"{what}: non-finite output"
@@ -67,11 +68,10 @@ def assert_close_to_oracle(out: torch.Tensor, ref: np.ndarray, what: str = ""):
     ideal = torch.from_numpy(ref).to(torch.bfloat16)
     rel0, _ = errors(ideal.float().numpy(), ref)
     assert rel <= rel0 * 1.05 + 1e-6, f"{what}: rel-L2 {rel:.3e} vs bf16 rounding floor {rel0:.3e}"
-    a = out.detach().cpu().view(torch.int16).to(torch.int32)
-    b = ideal.view(torch.int16).to(torch.int32)
-    # ordered-integer view of the bit patterns: adjacent bf16 values differ by 1
-    a = torch.where(a < 0, -(a & 0x7FFF), a)
-    b = torch.where(b < 0, -(b & 0x7FFF), b)
-    ulps = (a - b).abs().max().item() if a.numel() else 0
-    assert ulps <= 1, f"{what}: {ulps} bf16 ulps from RN_bf16(oracle)"
+    # element-wise: within one bf16 ulp of the oracle value (2^-7 relative), plus an
+    # absolute allowance for fp32 summation-order noise on outputs that nearly cancel
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2))) if ref.size else 0.0
+    bound = np.abs(ref) * 2.0 ** -7 + 1e-4 * rms + 1e-30
+    worst = float(np.max(np.abs(got - ref) / bound)) if ref.size else 0.0
+    assert worst <= 1.0, f"{what}: element error {worst:.2f}x the bf16 one-ulp bound"
     return rel, mx
