@@ -3,6 +3,7 @@
 // src/ops/matmul.mm:903-1029: the same checks in the same order with the same
 // messages, followed by the checks the reference leaves out (scales/zeros presence,
 // leading dimensions, even K for int4), all before any launch.
+#include <cuda.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -37,6 +38,35 @@ int check_cuda(cudaError_t e, const char* what)
                      : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) ? MNQ_DEVICE_NOT_FOUND
                      : MNQ_INTERNAL_ERROR;
     return fail(status, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                         uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1,
+                         CUtensorMapSwizzle swizzle)
+{
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;   // resolved once per process; the pointer never changes
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+            return fail(MNQ_INTERNAL_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    if (reinterpret_cast<uintptr_t>(base) % 16 || pitch_bytes % 16 || (static_cast<uint64_t>(box0) * elem_bytes) % 16)
+        return fail(MNQ_INVALID_ARGUMENT, "tensor map: base, pitch and box width must be multiples of 16 bytes");
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MNQ_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return MNQ_SUCCESS;
 }
 
 namespace {

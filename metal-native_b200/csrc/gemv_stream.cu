@@ -1,24 +1,43 @@
 // Decode-shaped fused dequantise + matmul, streaming variant: the kernel the benchmark
-// shapes run.  Same arithmetic as gemv_mma_kernel (gemv.cu) - exact (q-8) / q integers
-// into m16n8k16 warp MMAs with fp32 accumulators, per-group scale of the fp32 partial
-// sums, zeros through per-group activation sums - but the packed weights reach the
-// warps through shared memory:
+// shapes run (M <= 32).  Replaces the reference's dequant_matmul_int{4,8}_vecmat_fp16
+// (shaders/matmul_dequant_kernel.metal:229-345, 485-576), computing every row m < M.
 //
-//   * every warp owns a small ring of stages in shared memory; one stage holds a piece
-//     of CH consecutive packed bytes of each of the warp's 16 weight rows;
-//   * the warp fills its own stages with 16 bulk asynchronous copies (cp.async.bulk,
-//     one per row, each a contiguous CH-byte read) that signal an mbarrier, so the
-//     loads in flight are bounded by shared memory, not by registers or occupancy,
-//     and DRAM sees long contiguous bursts;
-//   * lanes then pick their MMA fragments out of the stage with conflict-free 128-bit
-//     shared loads (row stride CH + 64 bytes).
+// Data movement.  Every warp owns 16 consecutive weight rows at a time and a small
+// ring of stages in shared memory; one stage holds a piece of CH consecutive packed
+// bytes of each of those rows.  One lane fills a stage with a single TMA tile copy
+// (cp.async.bulk.tensor.2d over a [N, row_bytes] tensor map, box 16 rows x CH bytes,
+// out-of-range rows and bytes zero-filled) that signals an mbarrier, so the bytes in
+// flight are bounded by shared memory rather than by registers or occupancy, the copy
+// costs one instruction per 4-8 KB, and DRAM sees contiguous bursts.  Lanes pick their
+// MMA fragments out of the stage with 128-bit shared loads.
+//
+// Arithmetic.  m16n8k16 warp MMAs with fp32 accumulators; A = 16 weight rows,
+// B = up to NT x 8 activation rows.  The packed integers are fed to the MMA with (almost)
+// no conversion work, using encodings that are exact in the MMA's input type:
+//   int4, fp16:  a nibble masked in place is the fp16 subnormal  n * 2^-24  (low
+//                nibble of a byte) or  n * 2^-20  (high nibble): 5 logic ops per 8 weights;
+//   int8, fp16:  byte ^ 0x80 placed in the low mantissa bits is  (q + 128) * 2^-24;
+//   int4, bf16:  0x4300 | n  =  128 + n;
+//   int8, bf16:  q itself (through the fp32 2^23 trick).
+// With a = alpha * (q + beta) entering the MMA, the fp32 partial sum P of one
+// quantisation group gives
+//     sum_k (q - c) * s * x - z * x  =  (s / alpha) * P  -  ((beta + c) * s + z) * X
+// where c = 8 for int4 and 0 for int8, and X is the sum of the group's activations.
+// s / alpha and (beta + c) * s + z are computed once per (row, group) when the warp
+// stages its scales; X once per CTA when the activations are staged.
+//
+// When there are too few 16-row blocks to fill the GPU the K range is cut into chunks
+// (grid.y); each warp writes its fp32 partial block to the workspace and the last warp
+// to arrive for a row block adds the chunks in a fixed order (deterministic), writes the
+// output and clears the arrival counter.
 //
 // Requirements: packed row length a multiple of 16 bytes, 16-byte aligned base, group
 // size a multiple of one step (128 k for int4, 64 k for int8) or a single group.
-// Everything else runs gemv_mma_kernel or the any-shape kernel.
+// Everything else runs gemv_mma_kernel or the any-shape kernel (gemv.cu).
 //
 // Every wait on an mbarrier is bounded: if a copy never lands the warp records the
 // fact in the status word (mnq_device_status) and leaves instead of spinning forever.
+#include <cuda.h>
 #include <limits.h>
 
 #include "mnq_common.cuh"
@@ -29,9 +48,9 @@ __device__ unsigned int g_device_status = 0;  // bit 0: a bounded wait gave up
 
 namespace {
 
-constexpr int kStepBytes = 64;       // packed bytes of one row consumed per step (4 lanes x 16)
+constexpr int kStepBytes = 64;  // packed bytes of one row consumed per step (4 lanes x 16)
 constexpr int kMaxSplitK = 32;
-constexpr int kMaxSmem = 220 * 1024;
+constexpr int kMaxSmem = 224 * 1024;
 constexpr unsigned kSpinLimit = 1u << 24;
 
 struct StreamParams {
@@ -52,12 +71,11 @@ struct StreamParams {
     int steps_per_chunk;
     int total_steps;      // ceil(row_bytes / 64)
     int num_chunks;
-    int segs;
+    int segs;             // groups touched by one chunk, padded to a multiple of 4
     int xs_stride;
     int x_vec_ok;
     int rbw;              // row blocks per warp
-    int piece_bytes;      // CH
-    int stages;           // S
+    int stages;
     int row_blocks;       // ceil(N / 16)
 };
 
@@ -83,25 +101,163 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait; false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)  // bounded; false = gave up
 {
     for (unsigned i = 0; i < kSpinLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+// One TMA tile copy: box of the tensor map at element coordinates (x, y) -> shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {
     asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
+// D = A * B + C with C passed by value, so that a chain can start from literal zeros.
+template <typename T>
+__device__ __forceinline__ void mma_c(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                      uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3);
+template <>
+__device__ __forceinline__ void mma_c<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1, float c0, float c1,
+                                              float c2, float c3)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+template <>
+__device__ __forceinline__ void mma_c<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                     uint32_t a3, uint32_t b0, uint32_t b1, float c0,
+                                                     float c1, float c2, float c3)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+
+// Encodings (see the header comment).  inv_alpha multiplies the scale; hi_factor brings
+// the second accumulator chain to the first one's scaling; offset = beta + c.
+template <int QUANT, typename T> struct Enc;
+template <> struct Enc<MNQ_INT4, __half> {
+    static constexpr float inv_alpha = 16777216.f, hi_factor = 0.0625f, offset = 8.f;
+    // (n0,n4) (n1,n5) (n2,n6) (n3,n7) as L0 H0 L1 H1
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
+    {
+        const uint32_t w8 = w >> 8;
+        L0 = w & 0x000F000Fu; H0 = w & 0x00F000F0u; L1 = w8 & 0x000F000Fu; H1 = w8 & 0x00F000F0u;
+    }
+};
+template <> struct Enc<MNQ_INT4, __nv_bfloat16> {
+    static constexpr float inv_alpha = 1.f, hi_factor = 1.f, offset = 136.f;
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
+    {
+        constexpr uint32_t M = 0x000F000Fu, MAGIC = 0x43004300u;
+        L0 = lop3<0xEA>(w, M, MAGIC); H0 = lop3<0xEA>(w >> 4, M, MAGIC);
+        L1 = lop3<0xEA>(w >> 8, M, MAGIC); H1 = lop3<0xEA>(w >> 12, M, MAGIC);
+    }
+};
+template <> struct Enc<MNQ_INT8, __half> {
+    static constexpr float inv_alpha = 16777216.f, hi_factor = 1.f, offset = 128.f;
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
+    {
+        const uint32_t u = w ^ 0x80808080u;
+        A0 = prmt(u, 0u, 0x4140u); A1 = prmt(u, 0u, 0x4342u);
+    }
+};
+template <> struct Enc<MNQ_INT8, __nv_bfloat16> {
+    static constexpr float inv_alpha = 1.f, hi_factor = 1.f, offset = 0.f;
+    static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
+    {
+        uint32_t o[2];
+        UnpackInt8<__nv_bfloat16>::run(w, o);
+        A0 = o[0]; A1 = o[1];
+    }
+};
+
+// One step: 64 packed bytes of 16 rows against NT x 8 activation rows.  plo / phi are two
+// independent accumulator chains; with ZERO_START they start from zero in this step.
+template <int QUANT, typename T, int NT, bool ZERO_START>
+__device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const unsigned char* const (&xrow)[NT],
+                                         int xoff, int t, float (&plo)[NT][4], float (&phi)[NT][4])
+{
+    const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w};
+    const uint32_t bw[4] = {wb.x, wb.y, wb.z, wb.w};
+    if (QUANT == MNQ_INT4) {
+#pragma unroll
+        for (int jw = 0; jw < 4; ++jw) {
+            uint32_t aL0, aH0, aL1, aH1, bL0, bH0, bL1, bH1;
+            Enc<MNQ_INT4, T>::run(aw[jw], aL0, aH0, aL1, aH1);
+            Enc<MNQ_INT4, T>::run(bw[jw], bL0, bH0, bL1, bH1);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff + (jw * 4 + t) * 16);
+                if (ZERO_START && jw == 0) {
+                    mma_c<T>(plo[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
+                    mma_c<T>(phi[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, 0.f, 0.f, 0.f, 0.f);
+                } else {
+                    mma_c<T>(plo[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, plo[nt][0], plo[nt][1], plo[nt][2], plo[nt][3]);
+                    mma_c<T>(phi[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, phi[nt][0], phi[nt][1], phi[nt][2], phi[nt][3]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int jw = 0; jw < 4; jw += 2) {
+            uint32_t a0, a1, b0, b1, c0, c1, d0, d1;
+            Enc<MNQ_INT8, T>::run(aw[jw], a0, a1);
+            Enc<MNQ_INT8, T>::run(bw[jw], b0, b1);
+            Enc<MNQ_INT8, T>::run(aw[jw + 1], c0, c1);
+            Enc<MNQ_INT8, T>::run(bw[jw + 1], d0, d1);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff + (t * 16 + jw * 4) * 2);
+                if (ZERO_START && jw == 0) {
+                    mma_c<T>(plo[nt], a0, b0, a1, b1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
+                    mma_c<T>(phi[nt], c0, d0, c1, d1, xv.z, xv.w, 0.f, 0.f, 0.f, 0.f);
+                } else {
+                    mma_c<T>(plo[nt], a0, b0, a1, b1, xv.x, xv.y, plo[nt][0], plo[nt][1], plo[nt][2], plo[nt][3]);
+                    mma_c<T>(phi[nt], c0, d0, c1, d1, xv.z, xv.w, phi[nt][0], phi[nt][1], phi[nt][2], phi[nt][3]);
+                }
+            }
+        }
+    }
+}
+
+// tot += S * (plo + hi_factor * phi) - Z * X for the lane's two rows (S0/Z0: row r, S1/Z1: row r+8)
 template <int QUANT, typename T, int NT>
+__device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&plo)[NT][4], const float (&phi)[NT][4],
+                                            float S0, float S1, float Z0, float Z1, const float* xsum_seg, int t)
+{
+    constexpr float HF = Enc<QUANT, T>::hi_factor;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const float2 X = *reinterpret_cast<const float2*>(xsum_seg + nt * 8 + 2 * t);
+        const float v0 = fmaf(phi[nt][0], HF, plo[nt][0]);
+        const float v1 = fmaf(phi[nt][1], HF, plo[nt][1]);
+        const float v2 = fmaf(phi[nt][2], HF, plo[nt][2]);
+        const float v3 = fmaf(phi[nt][3], HF, plo[nt][3]);
+        tot[nt][0] = fmaf(-Z0, X.x, fmaf(S0, v0, tot[nt][0]));
+        tot[nt][1] = fmaf(-Z0, X.y, fmaf(S0, v1, tot[nt][1]));
+        tot[nt][2] = fmaf(-Z1, X.x, fmaf(S1, v2, tot[nt][2]));
+        tot[nt][3] = fmaf(-Z1, X.y, fmaf(S1, v3, tot[nt][3]));
+    }
+}
+
+template <int QUANT, typename T, int NT, int CH>
 __global__ void __launch_bounds__(512)
-gemv_stream_kernel(const StreamParams p)
+gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap)
 {
     constexpr int STEP = (QUANT == MNQ_INT4) ? 128 : 64;  // k per step
+    constexpr int RS = CH;                                 // row stride inside a stage (dense TMA box)
+    constexpr int STAGE_BYTES = 16 * RS;
+    constexpr int PSTEPS = CH / kStepBytes;                // steps in a full piece
 
     extern __shared__ __align__(128) unsigned char smem[];
 
@@ -112,6 +268,10 @@ gemv_stream_kernel(const StreamParams p)
     const int chunk = blockIdx.y;
     const int r = lane >> 2;
     const int t = lane & 3;
+    // Fragment row r reads stage row wr (and wr + 8).  (A TMA box is dense, so rows are a
+    // multiple of 128 bytes apart and the two rows a quarter-warp reads together collide on
+    // banks: a 2-way conflict on 2 of the ~12 shared loads per step.)
+    const int wr = r;
 
     const int step_begin = chunk * p.steps_per_chunk;
     const int step_end = min(p.total_steps, step_begin + p.steps_per_chunk);
@@ -121,23 +281,22 @@ gemv_stream_kernel(const StreamParams p)
     const int byte_end = min(p.row_bytes, step_end * kStepBytes);
     const int seg0 = (p.group_size == INT_MAX) ? 0 : k_begin / p.group_size;
     const bool has_zero = (p.zeros != nullptr);
+    const bool group_is_step = (p.steps_per_group == 1);
 
-    // ---- shared memory carve-up ------------------------------------------------------
-    const int CH = p.piece_bytes;
-    const int RS = CH + 64;                      // row stride inside a stage
-    const int stage_bytes = 16 * RS;
-    const int ring_bytes = p.stages * stage_bytes;
-    const int sc_elems = p.rbw * 16 * p.segs;    // per warp, per array (16-bit values)
-    const int sc_bytes = ((sc_elems * 2 * (has_zero ? 2 : 1)) + 15) & ~15;
-    unsigned char* xs = smem;                                         // [M][xs_stride]
-    float* xsum = reinterpret_cast<float*>(xs + (size_t)p.M * p.xs_stride);   // [segs][NT*8]
-    unsigned char* warp_base = reinterpret_cast<unsigned char*>(xsum + p.segs * NT * 8);
-    warp_base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(warp_base) + 127) & ~uintptr_t(127));
-    unsigned char* my = warp_base + (size_t)warp * (ring_bytes + sc_bytes + 64);
-    unsigned char* ring = my;                                         // [stages][16][RS]
-    unsigned short* ssc = reinterpret_cast<unsigned short*>(my + ring_bytes);   // [rbw][16][segs]
-    unsigned short* szr = ssc + sc_elems;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(my + ring_bytes + sc_bytes);  // [stages] <= 8
+    // ---- shared memory carve-up (offsets from the base, so every access stays a
+    //      shared-space access) ---------------------------------------------------------
+    const int ring_bytes = p.stages * STAGE_BYTES;
+    const int sc_floats = p.rbw * 16 * p.segs;               // per warp, per array
+    const int xsum_off = p.M * p.xs_stride;
+    const int warp0_off = (xsum_off + p.segs * NT * 8 * 4 + 1023) & ~1023;
+    const int per_warp = ring_bytes + sc_floats * 8 + 128;
+    unsigned char* xs = smem;                                                  // [M][xs_stride]
+    float* xsum = reinterpret_cast<float*>(smem + xsum_off);                   // [segs][NT*8]
+    unsigned char* my = smem + warp0_off + warp * per_warp;
+    unsigned char* ring = my;                                                  // [stages][16][CH]
+    float* sS = reinterpret_cast<float*>(my + ring_bytes);                     // [rbw][16][segs]  s / alpha
+    float* sZ = sS + sc_floats;                                                // [rbw][16][segs]  (beta+c) s + z
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sZ + sc_floats);  // [stages] <= 8
 
     // ---- this warp's row blocks ----------------------------------------------------------
     const int rb_first = (blockIdx.x * warps + warp) * p.rbw;
@@ -152,97 +311,154 @@ gemv_stream_kernel(const StreamParams p)
     }
     __syncwarp();
 
-    auto issue_piece = [&](int j) {
-        const int rbi = j / ppr;
-        const int pc = j - rbi * ppr;
-        const int stage = j % p.stages;
-        const int b0 = byte_begin + pc * CH;
-        const int bytes = min(CH, byte_end - b0);
-        const uint32_t bar = smem_u32(&bars[stage]);
-        if (lane == 0) mbar_expect_tx(bar, 16u * bytes);
-        __syncwarp();
-        if (lane < 16) {
-            const int n = min((rb_first + rbi) * 16 + lane, p.N - 1);
-            bulk_copy_g2s(smem_u32(ring + (size_t)stage * stage_bytes + lane * RS),
-                          p.wq + (size_t)n * p.row_bytes + b0, bytes, bar);
+    // Producer state: next piece to request (row block, piece, stage).  One lane issues a
+    // single TMA tile copy per piece; rows past N and bytes past the row end are zero-filled
+    // by the TMA unit, so every piece is a full box.
+    int iss_rbi = 0, iss_pc = 0, iss_stage = 0, iss_count = 0;
+    auto issue_piece = [&]() {
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars[iss_stage]);
+            mbar_expect_tx(bar, 16u * CH);
+            tma_load_2d(smem_u32(ring + iss_stage * STAGE_BYTES), &wmap, (byte_begin + iss_pc * CH) >> 2,
+                        (rb_first + iss_rbi) * 16, bar);
         }
+        ++iss_count;
+        if (++iss_stage == p.stages) iss_stage = 0;
+        if (++iss_pc == ppr) { iss_pc = 0; ++iss_rbi; }
     };
 
-    // ---- start streaming weights before anything else -----------------------------------
-    for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece(j);
+    // ---- prologue ------------------------------------------------------------------------
+    // Order matters for latency: the few small loads everything waits for (scales, zeros,
+    // activations) are issued first, all of them before any is used, so they cost one
+    // round trip and are not queued behind the bulk weight traffic; then the first weight
+    // pieces are requested; only then are the small loads consumed.
+    for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsum[i] = 0.f;
 
-    // ---- this warp's scales / zeros (raw 16-bit) -------------------------------------------
-    for (int i = lane; i < nrb * 16 * p.segs; i += 32) {
-        const int rr = i / p.segs;                 // rbi * 16 + row
+    constexpr int SCB = 16;                        // scale loads in flight per lane
+    constexpr int XB = (NT == 1) ? 2 : 4;          // activation loads in flight per thread
+    const int sc_count = nrb * 16 * p.segs;
+    const int blocks_per_row = nsteps * (STEP / 8);
+    const int x_count = p.M * blocks_per_row;
+    const T* xg = static_cast<const T*>(p.x);
+    const unsigned short* sc16 = static_cast<const unsigned short*>(p.scales);
+    const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
+
+    auto load_x_block = [&](int i, uint32_t (&v)[4], int& m, int& b, int& k) {
+        m = i / blocks_per_row;
+        b = i - m * blocks_per_row;
+        k = k_begin + b * 8;
+        if (p.x_vec_ok && k + 8 <= p.K) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)m * p.lda + k));
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+            const unsigned short* xr = reinterpret_cast<const unsigned short*>(xg + (size_t)m * p.lda);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t lo = (k + 2 * e < p.K) ? __ldg(xr + k + 2 * e) : 0u;
+                const uint32_t hi = (k + 2 * e + 1 < p.K) ? __ldg(xr + k + 2 * e + 1) : 0u;
+                v[e] = lo | (hi << 16);
+            }
+        }
+    };
+    auto store_x_block = [&](const uint32_t (&v)[4], int m, int b, int k) {
+        float sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const unsigned short lo = static_cast<unsigned short>(v[e] & 0xFFFFu);
+            const unsigned short hi = static_cast<unsigned short>(v[e] >> 16);
+            sum += F16Traits<T>::to_float(*reinterpret_cast<const T*>(&lo)) +
+                   F16Traits<T>::to_float(*reinterpret_cast<const T*>(&hi));
+        }
+        const int sg = (p.group_size == INT_MAX) ? 0 : (k / p.group_size - seg0);
+        atomicAdd(&xsum[sg * (NT * 8) + m], sum);
+        int pos;
+        uint4 o;
+        if (QUANT == MNQ_INT4) {
+            // inside a 128-k step the 8-blocks are laid out [word j][lane t]; inside an 8-block
+            // the order is k+0,k+4,k+2,k+6 | k+1,k+5,k+3,k+7: first the pairs the low-nibble MMA
+            // consumes, then the pairs of the high-nibble MMA
+            const int step = b >> 4;
+            const int bl = b & 15;
+            pos = step * STEP + ((bl & 3) * 4 + (bl >> 2)) * 8;
+            o.x = prmt(v[0], v[2], 0x5410u);   // (x0, x4)
+            o.y = prmt(v[1], v[3], 0x5410u);   // (x2, x6)
+            o.z = prmt(v[0], v[2], 0x7632u);   // (x1, x5)
+            o.w = prmt(v[1], v[3], 0x7632u);   // (x3, x7)
+        } else {
+            pos = b * 8;
+            o.x = v[0]; o.y = v[1]; o.z = v[2]; o.w = v[3];
+        }
+        *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
+    };
+    auto sc_index = [&](int i, bool& ok) -> size_t {
+        const int rr = i / p.segs;   // rbi * 16 + row
         const int sg = i - rr * p.segs;
         const int n = rb_first * 16 + rr;
         const int g = seg0 + sg;
-        unsigned short s = 0, z = 0;
-        if (n < p.N && g < p.G) {
-            s = __ldg(reinterpret_cast<const unsigned short*>(p.scales) + (size_t)n * p.G + g);
-            if (has_zero) z = __ldg(reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)n * p.G + g);
-        }
-        ssc[i] = s;
-        if (has_zero) szr[i] = z;
+        ok = (i < sc_count) && (n < p.N) && (g < p.G);
+        return (size_t)n * p.G + g;
+    };
+    auto fold_scale = [&](int i, unsigned short sb, unsigned short zb) {
+        const float sv = (p.scale_dtype == MNQ_BF16) ? __uint_as_float((uint32_t)sb << 16)
+                                                     : __half2float(__ushort_as_half(sb));
+        const float zv = (p.scale_dtype == MNQ_BF16) ? __uint_as_float((uint32_t)zb << 16)
+                                                     : __half2float(__ushort_as_half(zb));
+        sS[i] = sv * Enc<QUANT, T>::inv_alpha;
+        sZ[i] = fmaf(Enc<QUANT, T>::offset, sv, zv);
+    };
+
+    // first batch of small loads (the only one for the benchmark shapes)
+    unsigned short sreg[SCB], zreg[SCB];
+#pragma unroll
+    for (int u = 0; u < SCB; ++u) {
+        bool ok;
+        const size_t idx = sc_index(lane + 32 * u, ok);
+        sreg[u] = ok ? __ldg(sc16 + idx) : (unsigned short)0;
+        zreg[u] = (ok && has_zero) ? __ldg(zr16 + idx) : (unsigned short)0;
+    }
+    uint32_t xv[XB][4];
+    int xm[XB], xb[XB], xk[XB];
+#pragma unroll
+    for (int u = 0; u < XB; ++u) {
+        const int i = tid + u * blockDim.x;
+        xm[u] = -1;
+        if (i < x_count) load_x_block(i, xv[u], xm[u], xb[u], xk[u]);
     }
 
-    // ---- stage activations (re-ordered for the MMA) and their group sums, CTA-wide -------
-    if (has_zero) {
-        for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsum[i] = 0.f;
-        __syncthreads();
-    }
-    {
-        const int blocks_per_row = nsteps * (STEP / 8);
-        const T* xg = static_cast<const T*>(p.x);
-        for (int i = tid; i < p.M * blocks_per_row; i += blockDim.x) {
-            const int m = i / blocks_per_row;
-            const int b = i - m * blocks_per_row;
-            const int k = k_begin + b * 8;
-            uint32_t v[4];
-            if (p.x_vec_ok && k + 8 <= p.K) {
-                const uint4 q = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)m * p.lda + k));
-                v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
-            } else {
-                const unsigned short* xr = reinterpret_cast<const unsigned short*>(xg + (size_t)m * p.lda);
+    // the first weight pieces
+    for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
+    __syncthreads();   // xsum is zeroed
+
+    // consume the small loads
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t lo = (k + 2 * e < p.K) ? xr[k + 2 * e] : 0u;
-                    const uint32_t hi = (k + 2 * e + 1 < p.K) ? xr[k + 2 * e + 1] : 0u;
-                    v[e] = lo | (hi << 16);
-                }
-            }
-            if (has_zero) {
-                float s = 0.f;
+    for (int u = 0; u < SCB; ++u)
+        if (lane + 32 * u < sc_count) fold_scale(lane + 32 * u, sreg[u], zreg[u]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const unsigned short lo = static_cast<unsigned short>(v[e] & 0xFFFFu);
-                    const unsigned short hi = static_cast<unsigned short>(v[e] >> 16);
-                    s += F16Traits<T>::to_float(*reinterpret_cast<const T*>(&lo)) +
-                         F16Traits<T>::to_float(*reinterpret_cast<const T*>(&hi));
-                }
-                const int seg = (p.group_size == INT_MAX) ? 0 : (k / p.group_size - seg0);
-                atomicAdd(&xsum[seg * (NT * 8) + m], s);
-            }
-            int pos;
-            uint4 o;
-            if (QUANT == MNQ_INT4) {
-                // inside a 128-k step: 8-blocks laid out [word j][lane t]; inside an 8-block the
-                // order k+0,k+4,k+1,k+5,k+2,k+6,k+3,k+7 (the pairing UnpackInt4 produces)
-                const int step = b >> 4;
-                const int bl = b & 15;
-                const int tt = bl >> 2;
-                const int jj = bl & 3;
-                pos = step * STEP + (jj * 4 + tt) * 8;
-                o.x = prmt(v[0], v[2], 0x5410u);
-                o.y = prmt(v[0], v[2], 0x7632u);
-                o.z = prmt(v[1], v[3], 0x5410u);
-                o.w = prmt(v[1], v[3], 0x7632u);
-            } else {
-                pos = b * 8;
-                o.x = v[0]; o.y = v[1]; o.z = v[2]; o.w = v[3];
-            }
-            *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
+    for (int u = 0; u < XB; ++u)
+        if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
+    // whatever did not fit in the first batch (several row blocks per warp, many groups, M > 8)
+    for (int i0 = SCB * 32; i0 < sc_count; i0 += SCB * 32) {
+#pragma unroll
+        for (int u = 0; u < SCB; ++u) {
+            bool ok;
+            const size_t idx = sc_index(i0 + lane + 32 * u, ok);
+            sreg[u] = ok ? __ldg(sc16 + idx) : (unsigned short)0;
+            zreg[u] = (ok && has_zero) ? __ldg(zr16 + idx) : (unsigned short)0;
         }
+#pragma unroll
+        for (int u = 0; u < SCB; ++u)
+            if (i0 + lane + 32 * u < sc_count) fold_scale(i0 + lane + 32 * u, sreg[u], zreg[u]);
+    }
+    for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB * blockDim.x) {
+#pragma unroll
+        for (int u = 0; u < XB; ++u) {
+            const int i = i0 + tid + u * blockDim.x;
+            xm[u] = -1;
+            if (i < x_count) load_x_block(i, xv[u], xm[u], xb[u], xk[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < XB; ++u)
+            if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     }
     __syncthreads();
 
@@ -253,117 +469,98 @@ gemv_stream_kernel(const StreamParams p)
     T* out = static_cast<T*>(p.out);
     bool gave_up = false;
 
-    int j = 0;
+    int stage = 0;
+    uint32_t parity = 0;
     for (int rbi = 0; rbi < nrb && !gave_up; ++rbi) {
-        float part[NT][2][4], tot[NT][4];
+        float plo[NT][4], phi[NT][4], tot[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { part[nt][0][i] = 0.f; part[nt][1][i] = 0.f; tot[nt][i] = 0.f; }
+            for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; tot[nt][i] = 0.f; }
         int steps_left = (p.steps_per_group == INT_MAX)
                              ? INT_MAX
                              : p.steps_per_group - (step_begin % p.steps_per_group);
-        int seg = 0;
-        const unsigned short* s0p = ssc + (rbi * 16 + r) * p.segs;
-        const unsigned short* s1p = s0p + 8 * p.segs;
-        const unsigned short* z0p = szr + (rbi * 16 + r) * p.segs;
-        const unsigned short* z1p = z0p + 8 * p.segs;
-        int s = 0;   // step index inside the chunk
+        const float* S0p = sS + (rbi * 16 + wr) * p.segs;   // advanced as groups close
+        const float* S1p = S0p + 8 * p.segs;
+        const float* Z0p = sZ + (rbi * 16 + wr) * p.segs;
+        const float* Z1p = Z0p + 8 * p.segs;
+        const float* Xp = xsum;
+        int s = 0;          // step index inside the chunk
+        int xoff = 0;       // byte offset of step s in the staged activation rows
+        int bytes_left = byte_end - byte_begin;
 
-        for (int pc = 0; pc < ppr; ++pc, ++j) {
-            const int stage = j % p.stages;
-            const uint32_t parity = (j / p.stages) & 1;
+        for (int pc = 0; pc < ppr; ++pc) {
             if (!mbar_wait(smem_u32(&bars[stage]), parity)) { gave_up = true; break; }
-            const int b0 = pc * CH;
-            const int bytes = min(CH, byte_end - byte_begin - b0);
-            const int psteps = (bytes + kStepBytes - 1) / kStepBytes;
-            const unsigned char* st0 = ring + (size_t)stage * stage_bytes + r * RS + t * 16;
+            const unsigned char* st0 = ring + stage * STAGE_BYTES + wr * RS + t * 16;
             const unsigned char* st1 = st0 + 8 * RS;
-            for (int ps = 0; ps < psteps; ++ps, ++s) {
-                const bool valid = (ps * kStepBytes + t * 16 + 16 <= bytes);
-                uint4 wa = make_uint4(0, 0, 0, 0), wb = make_uint4(0, 0, 0, 0);
-                if (valid) {
-                    wa = *reinterpret_cast<const uint4*>(st0 + ps * kStepBytes);
-                    wb = *reinterpret_cast<const uint4*>(st1 + ps * kStepBytes);
+            if (bytes_left >= CH && group_is_step) {
+                // full piece, one quantisation group per step: fully unrolled
+                uint4 wa[PSTEPS], wb[PSTEPS];
+#pragma unroll
+                for (int ps = 0; ps < PSTEPS; ++ps) {
+                    wa[ps] = *reinterpret_cast<const uint4*>(st0 + ps * kStepBytes);
+                    wb[ps] = *reinterpret_cast<const uint4*>(st1 + ps * kStepBytes);
                 }
-                const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w};
-                const uint32_t bw[4] = {wb.x, wb.y, wb.z, wb.w};
-                if (QUANT == MNQ_INT4) {
+                float Sa[PSTEPS], Sb[PSTEPS], Za[PSTEPS], Zb[PSTEPS];
 #pragma unroll
-                    for (int jw = 0; jw < 4; ++jw) {
-                        uint32_t A[4], B[4];
-                        UnpackInt4<T>::run(aw[jw], A);
-                        UnpackInt4<T>::run(bw[jw], B);
-                        const int xoff = (s * STEP + (jw * 4 + t) * 8) * 2;
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff);
-                            mma_16x8x16<T>(part[nt][0], A[0], B[0], A[1], B[1], xv.x, xv.y);
-                            mma_16x8x16<T>(part[nt][1], A[2], B[2], A[3], B[3], xv.z, xv.w);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int jw = 0; jw < 4; jw += 2) {
-                        uint32_t A0[2], B0[2], A1[2], B1[2];
-                        UnpackInt8<T>::run(aw[jw], A0);
-                        UnpackInt8<T>::run(bw[jw], B0);
-                        UnpackInt8<T>::run(aw[jw + 1], A1);
-                        UnpackInt8<T>::run(bw[jw + 1], B1);
-                        const int xoff = (s * STEP + t * 16 + jw * 4) * 2;
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff);
-                            mma_16x8x16<T>(part[nt][0], A0[0], B0[0], A0[1], B0[1], xv.x, xv.y);
-                            mma_16x8x16<T>(part[nt][1], A1[0], B1[0], A1[1], B1[1], xv.z, xv.w);
-                        }
-                    }
+                for (int q4 = 0; q4 < PSTEPS; q4 += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(S0p + q4);
+                    const float4 b = *reinterpret_cast<const float4*>(S1p + q4);
+                    const float4 c = *reinterpret_cast<const float4*>(Z0p + q4);
+                    const float4 d = *reinterpret_cast<const float4*>(Z1p + q4);
+                    Sa[q4] = a.x; Sa[q4 + 1] = a.y; Sa[q4 + 2] = a.z; Sa[q4 + 3] = a.w;
+                    Sb[q4] = b.x; Sb[q4 + 1] = b.y; Sb[q4 + 2] = b.z; Sb[q4 + 3] = b.w;
+                    Za[q4] = c.x; Za[q4 + 1] = c.y; Za[q4 + 2] = c.z; Za[q4 + 3] = c.w;
+                    Zb[q4] = d.x; Zb[q4 + 1] = d.y; Zb[q4 + 2] = d.z; Zb[q4 + 3] = d.w;
                 }
-                if (--steps_left == 0 || s == nsteps - 1) {
-                    const float sc0 = (p.scale_dtype == MNQ_BF16)
-                                          ? __uint_as_float((uint32_t)s0p[seg] << 16)
-                                          : __half2float(__ushort_as_half(s0p[seg]));
-                    const float sc1 = (p.scale_dtype == MNQ_BF16)
-                                          ? __uint_as_float((uint32_t)s1p[seg] << 16)
-                                          : __half2float(__ushort_as_half(s1p[seg]));
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        tot[nt][0] = fmaf(sc0, part[nt][0][0] + part[nt][1][0], tot[nt][0]);
-                        tot[nt][1] = fmaf(sc0, part[nt][0][1] + part[nt][1][1], tot[nt][1]);
-                        tot[nt][2] = fmaf(sc1, part[nt][0][2] + part[nt][1][2], tot[nt][2]);
-                        tot[nt][3] = fmaf(sc1, part[nt][0][3] + part[nt][1][3], tot[nt][3]);
+                for (int ps = 0; ps < PSTEPS; ++ps) {
+                    step_mma<QUANT, T, NT, true>(wa[ps], wb[ps], xrow, xoff + ps * STEP * 2, t, plo, phi);
+                    close_group<QUANT, T, NT>(tot, plo, phi, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8), t);
+                }
+                s += PSTEPS;
+                xoff += PSTEPS * STEP * 2;
+                S0p += PSTEPS; S1p += PSTEPS; Z0p += PSTEPS; Z1p += PSTEPS;
+                Xp += PSTEPS * (NT * 8);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) { part[nt][0][i] = 0.f; part[nt][1][i] = 0.f; }
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; }
+            } else {
+                const int bytes = min(CH, bytes_left);
+                const int psteps = (bytes + kStepBytes - 1) / kStepBytes;
+                for (int ps = 0; ps < psteps; ++ps, ++s, xoff += STEP * 2) {
+                    // bytes of this piece past the chunk end belong to the next chunk
+                    const bool valid = (ps * kStepBytes + t * 16 + 16 <= bytes);
+                    uint4 wa = make_uint4(0, 0, 0, 0), wb = make_uint4(0, 0, 0, 0);
+                    if (valid) {
+                        wa = *reinterpret_cast<const uint4*>(st0 + ps * kStepBytes);
+                        wb = *reinterpret_cast<const uint4*>(st1 + ps * kStepBytes);
                     }
-                    if (has_zero) {
-                        const float z0 = (p.scale_dtype == MNQ_BF16)
-                                             ? __uint_as_float((uint32_t)z0p[seg] << 16)
-                                             : __half2float(__ushort_as_half(z0p[seg]));
-                        const float z1 = (p.scale_dtype == MNQ_BF16)
-                                             ? __uint_as_float((uint32_t)z1p[seg] << 16)
-                                             : __half2float(__ushort_as_half(z1p[seg]));
+                    step_mma<QUANT, T, NT, false>(wa, wb, xrow, xoff, t, plo, phi);
+                    if (--steps_left == 0 || s == nsteps - 1) {
+                        close_group<QUANT, T, NT>(tot, plo, phi, *S0p, *S1p, *Z0p, *Z1p, Xp, t);
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            const float2 xsv =
-                                *reinterpret_cast<const float2*>(&xsum[seg * (NT * 8) + nt * 8 + 2 * t]);
-                            tot[nt][0] = fmaf(-z0, xsv.x, tot[nt][0]);
-                            tot[nt][1] = fmaf(-z0, xsv.y, tot[nt][1]);
-                            tot[nt][2] = fmaf(-z1, xsv.x, tot[nt][2]);
-                            tot[nt][3] = fmaf(-z1, xsv.y, tot[nt][3]);
-                        }
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; }
+                        steps_left = p.steps_per_group;
+                        ++S0p; ++S1p; ++Z0p; ++Z1p;
+                        Xp += NT * 8;
                     }
-                    steps_left = p.steps_per_group;
-                    ++seg;
                 }
             }
+            bytes_left -= CH;
             __syncwarp();   // every lane is done reading this stage
-            if (j + p.stages < total_pieces) issue_piece(j + p.stages);
+            if (iss_count < total_pieces) issue_piece();
+            if (++stage == p.stages) { stage = 0; parity ^= 1u; }
         }
         if (gave_up) break;
 
         // ---- epilogue of this row block ---------------------------------------------------
+        // Accumulator i of tile nt is output (m = nt*8 + 2t + (i&1), n = n0 or n1).
         const int rb = rb_first + rbi;
-        const int n0 = rb * 16 + r;
+        const int n0 = rb * 16 + wr;
         const int n1 = n0 + 8;
         if (p.num_chunks == 1) {
 #pragma unroll
@@ -406,15 +603,17 @@ gemv_stream_kernel(const StreamParams p)
                 }
             }
         __syncwarp();
-        if (lane == 0) p.counters[rb] = 0u;   // leave the workspace ready for the next call
+        if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
     }
 
     if (gave_up) {
         if (lane == 0) atomicOr(&g_device_status, 1u);
-        // Copies already issued may still land in this CTA's shared memory: give each
-        // outstanding stage one more bounded wait before the CTA exits.
-        for (int jj = j; jj < total_pieces && jj < j + p.stages; ++jj)
-            mbar_wait(smem_u32(&bars[jj % p.stages]), (jj / p.stages) & 1);
+        // Copies already requested may still land in this CTA's shared memory: give each
+        // stage one more bounded wait before the CTA exits.
+        for (int k = 0; k < p.stages; ++k) {
+            mbar_wait(smem_u32(&bars[stage]), parity);
+            if (++stage == p.stages) { stage = 0; parity ^= 1u; }
+        }
     }
 }
 
@@ -438,16 +637,17 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     pl.nt = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
     pl.total_steps = static_cast<int>((row_bytes + kStepBytes - 1) / kStepBytes);
     const int64_t row_blocks = (a.N + 15) / 16;
-    const bool has_zero = a.zeros != nullptr;
 
-    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : 8;
+    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : 16;
     if (warps > 16) warps = 16;
     while (warps > 1 && row_blocks < warps) warps >>= 1;
     pl.warps = warps;
     pl.piece_bytes = (tuning && tuning->piece_bytes > 0) ? tuning->piece_bytes : 256;
-    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : 3;
+    if (pl.piece_bytes != 256 && pl.piece_bytes != 512) return false;
+    if (pl.nt > 1) pl.piece_bytes = 256;
+    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : 2;
     if (pl.stages > 8) pl.stages = 8;
-    if (pl.piece_bytes % 64) return false;
+    if (pl.stages < 2) pl.stages = 2;
     const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : 1;
     const int64_t slots = static_cast<int64_t>(a.sm_count) * ctas_per_sm * warps;
 
@@ -472,21 +672,26 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         if (rbw < 1) rbw = 1;
         pl.rbw = rbw;
         const int64_t chunk_k = static_cast<int64_t>(pl.steps_per_chunk) * step;
-        pl.segs = (a.group_size >= a.K) ? 1 : static_cast<int>(chunk_k / a.group_size + 2);
+        int segs = (a.group_size >= a.K) ? 1 : static_cast<int>(chunk_k / a.group_size + 1);
+        pl.segs = (segs + 3) & ~3;
         const int row_pad = (a.quant == MNQ_INT4) ? 64 : 16;
         pl.xs_stride = static_cast<int>(((chunk_k * 2 + 127) / 128) * 128 + row_pad);
-        const size_t ring = static_cast<size_t>(pl.stages) * 16 * (pl.piece_bytes + 64);
-        const size_t sc = ((static_cast<size_t>(rbw) * 16 * pl.segs * 2 * (has_zero ? 2 : 1)) + 15) & ~size_t(15);
-        pl.smem = static_cast<size_t>(a.M) * pl.xs_stride + static_cast<size_t>(pl.segs) * pl.nt * 8 * 4 + 128 +
-                  static_cast<size_t>(warps) * (ring + sc + 64);
+        const size_t ring = static_cast<size_t>(pl.stages) * 16 * pl.piece_bytes;
+        const size_t sc = static_cast<size_t>(rbw) * 16 * pl.segs * 8;
+        pl.smem = ((static_cast<size_t>(a.M) * pl.xs_stride + static_cast<size_t>(pl.segs) * pl.nt * 8 * 4 + 1023) &
+                   ~size_t(1023)) + static_cast<size_t>(warps) * (ring + sc + 128);
         size_t need_ws = 0;
-        if (pl.num_chunks > 1)
-            need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
+        if (pl.num_chunks > 1) need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
         const bool smem_ok = pl.smem <= kMaxSmem;
         const bool ws_ok = need_ws <= workspace_bytes;
         if (smem_ok && ws_ok) break;
         if (!smem_ok) {
             if (pl.stages > 2) { --pl.stages; continue; }
+            if (warps > 4 && !(tuning && tuning->warps_per_cta > 0)) {
+                warps >>= 1;
+                pl.warps = warps;
+                continue;   // `slots` keeps counting the original warps: rbw grows instead
+            }
             if (chunks >= pl.total_steps || chunks >= kMaxSplitK) return false;
             ++chunks;
             continue;
@@ -494,32 +699,36 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         if (chunks == 1) return false;
         --chunks;
     }
-    pl.grid_x = static_cast<unsigned>((row_blocks + static_cast<int64_t>(warps) * rbw - 1) /
-                                      (static_cast<int64_t>(warps) * rbw));
+    pl.grid_x = static_cast<unsigned>((row_blocks + static_cast<int64_t>(pl.warps) * rbw - 1) /
+                                      (static_cast<int64_t>(pl.warps) * rbw));
     *out = pl;
     return true;
 }
 
-template <int QUANT, typename T, int NT>
-int launch_stream_one(const StreamParams& p, dim3 grid, int threads, size_t smem, cudaStream_t stream)
+template <int QUANT, typename T, int NT, int CH>
+int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, dim3 grid, int threads, size_t smem,
+                      cudaStream_t stream)
 {
-    auto* kern = &gemv_stream_kernel<QUANT, T, NT>;
+    auto* kern = &gemv_stream_kernel<QUANT, T, NT, CH>;
     if (smem > 48 * 1024) {
         const int rc = check_cuda(
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem),
             "cudaFuncSetAttribute(gemv_stream)");
         if (rc) return rc;
     }
-    kern<<<grid, threads, smem, stream>>>(p);
+    kern<<<grid, threads, smem, stream>>>(p, wmap);
     return check_cuda(cudaGetLastError(), "gemv_stream launch");
 }
 
 template <int QUANT, typename T>
-int launch_stream_nt(const StreamParams& p, int nt, dim3 grid, int threads, size_t smem, cudaStream_t stream)
+int launch_stream_nt(const StreamParams& p, const CUtensorMap& wmap, int nt, int ch, dim3 grid, int threads,
+                     size_t smem, cudaStream_t stream)
 {
-    if (nt == 1) return launch_stream_one<QUANT, T, 1>(p, grid, threads, smem, stream);
-    if (nt == 2) return launch_stream_one<QUANT, T, 2>(p, grid, threads, smem, stream);
-    return launch_stream_one<QUANT, T, 4>(p, grid, threads, smem, stream);
+    // 512-byte pieces only for NT == 1: wider activation tiles run out of registers
+    if (nt == 1 && ch == 512) return launch_stream_one<QUANT, T, 1, 512>(p, wmap, grid, threads, smem, stream);
+    if (nt == 1) return launch_stream_one<QUANT, T, 1, 256>(p, wmap, grid, threads, smem, stream);
+    if (nt == 2) return launch_stream_one<QUANT, T, 2, 256>(p, wmap, grid, threads, smem, stream);
+    return launch_stream_one<QUANT, T, 4, 256>(p, wmap, grid, threads, smem, stream);
 }
 
 }  // namespace
@@ -548,16 +757,23 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.steps_per_chunk = pl.steps_per_chunk; p.total_steps = pl.total_steps; p.num_chunks = pl.num_chunks;
     p.segs = pl.segs; p.xs_stride = pl.xs_stride;
     p.x_vec_ok = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && (a.lda % 8 == 0);
-    p.rbw = pl.rbw; p.piece_bytes = pl.piece_bytes; p.stages = pl.stages;
+    p.rbw = pl.rbw; p.stages = pl.stages;
     p.row_blocks = static_cast<int>((a.N + 15) / 16);
     if (pl.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
+    // packed weights as a [N, row_bytes / 4] tensor of 32-bit words; box = 16 rows x CH bytes
+    CUtensorMap wmap;
+    const int rc = encode_tensor_map_2d(&wmap, a.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4,
+                                        static_cast<uint64_t>(p.row_bytes) / 4, static_cast<uint64_t>(a.N),
+                                        static_cast<uint64_t>(p.row_bytes), pl.piece_bytes / 4, 16,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
-#define MNQ_GS(Q, T) return launch_stream_nt<Q, T>(p, pl.nt, grid, threads, pl.smem, a.stream)
+#define MNQ_GS(Q, T) return launch_stream_nt<Q, T>(p, wmap, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_GS(MNQ_INT4, __half);
         MNQ_GS(MNQ_INT4, __nv_bfloat16);

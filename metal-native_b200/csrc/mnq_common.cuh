@@ -223,6 +223,14 @@ constexpr size_t kCounterBytes = 64 * 1024;
 constexpr int64_t kMaxCounters = kCounterBytes / 4;
 
 // Launchers (each returns an mnq_status)
+#ifdef CUDA_VERSION  // <cuda.h> included by the translation unit
+// Encodes a 2-D tiled TMA descriptor through the driver entry point obtained at run time
+// (no link-time dependency on libcuda).  dim0 is the contiguous dimension; sizes in
+// elements, the row pitch in bytes (a multiple of 16), the base 16-byte aligned.
+int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                         uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1,
+                         CUtensorMapSwizzle swizzle);
+#endif
 int launch_generic(const MatmulArgs& a);
 bool gemv_supported(const MatmulArgs& a);
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
