@@ -65,6 +65,7 @@ struct StreamParams {
     long long lda, ldc;
     int row_bytes;
     int group_size;       // INT_MAX: single group
+    int group_shift;      // log2(group_size) if it is a power of two, else -1
     int steps_per_group;  // INT_MAX: single group
     int G;
     int scale_dtype;
@@ -142,11 +143,15 @@ __device__ __forceinline__ void mma_c<__nv_bfloat16>(float (&d)[4], uint32_t a0,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
 
-// Encodings (see the header comment).  inv_alpha multiplies the scale; hi_factor brings
-// the second accumulator chain to the first one's scaling; offset = beta + c.
+// Encodings (see the header comment).  inv_alpha multiplies the scale; offset = beta + c.
+// hi_x_scale: the high-nibble encoding of int4/fp16 is 16 times larger than the low-nibble
+// one, so the activations those MMAs consume are staged pre-multiplied by 1/16 (exact in
+// fp16 down to |x| = 2^-10; below that the lost bits are worth less than 2^-25 each) and
+// both encodings accumulate into one fp32 chain.
 template <int QUANT, typename T> struct Enc;
 template <> struct Enc<MNQ_INT4, __half> {
-    static constexpr float inv_alpha = 16777216.f, hi_factor = 0.0625f, offset = 8.f;
+    static constexpr float inv_alpha = 16777216.f, offset = 8.f;
+    static constexpr bool hi_x_scale = true;
     // (n0,n4) (n1,n5) (n2,n6) (n3,n7) as L0 H0 L1 H1
     static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
     {
@@ -155,7 +160,8 @@ template <> struct Enc<MNQ_INT4, __half> {
     }
 };
 template <> struct Enc<MNQ_INT4, __nv_bfloat16> {
-    static constexpr float inv_alpha = 1.f, hi_factor = 1.f, offset = 136.f;
+    static constexpr float inv_alpha = 1.f, offset = 136.f;
+    static constexpr bool hi_x_scale = false;
     static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
     {
         constexpr uint32_t M = 0x000F000Fu, MAGIC = 0x43004300u;
@@ -164,7 +170,8 @@ template <> struct Enc<MNQ_INT4, __nv_bfloat16> {
     }
 };
 template <> struct Enc<MNQ_INT8, __half> {
-    static constexpr float inv_alpha = 16777216.f, hi_factor = 1.f, offset = 128.f;
+    static constexpr float inv_alpha = 16777216.f, offset = 128.f;
+    static constexpr bool hi_x_scale = false;
     static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
     {
         const uint32_t u = w ^ 0x80808080u;
@@ -172,7 +179,8 @@ template <> struct Enc<MNQ_INT8, __half> {
     }
 };
 template <> struct Enc<MNQ_INT8, __nv_bfloat16> {
-    static constexpr float inv_alpha = 1.f, hi_factor = 1.f, offset = 0.f;
+    static constexpr float inv_alpha = 1.f, offset = 0.f;
+    static constexpr bool hi_x_scale = false;
     static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
     {
         uint32_t o[2];
@@ -181,11 +189,13 @@ template <> struct Enc<MNQ_INT8, __nv_bfloat16> {
     }
 };
 
-// One step: 64 packed bytes of 16 rows against NT x 8 activation rows.  plo / phi are two
-// independent accumulator chains; with ZERO_START they start from zero in this step.
+// One step: 64 packed bytes of 16 rows against NT x 8 activation rows, accumulated into
+// acc (one chain of 8 MMAs; with ZERO_START it starts from zero in this step).  xb[nt] points
+// at this lane's 16 bytes of the step's first 8-block (int4) / 32 bytes (int8) in the staged
+// activation row; all further offsets are compile-time constants.
 template <int QUANT, typename T, int NT, bool ZERO_START>
-__device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const unsigned char* const (&xrow)[NT],
-                                         int xoff, int t, float (&plo)[NT][4], float (&phi)[NT][4])
+__device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const unsigned char* const (&xb)[NT],
+                                         float (&acc)[NT][4])
 {
     const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w};
     const uint32_t bw[4] = {wb.x, wb.y, wb.z, wb.w};
@@ -197,14 +207,12 @@ __device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const
             Enc<MNQ_INT4, T>::run(bw[jw], bL0, bH0, bL1, bH1);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff + (jw * 4 + t) * 16);
-                if (ZERO_START && jw == 0) {
-                    mma_c<T>(plo[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
-                    mma_c<T>(phi[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, 0.f, 0.f, 0.f, 0.f);
-                } else {
-                    mma_c<T>(plo[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, plo[nt][0], plo[nt][1], plo[nt][2], plo[nt][3]);
-                    mma_c<T>(phi[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, phi[nt][0], phi[nt][1], phi[nt][2], phi[nt][3]);
-                }
+                const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + jw * 64);
+                if (ZERO_START && jw == 0)
+                    mma_c<T>(acc[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
+                else
+                    mma_c<T>(acc[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+                mma_c<T>(acc[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
             }
         }
     } else {
@@ -217,36 +225,30 @@ __device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const
             Enc<MNQ_INT8, T>::run(bw[jw + 1], d0, d1);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xrow[nt] + xoff + (t * 16 + jw * 4) * 2);
-                if (ZERO_START && jw == 0) {
-                    mma_c<T>(plo[nt], a0, b0, a1, b1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
-                    mma_c<T>(phi[nt], c0, d0, c1, d1, xv.z, xv.w, 0.f, 0.f, 0.f, 0.f);
-                } else {
-                    mma_c<T>(plo[nt], a0, b0, a1, b1, xv.x, xv.y, plo[nt][0], plo[nt][1], plo[nt][2], plo[nt][3]);
-                    mma_c<T>(phi[nt], c0, d0, c1, d1, xv.z, xv.w, phi[nt][0], phi[nt][1], phi[nt][2], phi[nt][3]);
-                }
+                const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + jw * 8);
+                if (ZERO_START && jw == 0)
+                    mma_c<T>(acc[nt], a0, b0, a1, b1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
+                else
+                    mma_c<T>(acc[nt], a0, b0, a1, b1, xv.x, xv.y, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+                mma_c<T>(acc[nt], c0, d0, c1, d1, xv.z, xv.w, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
             }
         }
     }
 }
 
-// tot += S * (plo + hi_factor * phi) - Z * X for the lane's two rows (S0/Z0: row r, S1/Z1: row r+8)
-template <int QUANT, typename T, int NT>
-__device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&plo)[NT][4], const float (&phi)[NT][4],
-                                            float S0, float S1, float Z0, float Z1, const float* xsum_seg, int t)
+// tot += S * acc - Z * X for the lane's two rows (S0/Z0: row r, S1/Z1: row r+8).  xsum_lane
+// points at this lane's pair of activation sums of the group (columns 2t, 2t+1 of tile 0).
+template <int NT>
+__device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&acc)[NT][4], float S0, float S1,
+                                            float Z0, float Z1, const float* xsum_lane)
 {
-    constexpr float HF = Enc<QUANT, T>::hi_factor;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const float2 X = *reinterpret_cast<const float2*>(xsum_seg + nt * 8 + 2 * t);
-        const float v0 = fmaf(phi[nt][0], HF, plo[nt][0]);
-        const float v1 = fmaf(phi[nt][1], HF, plo[nt][1]);
-        const float v2 = fmaf(phi[nt][2], HF, plo[nt][2]);
-        const float v3 = fmaf(phi[nt][3], HF, plo[nt][3]);
-        tot[nt][0] = fmaf(-Z0, X.x, fmaf(S0, v0, tot[nt][0]));
-        tot[nt][1] = fmaf(-Z0, X.y, fmaf(S0, v1, tot[nt][1]));
-        tot[nt][2] = fmaf(-Z1, X.x, fmaf(S1, v2, tot[nt][2]));
-        tot[nt][3] = fmaf(-Z1, X.y, fmaf(S1, v3, tot[nt][3]));
+        const float2 X = *reinterpret_cast<const float2*>(xsum_lane + nt * 8);
+        tot[nt][0] = fmaf(-Z0, X.x, fmaf(S0, acc[nt][0], tot[nt][0]));
+        tot[nt][1] = fmaf(-Z0, X.y, fmaf(S0, acc[nt][1], tot[nt][1]));
+        tot[nt][2] = fmaf(-Z1, X.x, fmaf(S1, acc[nt][2], tot[nt][2]));
+        tot[nt][3] = fmaf(-Z1, X.y, fmaf(S1, acc[nt][3], tot[nt][3]));
     }
 }
 
@@ -334,9 +336,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // pieces are requested; only then are the small loads consumed.
     for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsum[i] = 0.f;
 
-    constexpr int SCB = 16;                        // scale loads in flight per lane
+    constexpr int SCB = 8;                         // scale pairs in flight per lane (32 groups per row)
     constexpr int XB = (NT == 1) ? 2 : 4;          // activation loads in flight per thread
-    const int sc_count = nrb * 16 * p.segs;
     const int blocks_per_row = nsteps * (STEP / 8);
     const int x_count = p.M * blocks_per_row;
     const T* xg = static_cast<const T*>(p.x);
@@ -344,7 +345,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
 
     auto load_x_block = [&](int i, uint32_t (&v)[4], int& m, int& b, int& k) {
-        m = i / blocks_per_row;
+        m = (p.M == 1) ? 0 : i / blocks_per_row;
         b = i - m * blocks_per_row;
         k = k_begin + b * 8;
         if (p.x_vec_ok && k + 8 <= p.K) {
@@ -369,7 +370,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             sum += F16Traits<T>::to_float(*reinterpret_cast<const T*>(&lo)) +
                    F16Traits<T>::to_float(*reinterpret_cast<const T*>(&hi));
         }
-        const int sg = (p.group_size == INT_MAX) ? 0 : (k / p.group_size - seg0);
+        const int sg = (p.group_size == INT_MAX) ? 0
+                     : (p.group_shift >= 0 ? (k >> p.group_shift) : k / p.group_size) - seg0;
         atomicAdd(&xsum[sg * (NT * 8) + m], sum);
         int pos;
         uint4 o;
@@ -384,38 +386,77 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             o.y = prmt(v[1], v[3], 0x5410u);   // (x2, x6)
             o.z = prmt(v[0], v[2], 0x7632u);   // (x1, x5)
             o.w = prmt(v[1], v[3], 0x7632u);   // (x3, x7)
+            if (Enc<QUANT, T>::hi_x_scale) {
+                const __half2 k16 = __half2half2(__ushort_as_half(0x2C00));   // 1/16
+                o.z = h2_as_u32(__hmul2(u32_as_h2(o.z), k16));
+                o.w = h2_as_u32(__hmul2(u32_as_h2(o.w), k16));
+            }
         } else {
             pos = b * 8;
             o.x = v[0]; o.y = v[1]; o.z = v[2]; o.w = v[3];
         }
         *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
     };
-    auto sc_index = [&](int i, bool& ok) -> size_t {
-        const int rr = i / p.segs;   // rbi * 16 + row
-        const int sg = i - rr * p.segs;
-        const int n = rb_first * 16 + rr;
-        const int g = seg0 + sg;
-        ok = (i < sc_count) && (n < p.N) && (g < p.G);
-        return (size_t)n * p.G + g;
+    // Scales / zeros of one row block: lane = (row, half); each lane owns segs/2 consecutive
+    // groups of its row, fetched as 32-bit pairs where the address allows.  `batch` selects
+    // which SCB pairs of the lane's share (one batch covers 4*SCB groups per row).
+    const int sc_row = lane >> 1;
+    const int sc_col0 = (lane & 1) * (p.segs >> 1);
+    auto load_scale_pairs = [&](int rbi, int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
+        const int n = (rb_first + rbi) * 16 + sc_row;
+        const size_t e0 = (size_t)n * p.G + seg0 + sc_col0;
+        const bool row_ok = (rbi < nrb) && (n < p.N);
+        const bool even = ((e0 & 1) == 0);
+#pragma unroll
+        for (int u = 0; u < SCB; ++u) {
+            const int c = (batch * SCB + u) * 2;           // column inside the lane's share
+            const int g = seg0 + sc_col0 + c;
+            const bool in_share = c < (p.segs >> 1);
+            const bool ok0 = row_ok && in_share && g < p.G;
+            const bool ok1 = row_ok && in_share && g + 1 < p.G;
+            uint32_t sv = 0, zv = 0;
+            if (ok1 && even) {
+                sv = __ldg(reinterpret_cast<const uint32_t*>(sc16 + e0 + c));
+                if (has_zero) zv = __ldg(reinterpret_cast<const uint32_t*>(zr16 + e0 + c));
+            } else if (ok0) {
+                sv = __ldg(sc16 + e0 + c);
+                if (has_zero) zv = __ldg(zr16 + e0 + c);
+                if (ok1) {
+                    sv |= (uint32_t)__ldg(sc16 + e0 + c + 1) << 16;
+                    if (has_zero) zv |= (uint32_t)__ldg(zr16 + e0 + c + 1) << 16;
+                }
+            }
+            sp[u] = sv; zp[u] = zv;
+        }
     };
-    auto fold_scale = [&](int i, unsigned short sb, unsigned short zb) {
-        const float sv = (p.scale_dtype == MNQ_BF16) ? __uint_as_float((uint32_t)sb << 16)
-                                                     : __half2float(__ushort_as_half(sb));
-        const float zv = (p.scale_dtype == MNQ_BF16) ? __uint_as_float((uint32_t)zb << 16)
-                                                     : __half2float(__ushort_as_half(zb));
-        sS[i] = sv * Enc<QUANT, T>::inv_alpha;
-        sZ[i] = fmaf(Enc<QUANT, T>::offset, sv, zv);
+    auto fold_scale_pairs = [&](int rbi, int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
+        float* dS = sS + (rbi * 16 + sc_row) * p.segs + sc_col0;
+        float* dZ = sZ + (rbi * 16 + sc_row) * p.segs + sc_col0;
+#pragma unroll
+        for (int u = 0; u < SCB; ++u) {
+            const int c = (batch * SCB + u) * 2;
+            if (rbi < nrb && c < (p.segs >> 1)) {
+                float s0, s1, z0, z1;
+                if (p.scale_dtype == MNQ_BF16) {
+                    s0 = __uint_as_float(sp[u] << 16); s1 = __uint_as_float(sp[u] & 0xFFFF0000u);
+                    z0 = __uint_as_float(zp[u] << 16); z1 = __uint_as_float(zp[u] & 0xFFFF0000u);
+                } else {
+                    const float2 sf = __half22float2(u32_as_h2(sp[u]));
+                    const float2 zf = __half22float2(u32_as_h2(zp[u]));
+                    s0 = sf.x; s1 = sf.y; z0 = zf.x; z1 = zf.y;
+                }
+                *reinterpret_cast<float2*>(dS + c) =
+                    make_float2(s0 * Enc<QUANT, T>::inv_alpha, s1 * Enc<QUANT, T>::inv_alpha);
+                *reinterpret_cast<float2*>(dZ + c) =
+                    make_float2(fmaf(Enc<QUANT, T>::offset, s0, z0), fmaf(Enc<QUANT, T>::offset, s1, z1));
+            }
+        }
     };
+    const int sc_batches = ((p.segs >> 2) + SCB - 1) / SCB;   // pairs per lane = segs / 4
 
     // first batch of small loads (the only one for the benchmark shapes)
-    unsigned short sreg[SCB], zreg[SCB];
-#pragma unroll
-    for (int u = 0; u < SCB; ++u) {
-        bool ok;
-        const size_t idx = sc_index(lane + 32 * u, ok);
-        sreg[u] = ok ? __ldg(sc16 + idx) : (unsigned short)0;
-        zreg[u] = (ok && has_zero) ? __ldg(zr16 + idx) : (unsigned short)0;
-    }
+    uint32_t sreg[SCB], zreg[SCB];
+    load_scale_pairs(0, 0, sreg, zreg);
     uint32_t xv[XB][4];
     int xm[XB], xb[XB], xk[XB];
 #pragma unroll
@@ -430,25 +471,16 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     __syncthreads();   // xsum is zeroed
 
     // consume the small loads
-#pragma unroll
-    for (int u = 0; u < SCB; ++u)
-        if (lane + 32 * u < sc_count) fold_scale(lane + 32 * u, sreg[u], zreg[u]);
+    fold_scale_pairs(0, 0, sreg, zreg);
 #pragma unroll
     for (int u = 0; u < XB; ++u)
         if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     // whatever did not fit in the first batch (several row blocks per warp, many groups, M > 8)
-    for (int i0 = SCB * 32; i0 < sc_count; i0 += SCB * 32) {
-#pragma unroll
-        for (int u = 0; u < SCB; ++u) {
-            bool ok;
-            const size_t idx = sc_index(i0 + lane + 32 * u, ok);
-            sreg[u] = ok ? __ldg(sc16 + idx) : (unsigned short)0;
-            zreg[u] = (ok && has_zero) ? __ldg(zr16 + idx) : (unsigned short)0;
+    for (int rbi = 0; rbi < nrb; ++rbi)
+        for (int batch = (rbi == 0 ? 1 : 0); batch < sc_batches; ++batch) {
+            load_scale_pairs(rbi, batch, sreg, zreg);
+            fold_scale_pairs(rbi, batch, sreg, zreg);
         }
-#pragma unroll
-        for (int u = 0; u < SCB; ++u)
-            if (i0 + lane + 32 * u < sc_count) fold_scale(i0 + lane + 32 * u, sreg[u], zreg[u]);
-    }
     for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB * blockDim.x) {
 #pragma unroll
         for (int u = 0; u < XB; ++u) {
@@ -463,20 +495,24 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     __syncthreads();
 
     // ---- main loop ----------------------------------------------------------------------------
+    // this lane's position inside a staged activation row: 16 bytes per 8-block at lane t (int4),
+    // 32 bytes at lane t (int8)
+    const int x_lane_off = (QUANT == MNQ_INT4) ? t * 16 : t * 32;
     const unsigned char* xrow[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) xrow[nt] = xs + (size_t)min(nt * 8 + r, p.M - 1) * p.xs_stride;
+    for (int nt = 0; nt < NT; ++nt)
+        xrow[nt] = xs + (size_t)min(nt * 8 + r, p.M - 1) * p.xs_stride + x_lane_off;
     T* out = static_cast<T*>(p.out);
     bool gave_up = false;
 
     int stage = 0;
     uint32_t parity = 0;
     for (int rbi = 0; rbi < nrb && !gave_up; ++rbi) {
-        float plo[NT][4], phi[NT][4], tot[NT][4];
+        float acc[NT][4], tot[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; tot[nt][i] = 0.f; }
+            for (int i = 0; i < 4; ++i) { acc[nt][i] = 0.f; tot[nt][i] = 0.f; }
         int steps_left = (p.steps_per_group == INT_MAX)
                              ? INT_MAX
                              : p.steps_per_group - (step_begin % p.steps_per_group);
@@ -484,7 +520,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         const float* S1p = S0p + 8 * p.segs;
         const float* Z0p = sZ + (rbi * 16 + wr) * p.segs;
         const float* Z1p = Z0p + 8 * p.segs;
-        const float* Xp = xsum;
+        const float* Xp = xsum + 2 * t;
         int s = 0;          // step index inside the chunk
         int xoff = 0;       // byte offset of step s in the staged activation rows
         int bytes_left = byte_end - byte_begin;
@@ -513,19 +549,19 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     Za[q4] = c.x; Za[q4 + 1] = c.y; Za[q4 + 2] = c.z; Za[q4 + 3] = c.w;
                     Zb[q4] = d.x; Zb[q4 + 1] = d.y; Zb[q4 + 2] = d.z; Zb[q4 + 3] = d.w;
                 }
+                const unsigned char* xb[NT];
 #pragma unroll
                 for (int ps = 0; ps < PSTEPS; ++ps) {
-                    step_mma<QUANT, T, NT, true>(wa[ps], wb[ps], xrow, xoff + ps * STEP * 2, t, plo, phi);
-                    close_group<QUANT, T, NT>(tot, plo, phi, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8), t);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff + ps * STEP * 2;
+                    float a4[NT][4];
+                    step_mma<QUANT, T, NT, true>(wa[ps], wb[ps], xb, a4);
+                    close_group<NT>(tot, a4, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8));
                 }
                 s += PSTEPS;
                 xoff += PSTEPS * STEP * 2;
                 S0p += PSTEPS; S1p += PSTEPS; Z0p += PSTEPS; Z1p += PSTEPS;
                 Xp += PSTEPS * (NT * 8);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; }
             } else {
                 const int bytes = min(CH, bytes_left);
                 const int psteps = (bytes + kStepBytes - 1) / kStepBytes;
@@ -537,13 +573,16 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                         wa = *reinterpret_cast<const uint4*>(st0 + ps * kStepBytes);
                         wb = *reinterpret_cast<const uint4*>(st1 + ps * kStepBytes);
                     }
-                    step_mma<QUANT, T, NT, false>(wa, wb, xrow, xoff, t, plo, phi);
+                    const unsigned char* xb[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff;
+                    step_mma<QUANT, T, NT, false>(wa, wb, xb, acc);
                     if (--steps_left == 0 || s == nsteps - 1) {
-                        close_group<QUANT, T, NT>(tot, plo, phi, *S0p, *S1p, *Z0p, *Z1p, Xp, t);
+                        close_group<NT>(tot, acc, *S0p, *S1p, *Z0p, *Z1p, Xp);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { plo[nt][i] = 0.f; phi[nt][i] = 0.f; }
+                            for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
                         steps_left = p.steps_per_group;
                         ++S0p; ++S1p; ++Z0p; ++Z1p;
                         Xp += NT * 8;
@@ -753,6 +792,10 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     const bool single_group = a.group_size >= a.K;
     p.group_size = single_group ? INT_MAX : a.group_size;
     p.steps_per_group = single_group ? INT_MAX : a.group_size / step;
+    p.group_shift = -1;
+    if (!single_group && (a.group_size & (a.group_size - 1)) == 0)
+        for (int sh = 0; sh < 31; ++sh)
+            if ((1 << sh) == a.group_size) p.group_shift = sh;
     p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.steps_per_chunk = pl.steps_per_chunk; p.total_steps = pl.total_steps; p.num_chunks = pl.num_chunks;
     p.segs = pl.segs; p.xs_stride = pl.xs_stride;
