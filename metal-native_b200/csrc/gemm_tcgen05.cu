@@ -1,5 +1,466 @@
+// Prefill-shaped fused dequantise + matmul (M > 32) on the 5th-generation tensor cores.
+// Replaces the reference's tiled kernels dequant_matmul_int4_fp16 / dequant_matmul_int8_fp16
+// (shaders/matmul_dequant_kernel.metal:55-223, 351-479): dequantise a weight tile into
+// shared memory, multiply, fp32 accumulate, 16-bit store.
+//
+// Orientation.  The MMA's 128-row operand A is the WEIGHT tile (128 output columns n x 64 k,
+// K-major), its N-side operand B the ACTIVATION tile (TOK <= 256 tokens x 64 k, K-major), so
+// the accumulator in tensor memory is out^T: TMEM lane = n, TMEM column = token.  One CTA
+// therefore dequantises a weight tile once for up to 256 tokens.
+//
+// Roles (192 threads):
+//   warp 0      one lane issues the TMA loads of activation tiles (128-byte swizzle);
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 per 64-k block) and
+//               tcgen05.commit, which frees the stage and finally publishes the accumulator;
+//   warps 2-5   stream the packed weights from global memory (prefetched several k-blocks
+//               ahead in registers), dequantise to fp16 with one rounding
+//               (fma(q-8, s, -z) on exact integers) and write the 128-byte-swizzled K-major
+//               tile the MMA reads; afterwards they read the accumulator back with tcgen05.ld
+//               and store out[m, n].
+// bf16 activations take this path only with one scale per row and no zeros: the tile then
+// holds the exact integers and the scale is applied to the fp32 accumulator (rounding
+// dequantised weights to bf16 would cost 1.6e-3 relative error by itself).
+//
+// Every mbarrier wait is bounded; a wait that gives up sets bit 1 of the device status word
+// and the CTA falls through to its teardown (tensor memory is always released).
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "mnq_common.cuh"
+
 namespace mnq {
-bool gemm_supported(const MatmulArgs&) { return false; }
-int launch_gemm(const MatmulArgs&, const mnq_tuning*) { return fail(MNQ_NOT_IMPLEMENTED, "gemm path not built yet"); }
+
+// Own status word (device variables are per translation unit without relocatable device
+// code); read_device_status() in gemv_stream.cu merges it through read_gemm_status().
+__device__ unsigned int g_gemm_status = 0;
+
+namespace {
+
+constexpr int BN = 128;          // weight rows per CTA (MMA M)
+constexpr int BK = 64;           // k per stage: one 128-byte swizzle row of 16-bit elements
+constexpr int A_BYTES = BN * BK * 2;
+constexpr unsigned kSpin = 1u << 24;
+
+struct GemmParams {
+    const uint8_t* wq;
+    const void* scales;
+    const void* zeros;
+    void* out;
+    int M, N, K;
+    long long ldc;
+    int row_bytes;
+    int group_size;     // >= K: one group
+    int G;
+    int scale_dtype;
+    int tok;            // tokens per CTA tile (multiple of 16, <= 256)
+    int stages;
+    int tmem_cols;      // power of two >= max(32, tok)
+    int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
+};
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity)
+{
+    for (unsigned i = 0; i < kSpin; ++i)
+        if (bar_try(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// K-major, 128-byte swizzle shared-memory matrix descriptor: rows of 128 bytes, 8-row
+// groups 1024 bytes apart.  Start address, leading and stride byte offsets are in units
+// of 16 bytes; bits 46-47 = 1 (descriptor version of this architecture); bits 61-63 = 2
+// (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: fp32 accumulate, A and B both K-major, M = 128, N = tok.
+__device__ __forceinline__ uint32_t instr_desc(int tok, bool bf16)
+{
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tok >> 3) << 17) |
+           (static_cast<uint32_t>(BN >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+// 8 consecutive k of one row -> one 16-byte chunk of 16-bit values in natural k order.
+template <int QUANT, typename T> struct TileChunk;
+
+template <> struct TileChunk<MNQ_INT4, __half> {
+    static constexpr int WORDS = 1;   // packed 32-bit words per chunk
+    static __device__ __forceinline__ uint4 run(const uint32_t* w, __half2 s2, __half2 nz2)
+    {
+        uint32_t P[4];
+        UnpackInt4<__half>::run(w[0], P);   // (q0-8,q4-8) (q1-8,q5-8) (q2-8,q6-8) (q3-8,q7-8)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) P[i] = h2_as_u32(__hfma2(u32_as_h2(P[i]), s2, nz2));
+        uint4 o;
+        o.x = prmt(P[0], P[1], 0x5410u);   // (w0, w1)
+        o.y = prmt(P[2], P[3], 0x5410u);   // (w2, w3)
+        o.z = prmt(P[0], P[1], 0x7632u);   // (w4, w5)
+        o.w = prmt(P[2], P[3], 0x7632u);   // (w6, w7)
+        return o;
+    }
+};
+template <> struct TileChunk<MNQ_INT8, __half> {
+    static constexpr int WORDS = 2;
+    static __device__ __forceinline__ uint4 run(const uint32_t* w, __half2 s2, __half2 nz2)
+    {
+        uint32_t a[2], b[2];
+        UnpackInt8<__half>::run(w[0], a);
+        UnpackInt8<__half>::run(w[1], b);
+        uint4 o;
+        o.x = h2_as_u32(__hfma2(u32_as_h2(a[0]), s2, nz2));
+        o.y = h2_as_u32(__hfma2(u32_as_h2(a[1]), s2, nz2));
+        o.z = h2_as_u32(__hfma2(u32_as_h2(b[0]), s2, nz2));
+        o.w = h2_as_u32(__hfma2(u32_as_h2(b[1]), s2, nz2));
+        return o;
+    }
+};
+// bf16: exact integers, no scale here
+template <> struct TileChunk<MNQ_INT4, __nv_bfloat16> {
+    static constexpr int WORDS = 1;
+    static __device__ __forceinline__ uint4 run(const uint32_t* w, __half2, __half2)
+    {
+        uint32_t P[4];
+        UnpackInt4<__nv_bfloat16>::run(w[0], P);
+        uint4 o;
+        o.x = prmt(P[0], P[1], 0x5410u);
+        o.y = prmt(P[2], P[3], 0x5410u);
+        o.z = prmt(P[0], P[1], 0x7632u);
+        o.w = prmt(P[2], P[3], 0x7632u);
+        return o;
+    }
+};
+template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
+    static constexpr int WORDS = 2;
+    static __device__ __forceinline__ uint4 run(const uint32_t* w, __half2, __half2)
+    {
+        uint32_t a[2], b[2];
+        UnpackInt8<__nv_bfloat16>::run(w[0], a);
+        UnpackInt8<__nv_bfloat16>::run(w[1], b);
+        return make_uint4(a[0], a[1], b[0], b[1]);
+    }
+};
+
+template <int QUANT, typename T>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap)
+{
+    constexpr int WPK = (QUANT == MNQ_INT4) ? 2 : 4;   // 16-byte loads per row per k-block
+    constexpr int KB_BYTES = WPK * 16;                  // packed bytes per row per k-block
+    constexpr int U = 4;                                // k-blocks of weights in flight per thread
+    constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
+
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];   // full[8], empty[8], accum
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * p.tok;
+    const int num_kb = p.K / BK;
+    const int S = p.stages;
+    const int b_bytes = p.tok * 128;
+    const int stage_bytes = A_BYTES + b_bytes;
+    const uint32_t tiles = (s_u32(smem_raw) + 1023u) & ~1023u;   // 1024-byte aligned tile area
+    const uint32_t full0 = s_u32(&bars[0]), empty0 = s_u32(&bars[8]), accum = s_u32(&bars[16]);
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 5); bar_init(empty0 + 8 * s, 1); }
+        bar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(s_u32(&tmem_base_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---------------- activation tiles by TMA ----------------
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
+                bar_expect_tx(full0 + 8 * s, (uint32_t)b_bytes);
+                tma_load_tile(tiles + s * stage_bytes + A_BYTES, &xmap, kb * BK, m0, full0 + 8 * s);
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(p.tok, IS_BF16);
+            int s = 0; uint32_t ph = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!bar_wait(full0 + 8 * s, ph)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = tiles + s * stage_bytes;
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j)
+                    umma(tmem_base, smem_desc_sw128(a_addr + j * 32), smem_desc_sw128(b_addr + j * 32), idesc,
+                         (kb > 0 || j > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+            umma_commit(accum);                // accumulator complete
+        }
+    } else {
+        // ---------------- dequantise weight tiles, then epilogue ----------------
+        const int quad = warp & 3;             // tensor-memory lane quadrant this warp may read
+        const int row = quad * 32 + lane;      // row of the tile = TMEM lane
+        const int n = n0 + row;
+        const uint8_t* wrow = p.wq + (size_t)min(n, p.N - 1) * p.row_bytes;
+        const size_t sc_row = (size_t)min(n, p.N - 1) * p.G;
+        const bool one_group = p.group_size >= p.K;
+        const unsigned short* sc16 = static_cast<const unsigned short*>(p.scales);
+        const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
+
+        uint4 wreg[U][WPK];
+        uint32_t szreg[U];
+        auto prefetch = [&](int kb, int u) {
+            if (kb < num_kb) {
+#pragma unroll
+                for (int i = 0; i < WPK; ++i) wreg[u][i] = ldg_stream_16(wrow + (size_t)kb * KB_BYTES + i * 16);
+                const int g = one_group ? 0 : (kb * BK) / p.group_size;
+                uint32_t sz = __ldg(sc16 + sc_row + g);
+                if (zr16) sz |= (uint32_t)__ldg(zr16 + sc_row + g) << 16;
+                szreg[u] = sz;
+            }
+        };
+#pragma unroll
+        for (int u = 0; u < U; ++u) prefetch(u, u);
+
+        int s = 0; uint32_t ph = 0;
+        for (int kb0 = 0; kb0 < num_kb && !failed; kb0 += U) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int kb = kb0 + u;
+                if (kb >= num_kb || failed) break;
+                uint32_t w[WPK * 4];
+#pragma unroll
+                for (int i = 0; i < WPK; ++i) {
+                    w[4 * i] = wreg[u][i].x; w[4 * i + 1] = wreg[u][i].y;
+                    w[4 * i + 2] = wreg[u][i].z; w[4 * i + 3] = wreg[u][i].w;
+                }
+                const uint32_t sz = szreg[u];
+                prefetch(kb + U, u);
+                __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
+                // -z with the sign flipped in place (exact)
+                __half2 nz2 = __half2half2(__ushort_as_half((unsigned short)((sz >> 16) ^ 0x8000u)));
+                if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
+                const uint32_t a_row = tiles + s * stage_bytes + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
+                    const uint32_t dst = a_row + ((c ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};"
+                                 ::"r"(dst), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) bar_arrive(full0 + 8 * s);
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+
+        // epilogue: accumulator row `row` holds out[m0 .. m0+tok, n]
+        if (!failed && !bar_wait(accum, 0)) failed = true;
+        if (!failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float scale = 1.f;
+            if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
+            T* out = static_cast<T*>(p.out);
+            for (int c0 = 0; c0 < p.tok; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int m = m0 + c0 + i;
+                        if (c0 + i < p.tok && m < p.M)
+                            out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
+                    }
+                }
+            }
+        }
+    }
+
+    if (failed && lane == 0) atomicOr(&g_gemm_status, 2u);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                     : "memory");
+    }
+}
+
+struct GemmPlan {
+    int tok, tiles_m, stages, tmem_cols;
+    size_t smem;
+};
+
+bool plan_gemm(const MatmulArgs& a, GemmPlan* out)
+{
+    if (a.M < 1 || a.N < 1 || a.K < BK || a.K % BK) return false;
+    if (a.K > (1 << 28) || a.N > (1 << 30) || a.M > (1 << 24)) return false;
+    if (reinterpret_cast<uintptr_t>(a.wq) % 16 || reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8) return false;
+    if (a.group_size < a.K && a.group_size % BK) return false;
+    if (a.act_dtype == MNQ_FP16) {
+        if (a.scale_dtype != MNQ_FP16) return false;            // the tile math is fp16 x fp16
+    } else {
+        if (a.group_size < a.K || a.zeros != nullptr) return false;   // bf16: scale in the epilogue only
+    }
+    GemmPlan pl{};
+    pl.tiles_m = static_cast<int>((a.M + 255) / 256);
+    const int64_t per_tile = (a.M + pl.tiles_m - 1) / pl.tiles_m;
+    pl.tok = static_cast<int>(((per_tile + 15) / 16) * 16);
+    if (pl.tok > 256) pl.tok = 256;
+    pl.tiles_m = static_cast<int>((a.M + pl.tok - 1) / pl.tok);
+    if (pl.tiles_m > 65535) return false;
+    const size_t stage = static_cast<size_t>(A_BYTES) + static_cast<size_t>(pl.tok) * 128;
+    int stages = static_cast<int>((224 * 1024 - 1024) / stage);
+    if (stages > 8) stages = 8;
+    if (stages < 2) return false;
+    pl.stages = stages;
+    pl.smem = stage * stages + 1024;
+    int cols = 32;
+    while (cols < pl.tok) cols <<= 1;
+    pl.tmem_cols = cols;
+    *out = pl;
+    return true;
+}
+
+template <int QUANT, typename T>
+int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, dim3 grid, size_t smem, cudaStream_t stream)
+{
+    auto* kern = &gemm_tcgen05_kernel<QUANT, T>;
+    if (smem > 48 * 1024) {
+        const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024),
+                                  "cudaFuncSetAttribute(gemm_tcgen05)");
+        if (rc) return rc;
+    }
+    kern<<<grid, 192, smem, stream>>>(p, xmap);
+    return check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
+}
+
+}  // namespace
+
+int read_gemm_status(unsigned int* out, bool clear)
+{
+    unsigned int v = 0;
+    int rc = check_cuda(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof v), "cudaMemcpyFromSymbol(gemm status)");
+    if (rc) return rc;
+    if (clear && v) {
+        const unsigned int zero = 0;
+        rc = check_cuda(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof zero), "cudaMemcpyToSymbol(gemm status)");
+        if (rc) return rc;
+    }
+    *out = v;
+    return MNQ_SUCCESS;
+}
+
+bool gemm_supported(const MatmulArgs& a)
+{
+    GemmPlan pl;
+    return plan_gemm(a, &pl);
+}
+
+int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
+{
+    (void)tuning;
+    GemmPlan pl;
+    if (!plan_gemm(a, &pl))
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: the tensor-core kernel cannot take this problem "
+                                          "(needs K % 64 == 0, 16-byte aligned operands, group_size % 64 == 0 or >= K; "
+                                          "bf16 only with one scale per row and no zeros)");
+    GemmParams p{};
+    p.wq = static_cast<const uint8_t*>(a.wq); p.scales = a.scales; p.zeros = a.zeros; p.out = a.out;
+    p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+    p.ldc = a.ldc;
+    p.row_bytes = static_cast<int>(a.quant == MNQ_INT4 ? a.K / 2 : a.K);
+    p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
+    p.tok = pl.tok; p.stages = pl.stages; p.tmem_cols = pl.tmem_cols;
+    p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
+
+    // activations as a [M, K] tensor of 16-bit elements; box = 64 k x tok rows, 128-byte swizzle
+    CUtensorMap xmap;
+    const int rc = encode_tensor_map_2d(&xmap, a.x, a.act_dtype == MNQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                        2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
+                                        static_cast<uint64_t>(a.lda) * 2, BK, static_cast<uint32_t>(pl.tok),
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    dim3 grid(static_cast<unsigned>((a.N + BN - 1) / BN), static_cast<unsigned>(pl.tiles_m), 1);
+    if (a.quant == MNQ_INT4) {
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, grid, pl.smem, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, grid, pl.smem, a.stream);
+    }
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, grid, pl.smem, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, grid, pl.smem, a.stream);
+}
+
+}  // namespace mnq

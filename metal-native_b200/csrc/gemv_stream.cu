@@ -44,7 +44,7 @@
 
 namespace mnq {
 
-__device__ unsigned int g_device_status = 0;  // bit 0: a bounded wait gave up
+__device__ unsigned int g_device_status = 0;  // bit 0 / bit 1: a bounded wait gave up (GEMV / GEMM)
 
 namespace {
 
@@ -677,7 +677,10 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     pl.total_steps = static_cast<int>((row_bytes + kStepBytes - 1) / kStepBytes);
     const int64_t row_blocks = (a.N + 15) / 16;
 
-    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : 16;
+    // 16 warps per CTA when the row blocks alone fill every SM; 8 when K has to be split as
+    // well (measured: fewer, longer chunks beat more warps there)
+    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta
+                : (row_blocks >= static_cast<int64_t>(a.sm_count) * 16 ? 16 : 8);
     if (warps > 16) warps = 16;
     while (warps > 1 && row_blocks < warps) warps >>= 1;
     pl.warps = warps;
@@ -826,6 +829,8 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
 #undef MNQ_GS
 }
 
+int read_gemm_status(unsigned int* out, bool clear);
+
 int read_device_status(unsigned int* out, bool clear)
 {
     unsigned int v = 0;
@@ -836,7 +841,10 @@ int read_device_status(unsigned int* out, bool clear)
         rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &zero, sizeof zero), "cudaMemcpyToSymbol(status)");
         if (rc) return rc;
     }
-    *out = v;
+    unsigned int g = 0;
+    rc = read_gemm_status(&g, clear);
+    if (rc) return rc;
+    *out = v | g;
     return MNQ_SUCCESS;
 }
 

@@ -231,14 +231,15 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
     return out
 
 
-def select_path(M, N, K, group_size, quant_type, dtype=torch.float16, lda=None, alignment=256) -> str:
+def select_path(M, N, K, group_size, quant_type, dtype=torch.float16, lda=None, alignment=256,
+                zeros=True) -> str:
     """Kernel family the library picks for a problem: 'gemv', 'gemm' or 'generic'.
     Host logic only (works without a GPU); ``alignment`` is the assumed alignment of the
-    buffers' base addresses."""
+    buffers' base addresses, ``zeros`` whether a zeros tensor is passed."""
     q = _quant_code(quant_type)
     fake = ctypes.c_void_p(alignment * 4096)
     rc = _lib.mnq_select_path(M, N, K, lda if lda is not None else K, int(group_size), q, _DT[dtype],
-                              fake, fake, fake, fake)
+                              fake, fake, fake, fake if zeros else None)
     if rc < 0:
         raise MetalNativeError(-rc, _lib.mnq_last_error().decode())
     return _PATH_NAMES[rc]

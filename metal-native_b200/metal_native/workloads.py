@@ -70,7 +70,7 @@ class Layer:
 
 def make_layer(name: str, M: int, K: int, N: int, *, quant_type: str = "int4", group_size: int = 128,
                act_dtype: torch.dtype = torch.float16, scale_dtype: torch.dtype = torch.float16,
-               asymmetric: bool = True, scale_range=(0.005, 0.02), seed: int = 0,
+               asymmetric: bool = True, scale_range=None, seed: int = 0,
                gen: torch.Generator | None = None) -> Layer:
     """Builds one layer.  Asymmetric int4 layers draw an integer zero-point zp in 0..15 per
     (row, group) and encode it as the post-scale offset the operator's formula uses,
@@ -87,6 +87,8 @@ def make_layer(name: str, M: int, K: int, N: int, *, quant_type: str = "int4", g
         wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
     else:
         raise ValueError(quant_type)
+    if scale_range is None:   # keeps |w| <= ~0.16 for both formats
+        scale_range = (0.005, 0.02) if quant_type == "int4" else (0.0003, 0.00125)
     lo, hi = scale_range
     scales32 = torch.rand((N, G), generator=g, dtype=torch.float32) * (hi - lo) + lo
     scales = scales32.to(scale_dtype)

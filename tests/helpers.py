@@ -49,7 +49,8 @@ def errors(got: np.ndarray, ref: np.ndarray):
 
 
 def assert_close_to_oracle(out: torch.Tensor, ref: np.ndarray, what: str = ""):
-    """fp16 outputs: rel-L2 <= 1e-3 and max-abs <= 2e-2 against the oracle's fp32 result.
+    """fp16 outputs: rel-L2 <= 1e-3 and max-abs <= 2e-2 against the oracle's fp32 result (for
+    |y| >= 32, where adjacent fp16 values are further apart than that, one fp16 ulp).
 
     bf16 outputs cannot meet that gate whatever the kernel does (rounding the exact result
     to bf16 already costs ~1.6e-3 rel-L2), so they are held to the rounding floor instead:
@@ -62,7 +63,12 @@ def assert_close_to_oracle(out: torch.Tensor, ref: np.ndarray, what: str = ""):
     rel, mx = errors(got, ref)
     if out.dtype == torch.float16:
         assert rel <= REL_L2_TOL, f"{what}: rel-L2 {rel:.3e} > {REL_L2_TOL}"
-        assert mx <= MAX_ABS_TOL, f"{what}: max-abs {mx:.3e} > {MAX_ABS_TOL}"
+        # max-abs <= 2e-2 wherever fp16 can deliver it.  From |y| >= 32 on the fp16 grid itself
+        # is 3.1e-2 wide (6.3e-2 from 64), so there the bound is one fp16 ulp of the value.
+        ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-30))) - 10)
+        bound = np.maximum(MAX_ABS_TOL, ulp)
+        worst = float(np.max(np.abs(got - ref) / bound)) if ref.size else 0.0
+        assert worst <= 1.0, f"{what}: max-abs {mx:.3e}: {worst:.2f}x the bound max(2e-2, 1 fp16 ulp)"
         return rel, mx
     assert out.dtype == torch.bfloat16
     ideal = torch.from_numpy(ref).to(torch.bfloat16)

@@ -1,0 +1,108 @@
+"""Parity of the tensor-core (tcgen05 / TMEM) prefill kernel with the CPU oracle, through
+the Python shim over the C ABI.  Needs a B200; run with -m gpu."""
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mn():
+    import metal_native
+    assert torch.cuda.is_available()
+    return metal_native
+
+
+def _gemm_tuning(mn):
+    t = mn._C.Tuning()
+    t.path = mn._C.PATH_GEMM
+    return t
+
+
+CASES = [
+    # quant, M, N, K, g, asym, act dtype, scale dtype
+    ("int4", 64, 128, 64, 64, True, torch.float16, torch.float16),        # one k-block, one tile
+    ("int4", 64, 128, 256, 128, True, torch.float16, torch.float16),      # reference LargeMatrix class
+    ("int4", 128, 256, 512, 128, True, torch.float16, torch.float16),
+    ("int4", 100, 200, 256, 64, True, torch.float16, torch.float16),      # ragged M (tok 112) and N
+    ("int4", 33, 130, 128, 128, False, torch.float16, torch.float16),     # smallest M on this path
+    ("int4", 300, 128, 1024, 128, True, torch.float16, torch.float16),    # two token tiles of 160
+    ("int4", 512, 384, 640, 128, True, torch.float16, torch.float16),     # more k-blocks than stages
+    ("int4", 64, 128, 192, 1 << 20, True, torch.float16, torch.float16),  # one group per row
+    ("int8", 64, 128, 256, 128, True, torch.float16, torch.float16),
+    ("int8", 96, 160, 512, 64, False, torch.float16, torch.float16),
+    ("int8", 64, 256, 512, 512, False, torch.bfloat16, torch.float16),    # config 4 style: scale in epilogue
+    ("int4", 80, 128, 256, 256, False, torch.bfloat16, torch.bfloat16),
+]
+
+
+@pytest.mark.parametrize("quant,M,N,K,g,asym,adt,sdt", CASES)
+def test_gemm_shapes(mn, quant, M, N, K, g, asym, adt, sdt):
+    from metal_native import workloads
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt, scale_dtype=sdt,
+                             asymmetric=asym, seed=M + N + K)
+    assert mn._C.select_path(M, N, K, g, quant, adt) in ("gemm", "generic")
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    buf = torch.full((M + 2, N + 8), 777.0, dtype=adt, device="cuda")
+    out = buf[1:M + 1, 3:N + 3]
+    mn._C.dequant_matmul(*d.args(), out=out, tuning=_gemm_tuning(mn))
+    mn._C.synchronize()
+    assert mn._C.device_status() == 0
+    H.assert_close_to_oracle(out, ref, f"gemm {quant} {M}x{N}x{K} g{g}")
+    chk = buf.clone()
+    chk[1:M + 1, 3:N + 3] = 777.0
+    assert bool((chk == 777.0).all()), "kernel wrote outside its [M, N] output block"
+
+
+def test_gemm_is_selected_for_prefill_shapes(mn):
+    sp = mn._C.select_path
+    assert sp(512, 18944, 3584, 128, "int4") == "gemm"
+    assert sp(512, 3584, 18944, 128, "int4") == "gemm"
+    assert sp(64, 57344, 8192, 8192, "int8", torch.bfloat16, zeros=False) == "gemm"
+    assert sp(64, 8192, 28672, 28672, "int8", torch.bfloat16, zeros=False) == "gemm"
+    assert sp(40, 70, 96, 32, "int4") == "generic"        # K % 64 != 0
+
+
+def test_gemm_agrees_with_other_paths(mn):
+    from metal_native import workloads
+    L = workloads.make_layer("t", 64, 1024, 256, seed=5).to("cuda")
+    a = mn._C.dequant_matmul(*L.args(), tuning=_gemm_tuning(mn))
+    t = mn._C.Tuning(); t.path = mn._C.PATH_GENERIC
+    b = mn._C.dequant_matmul(*L.args(), tuning=t)
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2
+
+
+def test_config3_prefill_full_size(mn):
+    from metal_native import workloads
+    rng = np.random.default_rng(3)
+    for L in workloads.config3():
+        d = L.to("cuda")
+        out = mn._C.dequant_matmul(*d.args())
+        mn._C.synchronize()
+        assert mn._C.device_status() == 0
+        cols = np.sort(rng.choice(L.N, 96, replace=False))
+        ref = H.oracle_matmul(L, cols=cols)
+        H.assert_close_to_oracle(out[:, torch.as_tensor(cols, device="cuda")], ref, L.name)
+        # whole output against fp32 math on the (bit-exactly verified) dequantised weights
+        W = mn.dequantize(d.wq, d.scales, d.zeros, d.group_size, "int4", torch.float32)
+        full = d.x.float() @ W.t()
+        rel = float((out.float() - full).norm() / full.norm())
+        assert rel < 1e-3, rel
+        del W, full
+
+
+def test_config4_m64_int8_bf16(mn):
+    from metal_native import workloads
+    rng = np.random.default_rng(5)
+    for L in workloads.config4(64, scale_down=8):
+        d = L.to("cuda")
+        out = mn._C.dequant_matmul(*d.args())
+        mn._C.synchronize()
+        assert mn._C.device_status() == 0
+        cols = np.sort(rng.choice(L.N, 64, replace=False))
+        ref = H.oracle_matmul(L, cols=cols)
+        H.assert_close_to_oracle(out[:, torch.as_tensor(cols, device="cuda")], ref, L.name)
