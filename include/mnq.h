@@ -157,6 +157,32 @@ MNQ_API int mnq_dequantize_flat(const void* input, const void* scales_fp16, void
  * include/metal_native/core/error.h:28).  No counterpart call in the reference. */
 MNQ_API int mnq_device_status(uint32_t* status, int32_t clear);
 
+/* Fused dequantise + matmul for callers that cannot allocate device memory.
+ * No counterpart in the reference (its operator allocates its own output).
+ *
+ * Same arguments and results as mnq_dequant_matmul, minus the workspace: the split-K
+ * scratch the decode kernels need lives in a fixed array inside the library,
+ * MNQ_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library, kept
+ * until the process exits.  It is meant for code that is handed only its inputs and
+ * outputs and must not call cudaMalloc or any allocator: plugins of a host runtime that
+ * owns all device memory, callbacks running inside an allocator, serving loops with a
+ * frozen memory budget.  The call itself allocates nothing (no cudaMalloc, cudaFree or
+ * allocating library routine).
+ *
+ *  - Limit: a problem whose scratch demand, mnq_workspace_bytes(M, N, K, ...), exceeds
+ *    MNQ_STATIC_SCRATCH_BYTES is refused with MNQ_INVALID_ARGUMENT; nothing is launched.
+ *  - The first call on each device looks up the array's device address (a synchronous
+ *    runtime query): make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  Each call clears the arrival counters
+ *    it needs on `stream` before launching, but two calls that overlap on the GPU
+ *    (different streams, or different threads) race on it and give wrong results:
+ *    serialise them, or use mnq_dequant_matmul with separate workspaces. */
+#define MNQ_STATIC_SCRATCH_BYTES (4u << 20)
+MNQ_API int mnq_dequant_matmul_static(const void* activations, const void* weights_packed, const void* scales,
+                              const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                              int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                              int32_t scale_dtype, void* stream);
+
 /* Library version, "major.minor.patch". */
 MNQ_API const char* mnq_version(void);
 
