@@ -46,6 +46,18 @@ for _p in (str(ROOT / "metal-native_b200"), str(ROOT)):
 FALLBACK_HBM_GBS = 6650.0   # used only if MEASURED_PEAKS.json is absent ("of fallback")
 METRIC = "int4 dequant-GEMV weight GB/s"
 UNIT = "GB/s"
+PREFILL_METRIC = "prefill TFLOP/s"
+FALLBACK_TFLOPS = 1590.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+# ncu captures summarised under profiles/ (one capture per kernel and workload)
+TRAFFIC = {
+    "qwen7b-decode:qwen2.5-7b.gate_up": 72_213_504 + 945_920,   # profiles/gemv_stream_qwen7b_gate_up.md
+}
+
+
+def is_prefill(name):
+    return name == "qwen7b-prefill"
 
 
 def parse_args():
@@ -71,6 +83,16 @@ def hbm_peak():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback", {}
+
+
+def tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_TFLOPS, "fallback"
 
 
 def workload_name(args, world):
@@ -150,22 +172,27 @@ def run_reference(args):
     name = workload_name(args, world)
     layers, desc = build_layers(name, 1, 0)
     sample, notes = cpu_sample_layers(layers)
+    prefill = is_prefill(name)
     wbytes = sum(L.weight_bytes for L in sample)
+    work = sum(L.flops for L in sample) / 1e3 if prefill else wbytes     # TFLOP = flops / 1e12
     times, threads = cpu_path_time(sample, 1e9, max_steps=args.warmup)          # warm-up steps
     times, threads = cpu_path_time(sample, 1e9, max_steps=max(1, args.steps))   # exactly K steps
     total = sum(times)
-    value = wbytes * len(times) / total / 1e9
+    value = work * len(times) / total / 1e9
     sample_desc = "whole workload per step" if not notes else "; ".join(notes)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": PREFILL_METRIC if prefill else METRIC, "value": value,
+        "unit": "TFLOP/s" if prefill else UNIT, "n_gpus": args.gpus,
         "steps": len(times), "warmup": args.warmup, "ms_per_step": total / len(times) * 1e3,
         "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "description": desc, "arm": "CPU oracle port of the reference's "
                    "dequantise-then-matmul helpers (tests/cpp/test_dequant_matmul.mm:119-213), "
                    "N split over host threads"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_desc},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s" if prefill else UNIT, "cores": threads, "kind": "port",
+                         "sample": sample_desc},
+        "e2e": {"value": value, "unit": "TFLOP/s" if prefill else UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -302,10 +329,13 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     total_wbytes = wbytes_rank * world
-    value = total_wbytes * args.steps / (ms * 1e-3) / 1e9
+    prefill = is_prefill(name)
+    total_flops = sum(L.flops for L in layers_cpu) * world
+    work_per_step = total_flops / 1e3 if prefill else total_wbytes      # TFLOP/s = flops / s / 1e12
+    value = work_per_step * args.steps / (ms * 1e-3) / 1e9
 
     # ---- roofline: the dominant kernel alone -------------------------------------------
-    dom = max(range(len(layers_cpu)), key=lambda j: layers_cpu[j].weight_bytes)
+    dom = max(range(len(layers_cpu)), key=lambda j: (layers_cpu[j].flops if prefill else layers_cpu[j].weight_bytes))
     Ld = layers_cpu[dom]
     reps = max(50, min(args.steps, 400))
     g2 = torch.cuda.CUDAGraph()
@@ -324,19 +354,22 @@ def run_ours(args):
         dom_us = k0.elapsed_time(k1) * 1e3 / reps
     peak, peak_kind, peaks = hbm_peak()
     algo_bytes = Ld.total_bytes
-    achieved = algo_bytes / (dom_us * 1e-6) / 1e9
-    traffic = None
-    tr_file = ROOT / "profiles" / "traffic.json"
-    if tr_file.exists():
-        try:
-            traffic = json.loads(tr_file.read_text()).get(f"{name}:{Ld.name}")
-        except Exception:
-            traffic = None
-    roofline = {"bound": "hbm", "kernel": f"gemv ({Ld.name})", "achieved": achieved, "peak": peak,
-                "peak_source": f"{peak_kind} HBM copy bandwidth", "unit": "GB/s", "frac": achieved / peak,
-                "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": traffic,
-                "algorithmic_bytes_per_launch": algo_bytes, "weight_bytes_per_launch": Ld.weight_bytes,
-                "weight_GBps": Ld.weight_bytes / (dom_us * 1e-6) / 1e9, "us_per_launch": dom_us}
+    traffic = TRAFFIC.get(f"{name}:{Ld.name}")
+    kernel = _C.select_path(Ld.M, Ld.N, Ld.K, Ld.group_size, Ld.quant_type, Ld.x.dtype, zeros=Ld.zeros is not None)
+    if prefill:
+        tpeak, tkind = tensor_peak()
+        achieved = Ld.flops / (dom_us * 1e-6) / 1e12
+        roofline = {"bound": "tensor", "kernel": f"{kernel} ({Ld.name})", "achieved": achieved, "peak": tpeak,
+                    "peak_source": f"{tkind} cuBLAS bf16 burst", "unit": "TFLOP/s", "frac": achieved / tpeak,
+                    "frac_of_nominal_2250TF": achieved / 2250.0, "traffic": traffic,
+                    "flops_per_launch": Ld.flops, "us_per_launch": dom_us}
+    else:
+        achieved = algo_bytes / (dom_us * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "kernel": f"{kernel} ({Ld.name})", "achieved": achieved, "peak": peak,
+                    "peak_source": f"{peak_kind} HBM copy bandwidth", "unit": "GB/s", "frac": achieved / peak,
+                    "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": traffic,
+                    "algorithmic_bytes_per_launch": algo_bytes, "weight_bytes_per_launch": Ld.weight_bytes,
+                    "weight_GBps": Ld.weight_bytes / (dom_us * 1e-6) / 1e9, "us_per_launch": dom_us}
 
     # ---- end to end through the public call, host buffers ------------------------------
     xs_host = [L.x.pin_memory() for L in layers_cpu]
@@ -369,7 +402,7 @@ def run_ours(args):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e = {"value": total_wbytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+    e2e = {"value": work_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "TFLOP/s" if prefill else UNIT,
            "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in xs_host),
            "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs_host),
            "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
@@ -389,14 +422,16 @@ def run_ours(args):
         sample, notes = cpu_sample_layers(layers_cpu)
         times, threads = cpu_path_time(sample, args.cpu_seconds)
         best = sorted(times)[len(times) // 2]
-        cpu = {"value": sum(L.weight_bytes for L in sample) / best / 1e9, "unit": UNIT, "cores": threads,
+        cpu_work = sum(L.flops for L in sample) / 1e3 if prefill else sum(L.weight_bytes for L in sample)
+        cpu = {"value": cpu_work / best / 1e9, "unit": "TFLOP/s" if prefill else UNIT, "cores": threads,
                "kind": "port", "ms_per_step": best * 1e3,
                "sample": (f"{len(times)} whole steps" if not notes else f"{len(times)} steps of: " + "; ".join(notes))
                + f", median, {threads} threads splitting N"}
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": PREFILL_METRIC if prefill else METRIC, "value": value,
+            "unit": "TFLOP/s" if prefill else UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
             "dtype": "f16" if layers_cpu[0].x.dtype == torch.float16 else "bf16", "data": "synthetic",
@@ -405,7 +440,8 @@ def run_ours(args):
                                     f"rotate, L2 = {l2 / 1e6:.0f} MB",
                        "launch": f"{args.steps} steps replayed from one CUDA graph",
                        "weight_bytes_per_step": total_wbytes,
-                       "frac_of_measured_hbm": value / (peak * world), "frac_of_nominal_8TBs": value / (8000.0 * world)},
+                       "frac_of_measured_hbm": None if prefill else value / (peak * world),
+                       "frac_of_nominal_8TBs": None if prefill else value / (8000.0 * world)},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": kernels_per_step * args.steps,
         }
