@@ -191,6 +191,7 @@ int mnq_device_status(uint32_t* status, int32_t clear)
 
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
+    if (M > 32) return gemm_workspace_bytes(M, N, K);
     return gemv_workspace_bytes(M, N, K, group_size, quant_type);
 }
 
@@ -206,7 +207,7 @@ int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_
               quant_type, act_dtype, MNQ_FP16, nullptr, 0, nullptr);
     // the answer must not depend on how much workspace a later call brings
     a.workspace = reinterpret_cast<void*>(uintptr_t(256));
-    a.workspace_bytes = gemv_workspace_bytes(M, N, K, group_size, quant_type);
+    a.workspace_bytes = mnq_workspace_bytes(M, N, K, group_size, quant_type);
     return choose_path(a);
 }
 

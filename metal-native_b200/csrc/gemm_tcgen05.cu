@@ -8,18 +8,22 @@
 // the accumulator in tensor memory is out^T: TMEM lane = n, TMEM column = token.  One CTA
 // therefore dequantises a weight tile once for up to 256 tokens.
 //
-// Roles (192 threads):
+// Roles (320 threads):
 //   warp 0      one lane issues the TMA loads of activation tiles (128-byte swizzle);
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 per 64-k block) and
 //               tcgen05.commit, which frees the stage and finally publishes the accumulator;
-//   warps 2-5   stream the packed weights from global memory (prefetched several k-blocks
-//               ahead in registers), dequantise to fp16 with one rounding
+//   warps 2-9   (two threads per weight row) stream the packed weights from global memory
+//               (prefetched several k-blocks ahead in registers), dequantise to fp16 with one rounding
 //               (fma(q-8, s, -z) on exact integers) and write the 128-byte-swizzled K-major
 //               tile the MMA reads; afterwards they read the accumulator back with tcgen05.ld
 //               and store out[m, n].
 // bf16 activations take this path only with one scale per row and no zeros: the tile then
 // holds the exact integers and the scale is applied to the fp32 accumulator (rounding
 // dequantised weights to bf16 would cost 1.6e-3 relative error by itself).
+//
+// Few tiles (a long-K, narrow-N layer) leave SMs idle, so K can be split over grid.z: every
+// split writes its fp32 partial tile to the workspace and, per warp-sized part of a tile, the
+// last split to arrive adds the partials in a fixed order and writes the output.
 //
 // Every mbarrier wait is bounded; a wait that gives up sets bit 1 of the device status word
 // and the CTA falls through to its teardown (tensor memory is always released).
@@ -57,6 +61,10 @@ struct GemmParams {
     int stages;
     int tmem_cols;      // power of two >= max(32, tok)
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
+    int splits;         // K splits (grid.z)
+    int kb_per_split;   // 64-k blocks per split
+    float* partial;     // [splits][M][N] fp32 (splits > 1)
+    unsigned int* counters;   // [tiles][8] arrival counters (splits > 1)
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -196,11 +204,11 @@ template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
 };
 
 template <int QUANT, typename T>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap)
 {
-    constexpr int WPK = (QUANT == MNQ_INT4) ? 2 : 4;   // 16-byte loads per row per k-block
-    constexpr int KB_BYTES = WPK * 16;                  // packed bytes per row per k-block
+    constexpr int WPK = (QUANT == MNQ_INT4) ? 1 : 2;   // 16-byte loads per thread per k-block (half a row)
+    constexpr int KB_BYTES = WPK * 32;                  // packed bytes per row per k-block
     constexpr int U = 4;                                // k-blocks of weights in flight per thread
     constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
 
@@ -213,7 +221,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const int lane = tid & 31;
     const int n0 = blockIdx.x * BN;
     const int m0 = blockIdx.y * p.tok;
-    const int num_kb = p.K / BK;
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int num_kb = min(p.K / BK, kb_begin + p.kb_per_split) - kb_begin;   // k-blocks of this split
     const int S = p.stages;
     const int b_bytes = p.tok * 128;
     const int stage_bytes = A_BYTES + b_bytes;
@@ -221,7 +230,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const uint32_t full0 = s_u32(&bars[0]), empty0 = s_u32(&bars[8]), accum = s_u32(&bars[16]);
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 5); bar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 9); bar_init(empty0 + 8 * s, 1); }
         bar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -243,7 +252,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
                 bar_expect_tx(full0 + 8 * s, (uint32_t)b_bytes);
-                tma_load_tile(tiles + s * stage_bytes + A_BYTES, &xmap, kb * BK, m0, full0 + 8 * s);
+                tma_load_tile(tiles + s * stage_bytes + A_BYTES, &xmap, (kb_begin + kb) * BK, m0, full0 + 8 * s);
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
         }
@@ -269,6 +278,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     } else {
         // ---------------- dequantise weight tiles, then epilogue ----------------
         const int quad = warp & 3;             // tensor-memory lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;      // which 32 k of each 64-k block / which columns in the epilogue
         const int row = quad * 32 + lane;      // row of the tile = TMEM lane
         const int n = n0 + row;
         const uint8_t* wrow = p.wq + (size_t)min(n, p.N - 1) * p.row_bytes;
@@ -282,8 +292,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         auto prefetch = [&](int kb, int u) {
             if (kb < num_kb) {
 #pragma unroll
-                for (int i = 0; i < WPK; ++i) wreg[u][i] = ldg_stream_16(wrow + (size_t)kb * KB_BYTES + i * 16);
-                const int g = one_group ? 0 : (kb * BK) / p.group_size;
+                for (int i = 0; i < WPK; ++i)
+                    wreg[u][i] = ldg_stream_16(wrow + (size_t)(kb_begin + kb) * KB_BYTES + half * (KB_BYTES / 2) + i * 16);
+                const int g = one_group ? 0 : ((kb_begin + kb) * BK) / p.group_size;
                 uint32_t sz = __ldg(sc16 + sc_row + g);
                 if (zr16) sz |= (uint32_t)__ldg(zr16 + sc_row + g) << 16;
                 szreg[u] = sz;
@@ -312,8 +323,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
                 const uint32_t a_row = tiles + s * stage_bytes + row * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int c = half * 4 + c4;
+                    const uint4 o = TileChunk<QUANT, T>::run(&w[c4 * TileChunk<QUANT, T>::WORDS], s2, nz2);
                     const uint32_t dst = a_row + ((c ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};"
                                  ::"r"(dst), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
@@ -325,14 +337,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             }
         }
 
-        // epilogue: accumulator row `row` holds out[m0 .. m0+tok, n]
+        // epilogue: accumulator row `row` holds out[m0 .. m0+tok, n]; this warp takes the
+        // 32-column chunks with chunk index % 2 == half
         if (!failed && !bar_wait(accum, 0)) failed = true;
         if (!failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float scale = 1.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
             T* out = static_cast<T*>(p.out);
-            for (int c0 = 0; c0 < p.tok; c0 += 32) {
+            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.M * p.N : nullptr;
+            for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -340,9 +354,38 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int m = m0 + c0 + i;
-                        if (c0 + i < p.tok && m < p.M)
-                            out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
+                        if (c0 + i < p.tok && m < p.M) {
+                            if (mine) __stcg(&mine[(size_t)m * p.N + n], __uint_as_float(v[i]));
+                            else out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
+                        }
                     }
+                }
+            }
+            if (mine) {
+                // split-K: the last split to arrive for this warp's part of the tile reduces it
+                __threadfence();
+                __syncwarp();
+                const unsigned int slot = ((blockIdx.y * gridDim.x + blockIdx.x) << 3) + (unsigned)(warp - 2);
+                unsigned int arrival = 0;
+                if (lane == 0) arrival = atomicAdd(&p.counters[slot], 1u);
+                arrival = __shfl_sync(0xffffffffu, arrival, 0);
+                if (arrival == (unsigned int)(p.splits - 1)) {
+                    __threadfence();
+                    if (n < p.N) {
+                        for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
+                            for (int i = 0; i < 32; ++i) {
+                                const int m = m0 + c0 + i;
+                                if (c0 + i < p.tok && m < p.M) {
+                                    float acc = 0.f;
+                                    for (int z = 0; z < p.splits; ++z)
+                                        acc += __ldcg(&p.partial[((size_t)z * p.M + m) * p.N + n]);
+                                    out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(acc * scale);
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.counters[slot] = 0u;   // ready for the next call
                 }
             }
         }
@@ -359,11 +402,13 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 }
 
 struct GemmPlan {
-    int tok, tiles_m, stages, tmem_cols;
+    int tok, tiles_m, stages, tmem_cols, splits, kb_per_split;
     size_t smem;
 };
 
-bool plan_gemm(const MatmulArgs& a, GemmPlan* out)
+constexpr int kMaxSplits = 6;
+
+bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
 {
     if (a.M < 1 || a.N < 1 || a.K < BK || a.K % BK) return false;
     if (a.K > (1 << 28) || a.N > (1 << 30) || a.M > (1 << 24)) return false;
@@ -390,6 +435,29 @@ bool plan_gemm(const MatmulArgs& a, GemmPlan* out)
     int cols = 32;
     while (cols < pl.tok) cols <<= 1;
     pl.tmem_cols = cols;
+
+    // K splits: pick the count that minimises waves x (k-blocks per split + fixed cost)
+    const int num_kb = static_cast<int>(a.K / BK);
+    const int64_t tiles = static_cast<int64_t>((a.N + BN - 1) / BN) * pl.tiles_m;
+    int best = 1;
+    if (tuning && tuning->split_k > 0) {
+        best = tuning->split_k;
+    } else {
+        double best_cost = 1e30;
+        for (int sp = 1; sp <= kMaxSplits; ++sp) {
+            const int64_t waves = (tiles * sp + a.sm_count - 1) / a.sm_count;
+            const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) + (sp > 1 ? 3.0 * sp : 0.0);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
+        }
+    }
+    if (best > kMaxSplits) best = kMaxSplits;
+    if (best > num_kb) best = num_kb;
+    if (tiles * 8 > kMaxCounters) best = 1;
+    while (best > 1 &&
+           kCounterBytes + static_cast<size_t>(best) * a.M * a.N * 4 > (a.workspace ? a.workspace_bytes : 0))
+        --best;   // not enough workspace: fewer splits (one split needs none)
+    pl.kb_per_split = (num_kb + best - 1) / best;
+    pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
     *out = pl;
     return true;
 }
@@ -403,7 +471,7 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, dim3 grid, siz
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
         if (rc) return rc;
     }
-    kern<<<grid, 192, smem, stream>>>(p, xmap);
+    kern<<<grid, 320, smem, stream>>>(p, xmap);
     return check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
 }
 
@@ -426,14 +494,23 @@ int read_gemm_status(unsigned int* out, bool clear)
 bool gemm_supported(const MatmulArgs& a)
 {
     GemmPlan pl;
-    return plan_gemm(a, &pl);
+    return plan_gemm(a, nullptr, &pl);
+}
+
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    // Upper bound of what plan_gemm can ask for: splits only happen when the tiles do not
+    // fill the GPU (192 SMs is above every part this library targets).
+    if (M <= 32 || N < 1 || K < BK) return 0;
+    const int64_t tiles = ((N + BN - 1) / BN) * ((M + 255) / 256);
+    if (tiles >= 192) return 0;
+    return kCounterBytes + static_cast<size_t>(kMaxSplits) * M * N * 4;
 }
 
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
 {
-    (void)tuning;
     GemmPlan pl;
-    if (!plan_gemm(a, &pl))
+    if (!plan_gemm(a, tuning, &pl))
         return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: the tensor-core kernel cannot take this problem "
                                           "(needs K % 64 == 0, 16-byte aligned operands, group_size % 64 == 0 or >= K; "
                                           "bf16 only with one scale per row and no zeros)");
@@ -445,6 +522,12 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.stages = pl.stages; p.tmem_cols = pl.tmem_cols;
     p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
+    p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+    if (pl.splits > 1) {
+        unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+        p.counters = reinterpret_cast<unsigned int*>(ws);
+        p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
+    }
 
     // activations as a [M, K] tensor of 16-bit elements; box = 64 k x tok rows, 128-byte swizzle
     CUtensorMap xmap;
@@ -454,7 +537,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
                                         static_cast<uint64_t>(a.lda) * 2, BK, static_cast<uint32_t>(pl.tok),
                                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    dim3 grid(static_cast<unsigned>((a.N + BN - 1) / BN), static_cast<unsigned>(pl.tiles_m), 1);
+    dim3 grid(static_cast<unsigned>((a.N + BN - 1) / BN), static_cast<unsigned>(pl.tiles_m),
+              static_cast<unsigned>(pl.splits));
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, grid, pl.smem, a.stream);
         return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, grid, pl.smem, a.stream);

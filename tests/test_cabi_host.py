@@ -105,7 +105,8 @@ def test_kernel_selection_for_benchmark_shapes(C):
 def test_workspace_bytes(C):
     wb = C._lib.mnq_workspace_bytes
     assert wb(0, 64, 128, 128, 0) == 0
-    assert wb(64, 64, 128, 128, 0) == 0          # M > 32: no split-K workspace
+    assert wb(512, 18944, 3584, 128, 0) == 0     # enough tiles to fill the GPU: no split-K workspace
+    assert wb(512, 3584, 18944, 128, 0) == (64 << 10) + 6 * 512 * 3584 * 4   # few tiles: K may be split
     small = wb(1, 3584, 18944, 128, 0)
     assert 3584 * 4 * 2 < small < 4 << 20
     assert wb(32, 57344, 8192, 8192, 1) < 64 << 20

@@ -58,6 +58,21 @@ def test_gemm_shapes(mn, quant, M, N, K, g, asym, adt, sdt):
     assert bool((chk == 777.0).all()), "kernel wrote outside its [M, N] output block"
 
 
+@pytest.mark.parametrize("split", [1, 2, 3, 5])
+def test_gemm_split_k_is_deterministic_and_reuses_workspace(mn, split):
+    from metal_native import workloads
+    L = workloads.make_layer("t", 200, 1024, 256, seed=split)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    t = _gemm_tuning(mn)
+    t.split_k = split
+    outs = [mn._C.dequant_matmul(*d.args(), tuning=t) for _ in range(3)]
+    mn._C.synchronize()
+    assert mn._C.device_status() == 0
+    H.assert_close_to_oracle(outs[0], ref, f"gemm split {split}")
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 def test_gemm_is_selected_for_prefill_shapes(mn):
     sp = mn._C.select_path
     assert sp(512, 18944, 3584, 128, "int4") == "gemm"
