@@ -191,7 +191,7 @@ int mnq_device_status(uint32_t* status, int32_t clear)
 
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
-    if (M > 32) return gemm_workspace_bytes(M, N, K);
+    if (M > 32) return gemm_workspace_bytes(M, N, K, group_size);
     return gemv_workspace_bytes(M, N, K, group_size, quant_type);
 }
 

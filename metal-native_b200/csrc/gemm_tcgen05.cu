@@ -4,16 +4,22 @@
 // shared memory, multiply, fp32 accumulate, 16-bit store.
 //
 // Orientation.  The MMA's 128-row operand A is the WEIGHT tile (128 output columns n x 64 k,
-// K-major), its N-side operand B the ACTIVATION tile (TOK <= 256 tokens x 64 k, K-major), so
-// the accumulator in tensor memory is out^T: TMEM lane = n, TMEM column = token.  One CTA
-// therefore dequantises a weight tile once for up to 256 tokens.
+// K-major), its N-side operand B an ACTIVATION tile (<= 256 tokens x 64 k, K-major), so the
+// accumulator in tensor memory is out^T: TMEM lane = n, TMEM column = token.  A CTA keeps one
+// or two accumulators (up to 2 x 256 columns = all of tensor memory) and multiplies the same
+// dequantised weight tile against one or two activation tiles, so each weight is dequantised
+// once for up to 512 tokens.  Weight tiles and activation tiles travel in separate rings.
 //
-// Roles (320 threads):
+// Roles (352 threads):
 //   warp 0      one lane issues the TMA loads of activation tiles (128-byte swizzle);
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 per 64-k block) and
 //               tcgen05.commit, which frees the stage and finally publishes the accumulator;
-//   warps 2-9   (two threads per weight row) stream the packed weights from global memory
-//               (prefetched several k-blocks ahead in registers), dequantise to fp16 with one rounding
+//   warp 10     one lane issues the TMA loads of PACKED weight tiles (128 rows x 128 bytes,
+//               128-byte swizzle) into a raw ring, so DRAM sees 128-byte row segments;
+//   warps 2-9   (two threads per weight row) first copy the CTA's scales and zeros into a
+//               shared-memory table (no global load may be in flight later: the proxy fence
+//               they execute per tile would wait for it), then read the packed words from
+//               the raw ring, dequantise to fp16 with one rounding
 //               (fma(q-8, s, -z) on exact integers) and write the 128-byte-swizzled K-major
 //               tile the MMA reads; afterwards they read the accumulator back with tcgen05.ld
 //               and store out[m, n].
@@ -57,10 +63,15 @@ struct GemmParams {
     int group_size;     // >= K: one group
     int G;
     int scale_dtype;
-    int tok;            // tokens per CTA tile (multiple of 16, <= 256)
-    int stages;
+    int tok;            // tokens per CTA tile = nh * tokh (<= 512)
+    int tokh;           // tokens per accumulator / activation tile (multiple of 16, <= 256)
+    int nh;             // accumulators per CTA (1 or 2)
+    int stages;         // weight-tile (A) ring
+    int b_stages;       // activation-tile (B) ring
     int tmem_cols;      // power of two >= max(32, tok)
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
+    int raw_stages;     // stages of the packed-weight ring
+    int table_groups;   // quantisation groups per row held in the shared-memory scale table
     int splits;         // K splits (grid.z)
     int kb_per_split;   // 64-k blocks per split
     float* partial;     // [splits][M][N] fp32 (splits > 1)
@@ -204,17 +215,20 @@ template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
 };
 
 template <int QUANT, typename T>
-__global__ void __launch_bounds__(320, 1)
-gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap)
+__global__ void __launch_bounds__(352, 1)
+gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
+                    const __grid_constant__ CUtensorMap wmap)
 {
     constexpr int WPK = (QUANT == MNQ_INT4) ? 1 : 2;   // 16-byte loads per thread per k-block (half a row)
     constexpr int KB_BYTES = WPK * 32;                  // packed bytes per row per k-block
-    constexpr int U = 4;                                // k-blocks of weights in flight per thread
+    constexpr int KPR = 128 / KB_BYTES;                 // k-blocks covered by one raw stage (128 packed bytes per row)
+    constexpr int RAW_BYTES = BN * 128;
     constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];   // full[8], empty[8], accum
+    // a_full[8], a_empty[8], accum, raw_full[4], raw_empty[4], b_full[8], b_empty[8]
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1 + 2 * 4 + 2 * 8];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -223,15 +237,23 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const int m0 = blockIdx.y * p.tok;
     const int kb_begin = blockIdx.z * p.kb_per_split;
     const int num_kb = min(p.K / BK, kb_begin + p.kb_per_split) - kb_begin;   // k-blocks of this split
-    const int S = p.stages;
-    const int b_bytes = p.tok * 128;
-    const int stage_bytes = A_BYTES + b_bytes;
-    const uint32_t tiles = (s_u32(smem_raw) + 1023u) & ~1023u;   // 1024-byte aligned tile area
+    const int S = p.stages, SB = p.b_stages;
+    const int b_bytes = p.tokh * 128;
+    const uint32_t tiles = (s_u32(smem_raw) + 1023u) & ~1023u;   // 1024-byte aligned: weight-tile ring
+    const uint32_t btiles = tiles + S * A_BYTES;                  // activation-tile ring
+    const uint32_t raw0 = btiles + SB * b_bytes;                  // packed-weight ring
+    const int R = p.raw_stages;
+    const uint32_t tbl0 = raw0 + R * RAW_BYTES;                   // [group][row] scale | zero << 16
+    const int num_raw = (num_kb + KPR - 1) / KPR;
     const uint32_t full0 = s_u32(&bars[0]), empty0 = s_u32(&bars[8]), accum = s_u32(&bars[16]);
+    const uint32_t rfull0 = s_u32(&bars[17]), rempty0 = s_u32(&bars[21]);
+    const uint32_t bfull0 = s_u32(&bars[25]), bempty0 = s_u32(&bars[33]);
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 9); bar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 8); bar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < SB; ++s) { bar_init(bfull0 + 8 * s, 1); bar_init(bempty0 + 8 * s, 1); }
         bar_init(accum, 1);
+        for (int r = 0; r < R; ++r) { bar_init(rfull0 + 8 * r, 1); bar_init(rempty0 + 8 * r, 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -248,32 +270,51 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     if (warp == 0) {
         // ---------------- activation tiles by TMA ----------------
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
-                bar_expect_tx(full0 + 8 * s, (uint32_t)b_bytes);
-                tma_load_tile(tiles + s * stage_bytes + A_BYTES, &xmap, (kb_begin + kb) * BK, m0, full0 + 8 * s);
-                if (++s == S) { s = 0; ph ^= 1u; }
+            int sb = 0; uint32_t ph = 0;
+            for (int kb = 0; kb < num_kb && !failed; ++kb) {
+                for (int h = 0; h < p.nh; ++h) {
+                    if (!bar_wait(bempty0 + 8 * sb, ph ^ 1u)) { failed = true; break; }
+                    bar_expect_tx(bfull0 + 8 * sb, (uint32_t)b_bytes);
+                    tma_load_tile(btiles + sb * b_bytes, &xmap, (kb_begin + kb) * BK, m0 + h * p.tokh, bfull0 + 8 * sb);
+                    if (++sb == SB) { sb = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------- packed weight tiles by TMA ----------------
+        if (lane == 0) {
+            int r = 0; uint32_t ph = 0;
+            for (int j = 0; j < num_raw; ++j) {
+                if (!bar_wait(rempty0 + 8 * r, ph ^ 1u)) { failed = true; break; }
+                bar_expect_tx(rfull0 + 8 * r, (uint32_t)RAW_BYTES);
+                tma_load_tile(raw0 + r * RAW_BYTES, &wmap, ((kb_begin + j * KPR) * KB_BYTES) >> 2, n0, rfull0 + 8 * r);
+                if (++r == R) { r = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(p.tok, IS_BF16);
+            const uint32_t idesc = instr_desc(p.tokh, IS_BF16);
             int s = 0; uint32_t ph = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            int sb = 0; uint32_t bph = 0;
+            for (int kb = 0; kb < num_kb && !failed; ++kb) {
                 if (!bar_wait(full0 + 8 * s, ph)) { failed = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = tiles + s * stage_bytes;
-                const uint32_t b_addr = a_addr + A_BYTES;
+                const uint32_t a_addr = tiles + s * A_BYTES;
+                for (int h = 0; h < p.nh; ++h) {
+                    if (!bar_wait(bfull0 + 8 * sb, bph)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t b_addr = btiles + sb * b_bytes;
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j)
-                    umma(tmem_base, smem_desc_sw128(a_addr + j * 32), smem_desc_sw128(b_addr + j * 32), idesc,
-                         (kb > 0 || j > 0) ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+                    for (int j = 0; j < BK / 16; ++j)
+                        umma(tmem_base + (uint32_t)(h * p.tokh), smem_desc_sw128(a_addr + j * 32),
+                             smem_desc_sw128(b_addr + j * 32), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(bempty0 + 8 * sb);   // frees the activation tile once these MMAs have read it
+                    if (++sb == SB) { sb = 0; bph ^= 1u; }
+                }
+                umma_commit(empty0 + 8 * s);         // frees the weight tile
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
-            umma_commit(accum);                // accumulator complete
+            umma_commit(accum);                      // accumulators complete
         }
     } else {
         // ---------------- dequantise weight tiles, then epilogue ----------------
@@ -281,60 +322,66 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         const int half = (warp - 2) >> 2;      // which 32 k of each 64-k block / which columns in the epilogue
         const int row = quad * 32 + lane;      // row of the tile = TMEM lane
         const int n = n0 + row;
-        const uint8_t* wrow = p.wq + (size_t)min(n, p.N - 1) * p.row_bytes;
         const size_t sc_row = (size_t)min(n, p.N - 1) * p.G;
+        // generic pointer to shared-window address 0: the tile loads/stores below are ordinary
+        // C++ accesses, so the compiler may interleave the four chunks of a k-block
+        unsigned char* const gen = smem_raw - s_u32(smem_raw);
         const bool one_group = p.group_size >= p.K;
-        const unsigned short* sc16 = static_cast<const unsigned short*>(p.scales);
-        const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
-
-        uint4 wreg[U][WPK];
-        uint32_t szreg[U];
-        auto prefetch = [&](int kb, int u) {
-            if (kb < num_kb) {
-#pragma unroll
-                for (int i = 0; i < WPK; ++i)
-                    wreg[u][i] = ldg_stream_16(wrow + (size_t)(kb_begin + kb) * KB_BYTES + half * (KB_BYTES / 2) + i * 16);
-                const int g = one_group ? 0 : ((kb_begin + kb) * BK) / p.group_size;
-                uint32_t sz = __ldg(sc16 + sc_row + g);
-                if (zr16) sz |= (uint32_t)__ldg(zr16 + sc_row + g) << 16;
-                szreg[u] = sz;
+        const int g_first = one_group ? 0 : (kb_begin * BK) / p.group_size;
+        {   // scale | zero << 16 of every (row, group) this CTA touches, [group][row]
+            const unsigned short* sc16 = static_cast<const unsigned short*>(p.scales);
+            const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
+            const int g_last = one_group ? 0 : ((kb_begin + num_kb) * BK - 1) / p.group_size;
+            const int gc = g_last - g_first + 1;          // <= p.table_groups
+            for (int idx = tid - 64; idx < BN * gc; idx += 256) {
+                const int rr = idx / gc;
+                const int gi = idx - rr * gc;
+                const size_t src = (size_t)min(n0 + rr, p.N - 1) * p.G + g_first + gi;
+                uint32_t v = __ldg(sc16 + src);
+                if (zr16) v |= (uint32_t)__ldg(zr16 + src) << 16;
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(tbl0 + (gi * BN + rr) * 4), "r"(v) : "memory");
             }
-        };
-#pragma unroll
-        for (int u = 0; u < U; ++u) prefetch(u, u);
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight dequantise warps only
+        }
 
         int s = 0; uint32_t ph = 0;
-        for (int kb0 = 0; kb0 < num_kb && !failed; kb0 += U) {
+        int r = 0; uint32_t rph = 0;
+        for (int j = 0; j < num_raw && !failed; ++j) {
+            if (!bar_wait(rfull0 + 8 * r, rph)) { failed = true; break; }
+            const uint32_t raw_row = raw0 + r * RAW_BYTES + row * 128;
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int kb = kb0 + u;
+            for (int q = 0; q < KPR; ++q) {
+                const int kb = j * KPR + q;
                 if (kb >= num_kb || failed) break;
                 uint32_t w[WPK * 4];
 #pragma unroll
                 for (int i = 0; i < WPK; ++i) {
-                    w[4 * i] = wreg[u][i].x; w[4 * i + 1] = wreg[u][i].y;
-                    w[4 * i + 2] = wreg[u][i].z; w[4 * i + 3] = wreg[u][i].w;
+                    const int chunk = q * (8 / KPR) + half * WPK + i;   // 16-byte chunk of the 128-byte raw row
+                    const uint4 pk = *reinterpret_cast<const uint4*>(gen + (raw_row + ((chunk ^ (row & 7)) << 4)));
+                    w[4 * i] = pk.x; w[4 * i + 1] = pk.y; w[4 * i + 2] = pk.z; w[4 * i + 3] = pk.w;
                 }
-                const uint32_t sz = szreg[u];
-                prefetch(kb + U, u);
+                const int gi = one_group ? 0 : ((kb_begin + kb) * BK) / p.group_size - g_first;
+                const uint32_t sz = *reinterpret_cast<const uint32_t*>(gen + (tbl0 + (gi * BN + row) * 4));
                 __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
                 // -z with the sign flipped in place (exact)
                 __half2 nz2 = __half2half2(__ushort_as_half((unsigned short)((sz >> 16) ^ 0x8000u)));
                 if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
-                const uint32_t a_row = tiles + s * stage_bytes + row * 128;
+                const uint32_t a_row = tiles + s * A_BYTES + row * 128;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const int c = half * 4 + c4;
                     const uint4 o = TileChunk<QUANT, T>::run(&w[c4 * TileChunk<QUANT, T>::WORDS], s2, nz2);
                     const uint32_t dst = a_row + ((c ^ (row & 7)) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};"
-                                 ::"r"(dst), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
+                    *reinterpret_cast<uint4*>(gen + dst) = o;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) bar_arrive(full0 + 8 * s);
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
+            __syncwarp();
+            if (lane == 0) bar_arrive(rempty0 + 8 * r);   // this warp is done with the raw stage
+            if (++r == R) { r = 0; rph ^= 1u; }
         }
 
         // epilogue: accumulator row `row` holds out[m0 .. m0+tok, n]; this warp takes the
@@ -373,14 +420,20 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     __threadfence();
                     if (n < p.N) {
                         for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
+                            float acc[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+                            for (int z = 0; z < p.splits; ++z) {   // fixed order: deterministic
+                                const float* src = p.partial + ((size_t)z * p.M + m0 + c0) * p.N + n;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (c0 + i < p.tok && m0 + c0 + i < p.M) acc[i] += __ldcg(src + (size_t)i * p.N);
+                            }
+#pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const int m = m0 + c0 + i;
-                                if (c0 + i < p.tok && m < p.M) {
-                                    float acc = 0.f;
-                                    for (int z = 0; z < p.splits; ++z)
-                                        acc += __ldcg(&p.partial[((size_t)z * p.M + m) * p.N + n]);
-                                    out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(acc * scale);
-                                }
+                                if (c0 + i < p.tok && m < p.M)
+                                    out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(acc[i] * scale);
                             }
                         }
                     }
@@ -402,11 +455,26 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 }
 
 struct GemmPlan {
-    int tok, tiles_m, stages, tmem_cols, splits, kb_per_split;
+    int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, table_groups, tmem_cols, splits, kb_per_split;
     size_t smem;
 };
 
 constexpr int kMaxSplits = 6;
+constexpr int kMaxTableGroups = 64;   // 32 KB of scale table at most
+
+// K splits: the count that minimises waves x (k-blocks per split + fixed per-CTA cost) plus
+// the cost of writing and re-reading one partial tile per split.
+int choose_splits(int64_t tiles, int num_kb, int sm_count)
+{
+    int best = 1;
+    double best_cost = 1e30;
+    for (int sp = 1; sp <= kMaxSplits && sp <= num_kb; ++sp) {
+        const int64_t waves = (tiles * sp + sm_count - 1) / sm_count;
+        const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) + (sp > 1 ? 4.0 * sp : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
+    }
+    return best;
+}
 
 bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
 {
@@ -420,58 +488,79 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
         if (a.group_size < a.K || a.zeros != nullptr) return false;   // bf16: scale in the epilogue only
     }
     GemmPlan pl{};
-    pl.tiles_m = static_cast<int>((a.M + 255) / 256);
+    // token tile: up to 512 tokens per CTA as two accumulators of up to 256
+    pl.tiles_m = static_cast<int>((a.M + 511) / 512);
     const int64_t per_tile = (a.M + pl.tiles_m - 1) / pl.tiles_m;
-    pl.tok = static_cast<int>(((per_tile + 15) / 16) * 16);
-    if (pl.tok > 256) pl.tok = 256;
+    if (per_tile > 256) {
+        pl.nh = 2;
+        pl.tokh = static_cast<int>((((per_tile + 1) / 2 + 31) / 32) * 32);
+    } else {
+        pl.nh = 1;
+        pl.tokh = static_cast<int>(((per_tile + 15) / 16) * 16);
+    }
+    if (pl.tokh > 256) pl.tokh = 256;
+    pl.tok = pl.nh * pl.tokh;
     pl.tiles_m = static_cast<int>((a.M + pl.tok - 1) / pl.tok);
     if (pl.tiles_m > 65535) return false;
-    const size_t stage = static_cast<size_t>(A_BYTES) + static_cast<size_t>(pl.tok) * 128;
-    int stages = static_cast<int>((224 * 1024 - 1024) / stage);
-    if (stages > 8) stages = 8;
-    if (stages < 2) return false;
-    pl.stages = stages;
-    pl.smem = stage * stages + 1024;
     int cols = 32;
     while (cols < pl.tok) cols <<= 1;
     pl.tmem_cols = cols;
 
-    // K splits: pick the count that minimises waves x (k-blocks per split + fixed cost)
     const int num_kb = static_cast<int>(a.K / BK);
     const int64_t tiles = static_cast<int64_t>((a.N + BN - 1) / BN) * pl.tiles_m;
-    int best = 1;
-    if (tuning && tuning->split_k > 0) {
-        best = tuning->split_k;
-    } else {
-        double best_cost = 1e30;
-        for (int sp = 1; sp <= kMaxSplits; ++sp) {
-            const int64_t waves = (tiles * sp + a.sm_count - 1) / a.sm_count;
-            const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) + (sp > 1 ? 3.0 * sp : 0.0);
-            if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
-        }
-    }
+    int best = (tuning && tuning->split_k > 0) ? tuning->split_k : choose_splits(tiles, num_kb, a.sm_count);
     if (best > kMaxSplits) best = kMaxSplits;
     if (best > num_kb) best = num_kb;
     if (tiles * 8 > kMaxCounters) best = 1;
     while (best > 1 &&
            kCounterBytes + static_cast<size_t>(best) * a.M * a.N * 4 > (a.workspace ? a.workspace_bytes : 0))
         --best;   // not enough workspace: fewer splits (one split needs none)
+    // the scale table holds at most kMaxTableGroups groups per row: split K further if needed
+    const int64_t total_groups = a.group_size >= a.K ? 1 : (a.K + a.group_size - 1) / a.group_size;
+    const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
+    if (best < min_splits) best = min_splits;
+    if (best > kMaxSplits || best > num_kb) return false;
+    if (best > 1 && (tiles * 8 > kMaxCounters ||
+                     kCounterBytes + static_cast<size_t>(best) * a.M * a.N * 4 > (a.workspace ? a.workspace_bytes : 0)))
+        return false;
     pl.kb_per_split = (num_kb + best - 1) / best;
     pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
+    pl.table_groups = a.group_size >= a.K
+                          ? 1
+                          : static_cast<int>((static_cast<int64_t>(pl.kb_per_split) * BK + a.group_size - 1) / a.group_size + 1);
+
+    // shared memory: packed ring, scale table, then weight tiles (>= 2) and activation tiles (>= 2, ideally 4)
+    pl.raw_stages = 3;
+    const size_t b_tile = static_cast<size_t>(pl.tokh) * 128;
+    const size_t ring = static_cast<size_t>(pl.raw_stages) * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
+    const size_t budget = 226 * 1024 - 1024 - ring;
+    int ast = 3, bst = static_cast<int>((budget - 3 * A_BYTES) / b_tile);
+    if (bst < 4) {
+        ast = 2;
+        bst = static_cast<int>((budget - 2 * A_BYTES) / b_tile);
+    }
+    if (bst > 8) bst = 8;
+    if (bst < 2) return false;
+    ast = static_cast<int>((budget - b_tile * bst) / A_BYTES);
+    if (ast > 6) ast = 6;
+    pl.b_stages = bst;
+    pl.stages = ast;
+    pl.smem = 1024 + ring + b_tile * bst + static_cast<size_t>(ast) * A_BYTES;
     *out = pl;
     return true;
 }
 
 template <int QUANT, typename T>
-int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, dim3 grid, size_t smem, cudaStream_t stream)
+int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensorMap& wmap, dim3 grid, size_t smem,
+                    cudaStream_t stream)
 {
     auto* kern = &gemm_tcgen05_kernel<QUANT, T>;
     if (smem > 48 * 1024) {
-        const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024),
+        const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
         if (rc) return rc;
     }
-    kern<<<grid, 320, smem, stream>>>(p, xmap);
+    kern<<<grid, 352, smem, stream>>>(p, xmap, wmap);
     return check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
 }
 
@@ -497,14 +586,19 @@ bool gemm_supported(const MatmulArgs& a)
     return plan_gemm(a, nullptr, &pl);
 }
 
-size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K)
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
 {
-    // Upper bound of what plan_gemm can ask for: splits only happen when the tiles do not
-    // fill the GPU (192 SMs is above every part this library targets).
-    if (M <= 32 || N < 1 || K < BK) return 0;
-    const int64_t tiles = ((N + BN - 1) / BN) * ((M + 255) / 256);
-    if (tiles >= 192) return 0;
-    return kCounterBytes + static_cast<size_t>(kMaxSplits) * M * N * 4;
+    // What plan_gemm asks for on a 148-SM part (B200).  On a device where it would split
+    // further, the plan falls back to the number of splits the given workspace can hold.
+    if (M <= 32 || N < 1 || K < BK || K % BK) return 0;
+    const int64_t tiles = ((N + BN - 1) / BN) * ((M + 511) / 512);
+    if (tiles * 8 > kMaxCounters) return 0;
+    int splits = choose_splits(tiles, static_cast<int>(K / BK), 148);
+    const int64_t total_groups = group_size >= K ? 1 : (K + group_size - 1) / group_size;
+    const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
+    if (splits < min_splits) splits = min_splits;
+    if (splits <= 1 || splits > kMaxSplits) return 0;
+    return kCounterBytes + static_cast<size_t>(splits) * M * N * 4;
 }
 
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
@@ -520,7 +614,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.ldc = a.ldc;
     p.row_bytes = static_cast<int>(a.quant == MNQ_INT4 ? a.K / 2 : a.K);
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
-    p.tok = pl.tok; p.stages = pl.stages; p.tmem_cols = pl.tmem_cols;
+    p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
+    p.raw_stages = pl.raw_stages; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
     p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     if (pl.splits > 1) {
@@ -534,17 +629,24 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     const int rc = encode_tensor_map_2d(&xmap, a.x, a.act_dtype == MNQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                         2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
-                                        static_cast<uint64_t>(a.lda) * 2, BK, static_cast<uint32_t>(pl.tok),
+                                        static_cast<uint64_t>(a.lda) * 2, BK, static_cast<uint32_t>(pl.tokh),
                                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    // packed weights as a [N, row_bytes / 4] tensor of 32-bit words; box = 128 bytes x 128 rows,
+    // 128-byte swizzle so that 32 threads reading 32 different rows do not collide on banks
+    CUtensorMap wmap;
+    const int rc2 = encode_tensor_map_2d(&wmap, a.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4,
+                                         static_cast<uint64_t>(p.row_bytes) / 4, static_cast<uint64_t>(a.N),
+                                         static_cast<uint64_t>(p.row_bytes), 32, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc2) return rc2;
     dim3 grid(static_cast<unsigned>((a.N + BN - 1) / BN), static_cast<unsigned>(pl.tiles_m),
               static_cast<unsigned>(pl.splits));
     if (a.quant == MNQ_INT4) {
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, grid, pl.smem, a.stream);
-        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, grid, pl.smem, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, wmap, grid, pl.smem, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, a.stream);
     }
-    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, grid, pl.smem, a.stream);
-    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, grid, pl.smem, a.stream);
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, wmap, grid, pl.smem, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, a.stream);
 }
 
 }  // namespace mnq
