@@ -392,24 +392,35 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             float scale = 1.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
             T* out = static_cast<T*>(p.out);
-            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.M * p.N : nullptr;
+            // split-K partial tiles live in the workspace as [split][n][padded token]: a thread's 32
+            // tokens of one chunk are 128 contiguous bytes, written and re-read as 16-byte vectors
+            const int tokp = (p.tok + 31) & ~31;          // chunks are 32 tokens: pad each tile to that
+            const size_t Mp = (size_t)gridDim.y * tokp;
+            const size_t mp0 = (size_t)blockIdx.y * tokp;
+            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.N * Mp : nullptr;
             for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (n < p.N) {
+                    if (mine) {
+                        float4* dst = reinterpret_cast<float4*>(mine + (size_t)n * Mp + mp0 + c0);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int m = m0 + c0 + i;
-                        if (c0 + i < p.tok && m < p.M) {
-                            if (mine) __stcg(&mine[(size_t)m * p.N + n], __uint_as_float(v[i]));
-                            else out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
+                        for (int i = 0; i < 8; ++i)
+                            __stcg(dst + i, make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                        __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int m = m0 + c0 + i;
+                            if (c0 + i < p.tok && m < p.M)
+                                out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
                         }
                     }
                 }
             }
             if (mine) {
-                // split-K: the last split to arrive for this warp's part of the tile reduces it
+                // the last split to arrive for this warp's part of the tile reduces it
                 __threadfence();
                 __syncwarp();
                 const unsigned int slot = ((blockIdx.y * gridDim.x + blockIdx.x) << 3) + (unsigned)(warp - 2);
@@ -420,20 +431,27 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     __threadfence();
                     if (n < p.N) {
                         for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
-                            float acc[32];
+                            float4 acc[8];
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+                            for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                             for (int z = 0; z < p.splits; ++z) {   // fixed order: deterministic
-                                const float* src = p.partial + ((size_t)z * p.M + m0 + c0) * p.N + n;
+                                const float4* src =
+                                    reinterpret_cast<const float4*>(p.partial + ((size_t)z * p.N + n) * Mp + mp0 + c0);
 #pragma unroll
-                                for (int i = 0; i < 32; ++i)
-                                    if (c0 + i < p.tok && m0 + c0 + i < p.M) acc[i] += __ldcg(src + (size_t)i * p.N);
+                                for (int i = 0; i < 8; ++i) {
+                                    const float4 t4 = __ldcg(src + i);
+                                    acc[i].x += t4.x; acc[i].y += t4.y; acc[i].z += t4.z; acc[i].w += t4.w;
+                                }
                             }
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const int m = m0 + c0 + i;
-                                if (c0 + i < p.tok && m < p.M)
-                                    out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(acc[i] * scale);
+                            for (int i = 0; i < 8; ++i) {
+                                const float e[4] = {acc[i].x, acc[i].y, acc[i].z, acc[i].w};
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const int m = m0 + c0 + 4 * i + k;
+                                    if (c0 + 4 * i + k < p.tok && m < p.M)
+                                        out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(e[k] * scale);
+                                }
                             }
                         }
                     }
@@ -458,6 +476,9 @@ struct GemmPlan {
     int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, table_groups, tmem_cols, splits, kb_per_split;
     size_t smem;
 };
+
+// Upper bound of tiles_m * tok, the padded token count of the split-K partial buffer.
+inline size_t padded_tokens(int64_t M) { return static_cast<size_t>(M + 96 * ((M + 511) / 512) + 96); }
 
 constexpr int kMaxSplits = 6;
 constexpr int kMaxTableGroups = 64;   // 32 KB of scale table at most
@@ -513,7 +534,7 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (best > num_kb) best = num_kb;
     if (tiles * 8 > kMaxCounters) best = 1;
     while (best > 1 &&
-           kCounterBytes + static_cast<size_t>(best) * a.M * a.N * 4 > (a.workspace ? a.workspace_bytes : 0))
+           kCounterBytes + static_cast<size_t>(best) * padded_tokens(a.M) * a.N * 4 > (a.workspace ? a.workspace_bytes : 0))
         --best;   // not enough workspace: fewer splits (one split needs none)
     // the scale table holds at most kMaxTableGroups groups per row: split K further if needed
     const int64_t total_groups = a.group_size >= a.K ? 1 : (a.K + a.group_size - 1) / a.group_size;
@@ -521,7 +542,8 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (best < min_splits) best = min_splits;
     if (best > kMaxSplits || best > num_kb) return false;
     if (best > 1 && (tiles * 8 > kMaxCounters ||
-                     kCounterBytes + static_cast<size_t>(best) * a.M * a.N * 4 > (a.workspace ? a.workspace_bytes : 0)))
+                     kCounterBytes + static_cast<size_t>(best) * padded_tokens(a.M) * a.N * 4 >
+                         (a.workspace ? a.workspace_bytes : 0)))
         return false;
     pl.kb_per_split = (num_kb + best - 1) / best;
     pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
@@ -598,7 +620,7 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
     const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
     if (splits < min_splits) splits = min_splits;
     if (splits <= 1 || splits > kMaxSplits) return 0;
-    return kCounterBytes + static_cast<size_t>(splits) * M * N * 4;
+    return kCounterBytes + static_cast<size_t>(splits) * padded_tokens(M) * N * 4;
 }
 
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
