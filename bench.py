@@ -261,7 +261,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     import metal_native
     from metal_native import _C
@@ -409,11 +410,11 @@ def run_ours(args):
            "call": "metal_native._C.dequant_matmul per projection, eager; weights resident"}
 
     # ---- keep the load on for the clock sampler, then read it ----------------------------
-    if rank == 0:
-        t_end = time.perf_counter() + 1.0
-        while time.perf_counter() < t_end:
-            graph.replay()
-            torch.cuda.synchronize()
+    # every rank replays the same number of times (the graph may hold collectives): about one
+    # second of load, counted from the all-reduced step time, never from a local clock
+    for _ in range(max(1, min(2000, int(1000.0 / max(ms, 1e-3))))):
+        graph.replay()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
 
     # ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------------
@@ -447,8 +448,15 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Leave together, with nothing in flight.  The process group is not torn down
+        # explicitly: destroying it while captured graphs still reference its communicator
+        # was seen to block, and the processes are about to exit anyway.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
