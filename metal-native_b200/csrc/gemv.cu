@@ -531,21 +531,26 @@ bool gemv_supported(const MatmulArgs& a)
 
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant)
 {
-    (void)group_size;
-    if (M < 1 || M > 32 || N < 1 || K < 1) return 0;
-    // Upper bound of the chunk count plan_gemv picks by itself on any device with up to
-    // kSmBound SMs: the occupancy-driven count with the fewest row tiles (16 warps per
-    // CTA), or the count forced by the shared-memory bound on the staged activations.
+    if (M < 1 || M > 32 || N < 1 || K < 1 || group_size < 1) return 0;
+    // what the streaming kernel's plan asks for; at least room for a 2-way split so that a
+    // caller can force one
+    bool streaming = false;
+    size_t need = gemv_stream_workspace_bytes(M, N, K, group_size, quant, &streaming);
+    const size_t two_way = kCounterBytes + static_cast<size_t>(2) * M * N * 4;
+    if (need < two_way) need = two_way;
+    if (streaming) return need;
+    // shapes only the register-prefetch kernel takes: bound of the chunk count plan_gemv picks
+    // on its own (occupancy-driven with the fewest row tiles, or forced by the staged activations)
     constexpr int64_t kSmBound = 192;
     const int64_t row_blocks = (N + 15) / 16;
     const int64_t row_tiles_min = (row_blocks + 15) / 16;
     int64_t chunks = (2 * kSmBound + row_tiles_min / 2) / row_tiles_min;
-    const int64_t k_bytes = (quant == MNQ_INT4 ? K : K) * 2 * M;  // staged activations, all of K
-    const int64_t by_smem = (k_bytes + 128 * 1024 - 1) / (128 * 1024);
+    const int64_t by_smem = (K * 2 * M + 128 * 1024 - 1) / (128 * 1024);
     if (chunks < by_smem) chunks = by_smem;
-    if (chunks < 2) chunks = 2;  // lets a caller force a 2-way split for testing
+    if (chunks < 2) chunks = 2;
     if (chunks > kMaxSplitK) chunks = kMaxSplitK;
-    return kCounterBytes + static_cast<size_t>(chunks) * M * N * 4;
+    const size_t v1 = kCounterBytes + static_cast<size_t>(chunks) * M * N * 4;
+    return v1 > need ? v1 : need;
 }
 
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning)

@@ -40,6 +40,8 @@
 #include <cuda.h>
 #include <limits.h>
 
+#include <type_traits>
+
 #include "mnq_common.cuh"
 
 namespace mnq {
@@ -252,10 +254,17 @@ __device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&a
     }
 }
 
+// T is the activation / output type.  The MMAs always run in fp16: bf16 activations are
+// converted while they are staged, multiplied by a power of two chosen per CTA so that the
+// largest one lands below 2^15 (exact: a bf16 significand fits fp16's), and the accumulated
+// result is multiplied back.  That gives bf16 callers the cheap fp16 encodings of the packed
+// weights and keeps every product exact.
 template <int QUANT, typename T, int NT, int CH>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(NT >= 4 ? 256 : 512)
 gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap)
 {
+    using MT = __half;                                     // MMA element type
+    constexpr bool CONVERT_X = !std::is_same<T, __half>::value;
     constexpr int STEP = (QUANT == MNQ_INT4) ? 128 : 64;  // k per step
     constexpr int RS = CH;                                 // row stride inside a stage (dense TMA box)
     constexpr int STAGE_BYTES = 16 * RS;
@@ -290,10 +299,14 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     const int ring_bytes = p.stages * STAGE_BYTES;
     const int sc_floats = p.rbw * 16 * p.segs;               // per warp, per array
     const int xsum_off = p.M * p.xs_stride;
-    const int warp0_off = (xsum_off + p.segs * NT * 8 * 4 + 1023) & ~1023;
+    const int xsumi_off = (xsum_off + p.segs * NT * 8 * 4 + 7) & ~7;
+    const int warp0_off = (xsumi_off + p.segs * NT * 8 * 8 + 1023) & ~1023;
     const int per_warp = ring_bytes + sc_floats * 8 + 128;
     unsigned char* xs = smem;                                                  // [M][xs_stride]
     float* xsum = reinterpret_cast<float*>(smem + xsum_off);                   // [segs][NT*8]
+    // the same sums as exact 2^-24 fixed point: integer adds commute, so the shared-memory
+    // atomics below give the same bits whatever order the threads arrive in
+    unsigned long long* xsumi = reinterpret_cast<unsigned long long*>(smem + xsumi_off);
     unsigned char* my = smem + warp0_off + warp * per_warp;
     unsigned char* ring = my;                                                  // [stages][16][CH]
     float* sS = reinterpret_cast<float*>(my + ring_bytes);                     // [rbw][16][segs]  s / alpha
@@ -334,7 +347,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // activations) are issued first, all of them before any is used, so they cost one
     // round trip and are not queued behind the bulk weight traffic; then the first weight
     // pieces are requested; only then are the small loads consumed.
-    for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsum[i] = 0.f;
+    for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsumi[i] = 0ull;
+    __shared__ unsigned int x_max_bits;   // largest |activation| of this CTA's chunk, as bf16 bits
+    if (CONVERT_X && tid == 0) x_max_bits = 0u;
+    float x_down = 1.f, x_up = 1.f;       // 2^-x_shift and 2^x_shift
 
     constexpr int SCB = 8;                         // scale pairs in flight per lane (32 groups per row)
     constexpr int XB = (NT == 1) ? 2 : 4;          // activation loads in flight per thread
@@ -361,18 +377,24 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             }
         }
     };
-    auto store_x_block = [&](const uint32_t (&v)[4], int m, int b, int k) {
-        float sum = 0.f;
+    auto store_x_block = [&](uint32_t (&v)[4], int m, int b, int k) {
+        if (CONVERT_X) {   // bf16 -> fp16, times 2^-x_shift (exact unless the result is subnormal)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(v[e] << 16) * x_down;
+                const float hi = __uint_as_float(v[e] & 0xFFFF0000u) * x_down;
+                v[e] = h2_as_u32(__floats2half2_rn(lo, hi));
+            }
+        }
+        long long sum = 0;   // exact: every fp16 value is an integer multiple of 2^-24
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const unsigned short lo = static_cast<unsigned short>(v[e] & 0xFFFFu);
-            const unsigned short hi = static_cast<unsigned short>(v[e] >> 16);
-            sum += F16Traits<T>::to_float(*reinterpret_cast<const T*>(&lo)) +
-                   F16Traits<T>::to_float(*reinterpret_cast<const T*>(&hi));
+            const float2 f = __half22float2(u32_as_h2(v[e]));
+            sum += __float2ll_rn(f.x * 16777216.f) + __float2ll_rn(f.y * 16777216.f);
         }
         const int sg = (p.group_size == INT_MAX) ? 0
                      : (p.group_shift >= 0 ? (k >> p.group_shift) : k / p.group_size) - seg0;
-        atomicAdd(&xsum[sg * (NT * 8) + m], sum);
+        atomicAdd(&xsumi[sg * (NT * 8) + m], static_cast<unsigned long long>(sum));
         int pos;
         uint4 o;
         if (QUANT == MNQ_INT4) {
@@ -386,7 +408,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             o.y = prmt(v[1], v[3], 0x5410u);   // (x2, x6)
             o.z = prmt(v[0], v[2], 0x7632u);   // (x1, x5)
             o.w = prmt(v[1], v[3], 0x7632u);   // (x3, x7)
-            if (Enc<QUANT, T>::hi_x_scale) {
+            if (Enc<QUANT, MT>::hi_x_scale) {
                 const __half2 k16 = __half2half2(__ushort_as_half(0x2C00));   // 1/16
                 o.z = h2_as_u32(__hmul2(u32_as_h2(o.z), k16));
                 o.w = h2_as_u32(__hmul2(u32_as_h2(o.w), k16));
@@ -446,9 +468,9 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     s0 = sf.x; s1 = sf.y; z0 = zf.x; z1 = zf.y;
                 }
                 *reinterpret_cast<float2*>(dS + c) =
-                    make_float2(s0 * Enc<QUANT, T>::inv_alpha, s1 * Enc<QUANT, T>::inv_alpha);
+                    make_float2(s0 * Enc<QUANT, MT>::inv_alpha, s1 * Enc<QUANT, MT>::inv_alpha);
                 *reinterpret_cast<float2*>(dZ + c) =
-                    make_float2(fmaf(Enc<QUANT, T>::offset, s0, z0), fmaf(Enc<QUANT, T>::offset, s1, z1));
+                    make_float2(fmaf(Enc<QUANT, MT>::offset, s0, z0), fmaf(Enc<QUANT, MT>::offset, s1, z1));
             }
         }
     };
@@ -468,7 +490,33 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
     // the first weight pieces
     for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
-    __syncthreads();   // xsum is zeroed
+    __syncthreads();   // xsum (and x_max_bits) are zeroed
+
+    if (CONVERT_X) {
+        // largest |x| of the chunk -> power-of-two scale that puts it just below 2^15
+        unsigned int mx = 0;
+#pragma unroll
+        for (int u = 0; u < XB; ++u)
+            if (xm[u] >= 0) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx = max(mx, max(xv[u][e] & 0x7FFFu, (xv[u][e] >> 16) & 0x7FFFu));
+            }
+        for (int i = XB * blockDim.x + tid; i < x_count; i += blockDim.x) {   // blocks beyond the first batch
+            uint32_t t4[4];
+            int a, b, c;
+            load_x_block(i, t4, a, b, c);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mx = max(mx, max(t4[e] & 0x7FFFu, (t4[e] >> 16) & 0x7FFFu));
+        }
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if (lane == 0 && mx) atomicMax(&x_max_bits, mx);
+        __syncthreads();
+        const int E = static_cast<int>(x_max_bits >> 7);          // biased bf16 exponent of the maximum
+        int sh = (E == 0) ? 0 : (E - 127) - 14;
+        sh = max(-100, min(100, sh));
+        x_down = __int_as_float((127 - sh) << 23);
+        x_up = __int_as_float((127 + sh) << 23);
+    }
 
     // consume the small loads
     fold_scale_pairs(0, 0, sreg, zreg);
@@ -492,6 +540,9 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         for (int u = 0; u < XB; ++u)
             if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     }
+    __syncthreads();
+    for (int i = tid; i < p.segs * NT * 8; i += blockDim.x)
+        xsum[i] = static_cast<float>(static_cast<long long>(xsumi[i])) * (1.f / 16777216.f);
     __syncthreads();
 
     // ---- main loop ----------------------------------------------------------------------------
@@ -555,7 +606,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff + ps * STEP * 2;
                     float a4[NT][4];
-                    step_mma<QUANT, T, NT, true>(wa[ps], wb[ps], xb, a4);
+                    step_mma<QUANT, MT, NT, true>(wa[ps], wb[ps], xb, a4);
                     close_group<NT>(tot, a4, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8));
                 }
                 s += PSTEPS;
@@ -576,7 +627,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     const unsigned char* xb[NT];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff;
-                    step_mma<QUANT, T, NT, false>(wa, wb, xb, acc);
+                    step_mma<QUANT, MT, NT, false>(wa, wb, xb, acc);
                     if (--steps_left == 0 || s == nsteps - 1) {
                         close_group<NT>(tot, acc, *S0p, *S1p, *Z0p, *Z1p, Xp);
 #pragma unroll
@@ -608,7 +659,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 for (int i = 0; i < 4; ++i) {
                     const int m = nt * 8 + 2 * t + (i & 1);
                     const int n = (i & 2) ? n1 : n0;
-                    if (m < p.M && n < p.N) out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(tot[nt][i]);
+                    if (m < p.M && n < p.N)
+                        out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]);
                 }
             continue;
         }
@@ -619,7 +671,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             for (int i = 0; i < 4; ++i) {
                 const int m = nt * 8 + 2 * t + (i & 1);
                 const int n = (i & 2) ? n1 : n0;
-                if (m < p.M && n < p.N) __stcg(&mine[(size_t)m * p.N + n], tot[nt][i]);
+                if (m < p.M && n < p.N) __stcg(&mine[(size_t)m * p.N + n], CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]);
             }
         __threadfence();
         __syncwarp();
@@ -677,11 +729,11 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     pl.total_steps = static_cast<int>((row_bytes + kStepBytes - 1) / kStepBytes);
     const int64_t row_blocks = (a.N + 15) / 16;
 
-    // 16 warps per CTA when the row blocks alone fill every SM; 8 when K has to be split as
-    // well (measured: fewer, longer chunks beat more warps there)
-    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta
-                : (row_blocks >= static_cast<int64_t>(a.sm_count) * 16 ? 16 : 8);
+    // 16 warps per CTA (measured: always better than 8 at equal work); the widest activation
+    // tile is compiled for 256 threads
+    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : (pl.nt >= 4 ? 8 : 16);
     if (warps > 16) warps = 16;
+    if (pl.nt >= 4 && warps > 8) warps = 8;
     while (warps > 1 && row_blocks < warps) warps >>= 1;
     pl.warps = warps;
     pl.piece_bytes = (tuning && tuning->piece_bytes > 0) ? tuning->piece_bytes : 256;
@@ -693,23 +745,36 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : 1;
     const int64_t slots = static_cast<int64_t>(a.sm_count) * ctas_per_sm * warps;
 
+    // K chunks.  A warp processes `rbw` units (row block x chunk) one after the other, so the
+    // kernel lasts about rbw x (steps per chunk + a fixed per-unit cost); pick the chunk count
+    // that minimises that, i.e. fills the warp slots without spilling into a nearly empty
+    // second pass.
     int chunks = 1, rbw = 1;
     if (tuning && tuning->split_k > 0) {
         chunks = tuning->split_k;
-    } else if (row_blocks < slots) {
-        chunks = static_cast<int>((slots + row_blocks / 2) / row_blocks);
-        const int min_steps = 4;
-        if (chunks > pl.total_steps / min_steps) chunks = pl.total_steps / min_steps;
+    } else if (row_blocks <= kMaxCounters) {
+        double best_cost = 1e30;
+        for (int c = 1; c <= kMaxSplitK && c <= pl.total_steps; ++c) {
+            const int spc = (pl.total_steps + c - 1) / c;
+            if (c > 1 && spc < 4) break;
+            const int64_t passes = (row_blocks * c + slots - 1) / slots;
+            const double cost = static_cast<double>(passes) * (spc + 8) + (c > 1 ? 0.25 * c : 0.0);
+            if (cost < best_cost - 1e-9) { best_cost = cost; chunks = c; }
+        }
     }
     if (chunks > kMaxSplitK) chunks = kMaxSplitK;
     if (chunks > pl.total_steps) chunks = pl.total_steps;
     if (chunks < 1 || row_blocks > kMaxCounters) chunks = 1;
 
+    int rbw_cap = 2;
     for (;;) {
         pl.steps_per_chunk = (pl.total_steps + chunks - 1) / chunks;
         pl.num_chunks = (pl.total_steps + pl.steps_per_chunk - 1) / pl.steps_per_chunk;
         const int64_t units = row_blocks * pl.num_chunks;
+        // a warp takes at most rbw_cap consecutive row blocks (their scales are all staged up
+        // front); beyond that the grid simply has more CTAs than SMs
         rbw = static_cast<int>((units + slots - 1) / slots);
+        if (rbw > rbw_cap) rbw = rbw_cap;
         if (tuning && tuning->row_blocks_per_warp > 0) rbw = tuning->row_blocks_per_warp;
         if (rbw < 1) rbw = 1;
         pl.rbw = rbw;
@@ -720,7 +785,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         pl.xs_stride = static_cast<int>(((chunk_k * 2 + 127) / 128) * 128 + row_pad);
         const size_t ring = static_cast<size_t>(pl.stages) * 16 * pl.piece_bytes;
         const size_t sc = static_cast<size_t>(rbw) * 16 * pl.segs * 8;
-        pl.smem = ((static_cast<size_t>(a.M) * pl.xs_stride + static_cast<size_t>(pl.segs) * pl.nt * 8 * 4 + 1023) &
+        pl.smem = ((static_cast<size_t>(a.M) * pl.xs_stride + static_cast<size_t>(pl.segs) * pl.nt * 8 * 12 + 8 + 1023) &
                    ~size_t(1023)) + static_cast<size_t>(warps) * (ring + sc + 128);
         size_t need_ws = 0;
         if (pl.num_chunks > 1) need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
@@ -728,15 +793,21 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         const bool ws_ok = need_ws <= workspace_bytes;
         if (smem_ok && ws_ok) break;
         if (!smem_ok) {
+            // too much shared memory: fewer stages, then shorter chunks (less staged
+            // activation), then fewer warps
             if (pl.stages > 2) { --pl.stages; continue; }
+            if (rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap = 1; continue; }
+            if (chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
+                !(tuning && tuning->split_k > 0)) {
+                ++chunks;
+                continue;
+            }
             if (warps > 4 && !(tuning && tuning->warps_per_cta > 0)) {
                 warps >>= 1;
                 pl.warps = warps;
                 continue;   // `slots` keeps counting the original warps: rbw grows instead
             }
-            if (chunks >= pl.total_steps || chunks >= kMaxSplitK) return false;
-            ++chunks;
-            continue;
+            return false;
         }
         if (chunks == 1) return false;
         --chunks;
@@ -774,6 +845,24 @@ int launch_stream_nt(const StreamParams& p, const CUtensorMap& wmap, int nt, int
 }
 
 }  // namespace
+
+// Workspace the streaming plan wants for a problem on a 148-SM part with ideally aligned
+// buffers and zeros present (the largest shared-memory footprint); 0 if K is not split, and
+// `*supported` tells whether the streaming kernel takes the problem at all.
+size_t gemv_stream_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant, bool* supported)
+{
+    MatmulArgs a{};
+    a.x = a.wq = a.scales = a.zeros = reinterpret_cast<const void*>(uintptr_t(4096));
+    a.M = M; a.N = N; a.K = K; a.lda = K; a.ldc = N;
+    a.group_size = group_size;
+    a.G = K > 0 ? static_cast<int32_t>((K + group_size - 1) / group_size) : 0;
+    a.quant = quant; a.act_dtype = MNQ_FP16; a.scale_dtype = MNQ_FP16;
+    a.sm_count = 148;
+    StreamPlan pl;
+    *supported = plan_stream(a, nullptr, ~size_t(0), &pl);
+    if (!*supported || pl.num_chunks <= 1) return 0;
+    return kCounterBytes + static_cast<size_t>(pl.num_chunks) * M * N * 4;
+}
 
 bool gemv_stream_supported(const MatmulArgs& a, const mnq_tuning* tuning)
 {

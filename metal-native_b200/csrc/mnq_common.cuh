@@ -237,6 +237,7 @@ int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
 bool gemv_stream_supported(const MatmulArgs& a, const mnq_tuning* tuning);
 int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning);
 int read_device_status(unsigned int* out, bool clear);
+size_t gemv_stream_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant, bool* supported);
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
 bool gemm_supported(const MatmulArgs& a);
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size);

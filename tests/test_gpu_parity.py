@@ -195,6 +195,21 @@ def test_activation_row_stride_and_unaligned_views(mn):
     assert torch.equal(out2, mn._C.dequant_matmul(*d.args()))
 
 
+@pytest.mark.parametrize("scale", [3e5, 1.0, 1e-7])
+@pytest.mark.parametrize("quant,g", [("int4", 128), ("int8", 1024)])
+def test_bf16_activation_range(mn, scale, quant, g):
+    """bf16 activations run on fp16 tensor-core instructions after an exact power-of-two
+    rescale per CTA: magnitudes far outside the fp16 range must still come out right."""
+    from metal_native import workloads
+    L = workloads.make_layer("t", 3, 1024, 160, quant_type=quant, group_size=g, act_dtype=torch.bfloat16,
+                             scale_dtype=torch.bfloat16, asymmetric=(quant == "int4"), seed=17)
+    L.x = (L.x.float() * scale).to(torch.bfloat16)
+    ref = H.oracle_matmul(L, threads=1)
+    out = mn._C.dequant_matmul(*L.to("cuda").args())
+    assert mn._C.select_path(3, 160, 1024, g, quant, torch.bfloat16) == "gemv"
+    H.assert_close_to_oracle(out, ref, f"bf16 x{scale:g}")
+
+
 def test_paths_agree(mn):
     """The three kernel families compute the same function."""
     from metal_native import workloads
