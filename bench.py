@@ -295,7 +295,14 @@ def run_ours(args):
             if world > 1:
                 gathered[j].all_gather(outs[j])
 
-    kernels_per_step = len(layers_cpu)
+    def launches(L):
+        # one kernel per projection; the tensor-core path with K split adds its reduce kernel
+        path = _C.select_path(L.M, L.N, L.K, L.group_size, L.quant_type, L.x.dtype, zeros=L.zeros is not None)
+        q = 0 if L.quant_type == "int4" else 1
+        split = path == "gemm" and _C._lib.mnq_workspace_bytes(L.M, L.N, L.K, int(L.group_size), q) > 0
+        return 2 if split else 1
+
+    kernels_per_step = sum(launches(L) for L in layers_cpu)
 
     def barrier():
         if world > 1:

@@ -28,8 +28,10 @@
 // dequantised weights to bf16 would cost 1.6e-3 relative error by itself).
 //
 // Few tiles (a long-K, narrow-N layer) leave SMs idle, so K can be split over grid.z: every
-// split writes its fp32 partial tile to the workspace and, per warp-sized part of a tile, the
-// last split to arrive adds the partials in a fixed order and writes the output.
+// split writes its fp32 partial result to the workspace as [split][M][N], and a second small
+// kernel on the same stream adds the splits in a fixed order and writes the output.  (Letting
+// the last CTA to arrive do the addition inside the GEMM kernel left the whole reduction to a
+// few hundred warps with a handful of loads in flight each; it took longer than the GEMM.)
 //
 // Every mbarrier wait is bounded; a wait that gives up sets bit 1 of the device status word
 // and the CTA falls through to its teardown (tensor memory is always released).
@@ -51,6 +53,8 @@ constexpr int BN = 128;          // weight rows per CTA (MMA M)
 constexpr int BK = 64;           // k per stage: one 128-byte swizzle row of 16-bit elements
 constexpr int A_BYTES = BN * BK * 2;
 constexpr unsigned kSpin = 1u << 24;
+
+constexpr int kMaxSplits = 6;
 
 struct GemmParams {
     const uint8_t* wq;
@@ -75,7 +79,6 @@ struct GemmParams {
     int splits;         // K splits (grid.z)
     int kb_per_split;   // 64-k blocks per split
     float* partial;     // [splits][M][N] fp32 (splits > 1)
-    unsigned int* counters;   // [tiles][8] arrival counters (splits > 1)
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -392,23 +395,19 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             float scale = 1.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
             T* out = static_cast<T*>(p.out);
-            // split-K partial tiles live in the workspace as [split][n][padded token]: a thread's 32
-            // tokens of one chunk are 128 contiguous bytes, written and re-read as 16-byte vectors
-            const int tokp = (p.tok + 31) & ~31;          // chunks are 32 tokens: pad each tile to that
-            const size_t Mp = (size_t)gridDim.y * tokp;
-            const size_t mp0 = (size_t)blockIdx.y * tokp;
-            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.N * Mp : nullptr;
+            // with K split, this CTA's result goes to its [M][N] plane of the workspace instead
+            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.M * p.N : nullptr;
             for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (n < p.N) {
                     if (mine) {
-                        float4* dst = reinterpret_cast<float4*>(mine + (size_t)n * Mp + mp0 + c0);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            __stcg(dst + i, make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                        __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+                        for (int i = 0; i < 32; ++i) {
+                            const int m = m0 + c0 + i;
+                            if (c0 + i < p.tok && m < p.M) __stcg(mine + (size_t)m * p.N + n, __uint_as_float(v[i]) * scale);
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -417,46 +416,6 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                                 out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
                         }
                     }
-                }
-            }
-            if (mine) {
-                // the last split to arrive for this warp's part of the tile reduces it
-                __threadfence();
-                __syncwarp();
-                const unsigned int slot = ((blockIdx.y * gridDim.x + blockIdx.x) << 3) + (unsigned)(warp - 2);
-                unsigned int arrival = 0;
-                if (lane == 0) arrival = atomicAdd(&p.counters[slot], 1u);
-                arrival = __shfl_sync(0xffffffffu, arrival, 0);
-                if (arrival == (unsigned int)(p.splits - 1)) {
-                    __threadfence();
-                    if (n < p.N) {
-                        for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
-                            float4 acc[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            for (int z = 0; z < p.splits; ++z) {   // fixed order: deterministic
-                                const float4* src =
-                                    reinterpret_cast<const float4*>(p.partial + ((size_t)z * p.N + n) * Mp + mp0 + c0);
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    const float4 t4 = __ldcg(src + i);
-                                    acc[i].x += t4.x; acc[i].y += t4.y; acc[i].z += t4.z; acc[i].w += t4.w;
-                                }
-                            }
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float e[4] = {acc[i].x, acc[i].y, acc[i].z, acc[i].w};
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const int m = m0 + c0 + 4 * i + k;
-                                    if (c0 + 4 * i + k < p.tok && m < p.M)
-                                        out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(e[k] * scale);
-                                }
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) p.counters[slot] = 0u;   // ready for the next call
                 }
             }
         }
@@ -472,29 +431,75 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     }
 }
 
+// out[m, n] = sum over splits of partial[z][m][n], splits added in index order (deterministic).
+// VEC: eight consecutive n per thread as two 16-byte loads per split and one 16-byte store.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, T* __restrict__ out, int M,
+                                                            int N, int64_t ldc, int splits)
+{
+    const size_t plane = (size_t)M * N;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if (VEC) {
+        const size_t total = plane / 8;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+            const size_t e = i * 8;
+            float4 lo[kMaxSplits], hi[kMaxSplits];
+#pragma unroll
+            for (int z = 0; z < kMaxSplits; ++z)
+                if (z < splits) {
+                    lo[z] = __ldcs(reinterpret_cast<const float4*>(partial + z * plane + e));
+                    hi[z] = __ldcs(reinterpret_cast<const float4*>(partial + z * plane + e + 4));
+                }
+            float4 a = lo[0], b = hi[0];
+#pragma unroll
+            for (int z = 1; z < kMaxSplits; ++z)
+                if (z < splits) {
+                    a.x += lo[z].x; a.y += lo[z].y; a.z += lo[z].z; a.w += lo[z].w;
+                    b.x += hi[z].x; b.y += hi[z].y; b.z += hi[z].z; b.w += hi[z].w;
+                }
+            const size_t m = e / N, n = e % N;
+            union { T h[8]; uint4 u; } pk;
+            pk.h[0] = F16Traits<T>::from_float(a.x); pk.h[1] = F16Traits<T>::from_float(a.y);
+            pk.h[2] = F16Traits<T>::from_float(a.z); pk.h[3] = F16Traits<T>::from_float(a.w);
+            pk.h[4] = F16Traits<T>::from_float(b.x); pk.h[5] = F16Traits<T>::from_float(b.y);
+            pk.h[6] = F16Traits<T>::from_float(b.z); pk.h[7] = F16Traits<T>::from_float(b.w);
+            *reinterpret_cast<uint4*>(out + m * ldc + n) = pk.u;
+        }
+    } else {
+        for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < plane; e += stride) {
+            float acc = __ldcs(partial + e);
+            for (int z = 1; z < splits; ++z) acc += __ldcs(partial + z * plane + e);
+            out[(e / N) * ldc + (e % N)] = F16Traits<T>::from_float(acc);
+        }
+    }
+}
+
 struct GemmPlan {
     int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, table_groups, tmem_cols, splits, kb_per_split;
     size_t smem;
 };
 
-// Upper bound of tiles_m * tok, the padded token count of the split-K partial buffer.
-inline size_t padded_tokens(int64_t M) { return static_cast<size_t>(M + 96 * ((M + 511) / 512) + 96); }
-
-constexpr int kMaxSplits = 6;
 constexpr int kMaxTableGroups = 64;   // 32 KB of scale table at most
 
 // K splits: the count that minimises waves x (k-blocks per split + fixed per-CTA cost) plus
-// the cost of writing and re-reading one partial tile per split.
-int choose_splits(int64_t tiles, int num_kb, int sm_count)
+// the cost of writing and re-reading one fp32 result plane per split and of the second
+// launch, all in units of one k-block time (a little under a microsecond).
+int choose_splits(int64_t tiles, int num_kb, int sm_count, double plane_bytes)
 {
     int best = 1;
     double best_cost = 1e30;
     for (int sp = 1; sp <= kMaxSplits && sp <= num_kb; ++sp) {
         const int64_t waves = (tiles * sp + sm_count - 1) / sm_count;
-        const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) + (sp > 1 ? 4.0 * sp : 0.0);
+        const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) +
+                            (sp > 1 ? 4.0 + sp * plane_bytes / 2.5e6 : 0.0);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
     }
     return best;
+}
+
+inline size_t split_workspace_bytes(int splits, int64_t M, int64_t N)
+{
+    return kCounterBytes + static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * 4;
 }
 
 bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
@@ -529,22 +534,17 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
 
     const int num_kb = static_cast<int>(a.K / BK);
     const int64_t tiles = static_cast<int64_t>((a.N + BN - 1) / BN) * pl.tiles_m;
-    int best = (tuning && tuning->split_k > 0) ? tuning->split_k : choose_splits(tiles, num_kb, a.sm_count);
+    int best = (tuning && tuning->split_k > 0) ? tuning->split_k : choose_splits(tiles, num_kb, a.sm_count, 4.0 * a.M * a.N);
     if (best > kMaxSplits) best = kMaxSplits;
     if (best > num_kb) best = num_kb;
-    if (tiles * 8 > kMaxCounters) best = 1;
-    while (best > 1 &&
-           kCounterBytes + static_cast<size_t>(best) * padded_tokens(a.M) * a.N * 4 > (a.workspace ? a.workspace_bytes : 0))
+    while (best > 1 && split_workspace_bytes(best, a.M, a.N) > (a.workspace ? a.workspace_bytes : 0))
         --best;   // not enough workspace: fewer splits (one split needs none)
     // the scale table holds at most kMaxTableGroups groups per row: split K further if needed
     const int64_t total_groups = a.group_size >= a.K ? 1 : (a.K + a.group_size - 1) / a.group_size;
     const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
     if (best < min_splits) best = min_splits;
     if (best > kMaxSplits || best > num_kb) return false;
-    if (best > 1 && (tiles * 8 > kMaxCounters ||
-                     kCounterBytes + static_cast<size_t>(best) * padded_tokens(a.M) * a.N * 4 >
-                         (a.workspace ? a.workspace_bytes : 0)))
-        return false;
+    if (best > 1 && split_workspace_bytes(best, a.M, a.N) > (a.workspace ? a.workspace_bytes : 0)) return false;
     pl.kb_per_split = (num_kb + best - 1) / best;
     pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.table_groups = a.group_size >= a.K
@@ -583,7 +583,19 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
         if (rc) return rc;
     }
     kern<<<grid, 352, smem, stream>>>(p, xmap, wmap);
-    return check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
+    const int rc = check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
+    if (rc || p.splits <= 1) return rc;
+    // second launch: add the splits' planes and write the output
+    T* out = static_cast<T*>(p.out);
+    const bool vec = p.N % 8 == 0 && p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const size_t work = vec ? (size_t)p.M * p.N / 8 : (size_t)p.M * p.N;
+    size_t blocks = (work + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (vec)
+        splitk_reduce_kernel<T, true><<<(unsigned)blocks, 256, 0, stream>>>(p.partial, out, p.M, p.N, p.ldc, p.splits);
+    else
+        splitk_reduce_kernel<T, false><<<(unsigned)blocks, 256, 0, stream>>>(p.partial, out, p.M, p.N, p.ldc, p.splits);
+    return check_cuda(cudaGetLastError(), "splitk_reduce launch");
 }
 
 }  // namespace
@@ -614,13 +626,12 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
     // further, the plan falls back to the number of splits the given workspace can hold.
     if (M <= 32 || N < 1 || K < BK || K % BK) return 0;
     const int64_t tiles = ((N + BN - 1) / BN) * ((M + 511) / 512);
-    if (tiles * 8 > kMaxCounters) return 0;
-    int splits = choose_splits(tiles, static_cast<int>(K / BK), 148);
+    int splits = choose_splits(tiles, static_cast<int>(K / BK), 148, 4.0 * M * N);
     const int64_t total_groups = group_size >= K ? 1 : (K + group_size - 1) / group_size;
     const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
     if (splits < min_splits) splits = min_splits;
     if (splits <= 1 || splits > kMaxSplits) return 0;
-    return kCounterBytes + static_cast<size_t>(splits) * padded_tokens(M) * N * 4;
+    return split_workspace_bytes(splits, M, N);
 }
 
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
@@ -642,7 +653,6 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     if (pl.splits > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
-        p.counters = reinterpret_cast<unsigned int*>(ws);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
 

@@ -106,7 +106,7 @@ def test_workspace_bytes(C):
     wb = C._lib.mnq_workspace_bytes
     assert wb(0, 64, 128, 128, 0) == 0
     assert wb(512, 18944, 3584, 128, 0) == 0     # enough tiles to fill the GPU: no split-K workspace
-    assert wb(512, 3584, 18944, 128, 0) == (64 << 10) + 5 * (512 + 96 + 96) * 3584 * 4   # 28 tiles: K split 5 ways
+    assert wb(512, 3584, 18944, 128, 0) == (64 << 10) + 5 * 512 * 3584 * 4   # 28 tiles: K split 5 ways, one fp32 plane each
     small = wb(1, 3584, 18944, 128, 0)
     assert 3584 * 4 * 2 < small < 4 << 20
     assert wb(32, 57344, 8192, 8192, 1) < 64 << 20
