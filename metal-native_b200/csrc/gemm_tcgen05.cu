@@ -47,12 +47,16 @@ namespace mnq {
 // code); read_device_status() in gemv_stream.cu merges it through read_gemm_status().
 __device__ unsigned int g_gemm_status = 0;
 
+
 namespace {
 
 constexpr int BN = 128;          // weight rows per CTA (MMA M)
 constexpr int BK = 64;           // k per stage: one 128-byte swizzle row of 16-bit elements
 constexpr int A_BYTES = BN * BK * 2;
-constexpr unsigned kSpin = 1u << 24;
+// A waiting thread may stay suspended in hardware for up to kSuspendNs per try (it is woken
+// when the phase completes), so a wait costs few instructions; kSpin tries bound the total.
+constexpr unsigned kSpin = 1u << 22;
+constexpr uint32_t kSuspendNs = 1000;
 
 constexpr int kMaxSplits = 6;
 
@@ -75,10 +79,12 @@ struct GemmParams {
     int tmem_cols;      // power of two >= max(32, tok)
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
     int raw_stages;     // stages of the packed-weight ring
+    int raw_segs;       // 128-byte-wide boxes per stage (consecutive along k)
     int table_groups;   // quantisation groups per row held in the shared-memory scale table
     int splits;         // K splits (grid.z)
     int kb_per_split;   // 64-k blocks per split
     float* partial;     // [splits][M][N] fp32 (splits > 1)
+    int vec_store;      // bit 0: out allows 16-byte stores, bit 1: the split-K planes do
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -99,9 +105,9 @@ __device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity)
@@ -110,6 +116,57 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity)
         if (bar_try(bar, parity)) return true;
     return false;
 }
+// ---- CTA pair (cluster of two) helpers ----
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// Arrival on a barrier of either CTA of the pair.  Default (CTA-scope) release: what the
+// arrival publishes is this warp's dequantised tile, already pushed to the async proxy by
+// fence.proxy.async, and it is read only by this SM's own tensor core; the barrier is merely
+// where the leader learns of it.  (A cluster-scope release here costs ~0.4 us per k-block.)
+__device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// wait that also acquires writes released by the peer CTA's threads
+__device__ __forceinline__ bool bar_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    for (unsigned i = 0; i < kSpin; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// hardware barrier over all threads of both CTAs (no spinning)
+__device__ __forceinline__ void cluster_sync()
+{
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA tile load whose completion may be signalled on a barrier of either CTA of the pair
+// (`bar` is a shared::cluster address); the destination is this CTA's shared memory
+__device__ __forceinline__ void tma_load_tile_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {
     asm volatile(
@@ -126,12 +183,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
-// kind::f16 instruction descriptor: fp32 accumulate, A and B both K-major, M = 128, N = tok.
-__device__ __forceinline__ uint32_t instr_desc(int tok, bool bf16)
+// kind::f16 instruction descriptor: fp32 accumulate, A and B both K-major, M = rows (128, or
+// 256 for a CTA pair), N = tok.
+__device__ __forceinline__ uint32_t instr_desc(int tok, bool bf16, int rows)
 {
     const uint32_t fmt = bf16 ? 1u : 0u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tok >> 3) << 17) |
-           (static_cast<uint32_t>(BN >> 4) << 24);
+           (static_cast<uint32_t>(rows >> 4) << 24);
 }
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
@@ -144,6 +202,21 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// CTA pair: one MMA over both CTAs' weight tiles (256 rows) and both halves of the activation tile
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
@@ -155,6 +228,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // 8 consecutive k of one row -> one 16-byte chunk of 16-bit values in natural k order.
@@ -217,12 +307,96 @@ template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
     }
 };
 
-template <int QUANT, typename T>
+// Staged element stores for the epilogue.
+template <typename E> struct StageIO;
+template <> struct StageIO<float> {
+    static __device__ __forceinline__ void put(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+    static __device__ __forceinline__ float get(uint32_t addr) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr)); return v; }
+    static __device__ __forceinline__ float from(float v) { return v; }
+};
+template <> struct StageIO<__half> {
+    static __device__ __forceinline__ void put(uint32_t addr, __half v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(__half_as_ushort(v)) : "memory"); }
+    static __device__ __forceinline__ __half get(uint32_t addr) { unsigned short v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr)); return __ushort_as_half(v); }
+    static __device__ __forceinline__ __half from(float v) { return __float2half_rn(v); }
+};
+template <> struct StageIO<__nv_bfloat16> {
+    static __device__ __forceinline__ void put(uint32_t addr, __nv_bfloat16 v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(__bfloat16_as_ushort(v)) : "memory"); }
+    static __device__ __forceinline__ __nv_bfloat16 get(uint32_t addr) { unsigned short v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr)); return __ushort_as_bfloat16(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Epilogue of one CTA tile, run by the eight dequantise warps (256 threads, `e` = 0..255).
+// Accumulator lane = weight row, columns = tokens, but the output is [token][row]: a thread
+// storing its own accumulator elements writes 2 or 4 bytes per token row.  Instead the tile
+// goes through shared memory in slabs of 64 tokens (two buffers, so one barrier per slab):
+// each warp drops its 32 x 32 block as [token][row], then all threads copy the slab out as
+// 16-byte pieces of whole 128-row lines.  `vec`: destination base and leading dimension allow
+// 16-byte stores; otherwise the copy is element by element (still whole lines per warp).
+template <typename E>
+__device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int half, int row, int e, int tok,
+                                              uint32_t stage0, float scale, E* dst, size_t ld, int n0, int N, int m0,
+                                              int M, bool vec)
+{
+    constexpr int RB = BN * (int)sizeof(E);    // bytes per staged token row
+    constexpr int PPR = RB / 16;               // 16-byte pieces per row
+    constexpr int RPS = 256 / PPR;             // rows per copy step
+    constexpr int EPP = 16 / (int)sizeof(E);   // elements per piece
+    const int slabs = (tok + 63) / 64;
+    for (int j = 0; j < slabs; ++j) {
+        const uint32_t stage = stage0 + (uint32_t)((j & 1) * 64 * RB);
+        const int c0 = j * 64 + half * 32;     // this warp's 32 tokens of the slab
+        if (c0 < tok) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const uint32_t at = stage + (uint32_t)(half * 32 * RB) + (uint32_t)row * (uint32_t)sizeof(E);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) StageIO<E>::put(at + i * RB, StageIO<E>::from(__uint_as_float(v[i]) * scale));
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (vec) {
+            const int piece = e % PPR, rsub = e / PPR;
+            const int n = n0 + piece * EPP;
+#pragma unroll 4
+            for (int r = rsub; r < 64; r += RPS) {
+                const int c = j * 64 + r;
+                const int m = m0 + c;
+                if (c < tok && m < M) {
+                    if (n + EPP <= N) {
+                        const uint4 q = lds128(stage + (uint32_t)(r * RB + piece * 16));
+                        __stcg(reinterpret_cast<uint4*>(dst + (size_t)m * ld + n), q);
+                    } else {
+                        for (int k = 0; k < EPP; ++k)
+                            if (n + k < N)
+                                dst[(size_t)m * ld + n + k] = StageIO<E>::get(stage + (uint32_t)(r * RB + (piece * EPP + k) * (int)sizeof(E)));
+                    }
+                }
+            }
+        } else {
+            for (int idx = e; idx < 64 * BN; idx += 256) {
+                const int r = idx / BN, nn = idx % BN;
+                const int c = j * 64 + r;
+                const int m = m0 + c;
+                if (c < tok && m < M && n0 + nn < N)
+                    dst[(size_t)m * ld + n0 + nn] = StageIO<E>::get(stage + (uint32_t)(r * RB + nn * (int)sizeof(E)));
+            }
+        }
+    }
+}
+
+// PAIR: launched as clusters of two CTAs along x.  Each CTA still owns 128 weight rows and its
+// own accumulators, but one `cta_group::2` MMA, issued by the even CTA (the leader), covers
+// both: every CTA loads only half of each activation tile (tokh / 2 tokens) and the tensor
+// cores read the other half from the peer's shared memory, which halves the L2 -> SM traffic
+// of activation tiles.  Both CTAs run the same stage sequence; "tile ready" barriers live in
+// the leader (the peer's dequantise warps and TMA signal them remotely), "tile free" barriers
+// in each CTA (the leader commits to both).
+template <int QUANT, typename T, bool PAIR>
 __global__ void __launch_bounds__(352, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                     const __grid_constant__ CUtensorMap wmap)
 {
-    constexpr int WPK = (QUANT == MNQ_INT4) ? 1 : 2;   // 16-byte loads per thread per k-block (half a row)
+    constexpr int WPK = (QUANT == MNQ_INT4) ? 1 : 2;   // 16-byte packed chunks per 32 k of one row
     constexpr int KB_BYTES = WPK * 32;                  // packed bytes per row per k-block
     constexpr int KPR = 128 / KB_BYTES;                 // k-blocks covered by one raw stage (128 packed bytes per row)
     constexpr int RAW_BYTES = BN * 128;
@@ -230,8 +404,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
-    // a_full[8], a_empty[8], accum, raw_full[4], raw_empty[4], b_full[8], b_empty[8]
-    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1 + 2 * 4 + 2 * 8];
+    // ready[8], done[8], accum, raw_full[4], raw_empty[4]
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1 + 2 * 4];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -240,32 +414,54 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const int m0 = blockIdx.y * p.tok;
     const int kb_begin = blockIdx.z * p.kb_per_split;
     const int num_kb = min(p.K / BK, kb_begin + p.kb_per_split) - kb_begin;   // k-blocks of this split
-    const int S = p.stages, SB = p.b_stages;
-    const int b_bytes = p.tokh * 128;
+    // Rings: S weight tiles, SB activation stages (one stage = the nh tiles of one k-block).
+    // Synchronisation is per k-block, on D = max(S, SB) barrier pairs indexed kb % D:
+    // ready[kb % D] completes when the k-block's weight tile is dequantised (one arrival per
+    // dequantise warp that works on it: four per CTA) and its activation tiles have landed (one arrival with the byte count);
+    // done[kb % D] completes when the MMAs of that k-block have read their operands (one commit).
+    // A producer refilling ring slot kb % S (or kb % SB) waits for done of k-block kb - S (kb - SB).
+    // So the MMA thread does one wait and one commit per k-block.
+    const int S = p.stages, SB = p.b_stages, D = max(S, SB);
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;   // 0: leader (issues the MMAs), 1: peer
+    const int b_rows = PAIR ? p.tokh / 2 : p.tokh;       // tokens of each activation tile this CTA loads
+    const int b_bytes = b_rows * 128;
     const uint32_t tiles = (s_u32(smem_raw) + 1023u) & ~1023u;   // 1024-byte aligned: weight-tile ring
     const uint32_t btiles = tiles + S * A_BYTES;                  // activation-tile ring
-    const uint32_t raw0 = btiles + SB * b_bytes;                  // packed-weight ring
+    const uint32_t raw0 = btiles + SB * p.nh * b_bytes;           // packed-weight ring
     const int R = p.raw_stages;
-    const uint32_t tbl0 = raw0 + R * RAW_BYTES;                   // [group][row] scale | zero << 16
-    const int num_raw = (num_kb + KPR - 1) / KPR;
-    const uint32_t full0 = s_u32(&bars[0]), empty0 = s_u32(&bars[8]), accum = s_u32(&bars[16]);
+    const int NSEG = p.raw_segs;
+    const uint32_t tbl0 = raw0 + R * NSEG * RAW_BYTES;                   // [group][row] scale | zero << 16
+    const int KPS = KPR * NSEG;                                   // k-blocks per packed stage
+    const int num_raw = (num_kb + KPS - 1) / KPS;
+    // Every CTA (pair) walks its k-blocks in a rotated order, starting at a different packed
+    // stage: CTAs launched together would otherwise all ask L2 for the same activation lines
+    // at the same moment.  Sequence index i -> k-block (i + k_rot) mod num_kb.
+    const int st = (int)((blockIdx.x >> 1) % (unsigned)num_raw);
+    const int k_rot = st * KPS;
+    const uint32_t ready0 = s_u32(&bars[0]), done0 = s_u32(&bars[8]), accum = s_u32(&bars[16]);
     const uint32_t rfull0 = s_u32(&bars[17]), rempty0 = s_u32(&bars[21]);
-    const uint32_t bfull0 = s_u32(&bars[25]), bempty0 = s_u32(&bars[33]);
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { bar_init(full0 + 8 * s, 8); bar_init(empty0 + 8 * s, 1); }
-        for (int s = 0; s < SB; ++s) { bar_init(bfull0 + 8 * s, 1); bar_init(bempty0 + 8 * s, 1); }
+        // ready: the dequantise warps of every CTA feeding the MMA, plus the thread that announces the bytes
+        for (int d = 0; d < D; ++d) { bar_init(ready0 + 8 * d, (PAIR ? 8 : 4) + 1); bar_init(done0 + 8 * d, 1); }
         bar_init(accum, 1);
         for (int r = 0; r < R; ++r) { bar_init(rfull0 + 8 * r, 1); bar_init(rempty0 + 8 * r, 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(s_u32(&tmem_base_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {   // one warp of each CTA of the pair
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(s_u32(&tmem_base_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(s_u32(&tmem_base_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
-    __syncthreads();
+    if (PAIR) cluster_sync();   // the peer's barriers are initialised before anything signals them
+    else __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
     bool failed = false;
@@ -273,14 +469,28 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     if (warp == 0) {
         // ---------------- activation tiles by TMA ----------------
         if (lane == 0) {
-            int sb = 0; uint32_t ph = 0;
-            for (int kb = 0; kb < num_kb && !failed; ++kb) {
-                for (int h = 0; h < p.nh; ++h) {
-                    if (!bar_wait(bempty0 + 8 * sb, ph ^ 1u)) { failed = true; break; }
-                    bar_expect_tx(bfull0 + 8 * sb, (uint32_t)b_bytes);
-                    tma_load_tile(btiles + sb * b_bytes, &xmap, (kb_begin + kb) * BK, m0 + h * p.tokh, bfull0 + 8 * sb);
-                    if (++sb == SB) { sb = 0; ph ^= 1u; }
+            const uint32_t ready_at = PAIR ? map_to_rank(ready0, 0) : ready0;   // the leader's barriers
+            const uint32_t stage_bytes = (uint32_t)(p.nh * b_bytes);
+            int sb = 0, d = 0;
+            int wd = 0; uint32_t wph = 0;   // done[(kb - SB) % D] and its phase
+            for (int i = 0; i < num_kb; ++i) {
+                const int kb = i + k_rot < num_kb ? i + k_rot : i + k_rot - num_kb;
+                if (i >= SB) {
+                    if (!bar_wait(done0 + 8 * wd, wph)) { failed = true; break; }
+                    if (++wd == D) { wd = 0; wph ^= 1u; }
                 }
+                // one arrival announcing all the bytes of the k-block (both CTAs' halves for a pair)
+                if (rank == 0) bar_expect_tx(ready0 + 8 * d, PAIR ? 2u * stage_bytes : stage_bytes);
+                for (int h = 0; h < p.nh; ++h) {
+                    const uint32_t dst = btiles + (uint32_t)(sb * p.nh + h) * (uint32_t)b_bytes;
+                    if (PAIR)
+                        tma_load_tile_pair(dst, &xmap, (kb_begin + kb) * BK, m0 + h * p.tokh + (int)rank * b_rows,
+                                           ready_at + 8 * d);
+                    else
+                        tma_load_tile(dst, &xmap, (kb_begin + kb) * BK, m0 + h * p.tokh, ready0 + 8 * d);
+                }
+                if (++sb == SB) sb = 0;
+                if (++d == D) d = 0;
             }
         }
     } else if (warp == 10) {
@@ -289,46 +499,58 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             int r = 0; uint32_t ph = 0;
             for (int j = 0; j < num_raw; ++j) {
                 if (!bar_wait(rempty0 + 8 * r, ph ^ 1u)) { failed = true; break; }
-                bar_expect_tx(rfull0 + 8 * r, (uint32_t)RAW_BYTES);
-                tma_load_tile(raw0 + r * RAW_BYTES, &wmap, ((kb_begin + j * KPR) * KB_BYTES) >> 2, n0, rfull0 + 8 * r);
+                // NSEG boxes side by side along k: each row's 128-byte pieces are adjacent in memory
+                // and requested back to back (boxes past the end of K are zero-filled)
+                bar_expect_tx(rfull0 + 8 * r, (uint32_t)(NSEG * RAW_BYTES));
+                const int jj = st + j < num_raw ? st + j : st + j - num_raw;
+                for (int u = 0; u < NSEG; ++u)
+                    tma_load_tile(raw0 + (r * NSEG + u) * RAW_BYTES, &wmap,
+                                  (((kb_begin + (jj * NSEG + u) * KPR) * KB_BYTES) >> 2), n0, rfull0 + 8 * r);
                 if (++r == R) { r = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
-        if (lane == 0) {
-            const uint32_t idesc = instr_desc(p.tokh, IS_BF16);
-            int s = 0; uint32_t ph = 0;
-            int sb = 0; uint32_t bph = 0;
-            for (int kb = 0; kb < num_kb && !failed; ++kb) {
-                if (!bar_wait(full0 + 8 * s, ph)) { failed = true; break; }
-                const uint32_t a_addr = tiles + s * A_BYTES;
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc(p.tokh, IS_BF16, PAIR ? 2 * BN : BN);
+            int s = 0, sb = 0, d = 0; uint32_t dph = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {   // kb: position in this CTA's k order
+                if (!(PAIR ? bar_wait_cluster(ready0 + 8 * d, dph) : bar_wait(ready0 + 8 * d, dph))) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = smem_desc_sw128(tiles + s * A_BYTES);
                 for (int h = 0; h < p.nh; ++h) {
-                    if (!bar_wait(bfull0 + 8 * sb, bph)) { failed = true; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t b_addr = btiles + sb * b_bytes;
+                    const uint64_t bdesc = smem_desc_sw128(btiles + (uint32_t)(sb * p.nh + h) * (uint32_t)b_bytes);
+                    const uint32_t acc = tmem_base + (uint32_t)(h * p.tokh);
 #pragma unroll
-                    for (int j = 0; j < BK / 16; ++j)
-                        umma(tmem_base + (uint32_t)(h * p.tokh), smem_desc_sw128(a_addr + j * 32),
-                             smem_desc_sw128(b_addr + j * 32), idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                    umma_commit(bempty0 + 8 * sb);   // frees the activation tile once these MMAs have read it
-                    if (++sb == SB) { sb = 0; bph ^= 1u; }
+                    for (int j = 0; j < BK / 16; ++j) {   // 32 bytes along k = 2 descriptor address units
+                        if (PAIR) umma_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        else umma(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
                 }
-                umma_commit(empty0 + 8 * s);         // frees the weight tile
-                if (++s == S) { s = 0; ph ^= 1u; }
+                // operands of this k-block are free once these MMAs have read them
+                if (PAIR) umma_commit_pair(done0 + 8 * d);
+                else umma_commit(done0 + 8 * d);
+                if (++s == S) s = 0;
+                if (++sb == SB) sb = 0;
+                if (++d == D) { d = 0; dph ^= 1u; }
             }
-            umma_commit(accum);                      // accumulators complete
+            if (PAIR) umma_commit_pair(accum);   // accumulators complete, in both CTAs
+            else umma_commit(accum);
         }
     } else {
         // ---------------- dequantise weight tiles, then epilogue ----------------
         const int quad = warp & 3;             // tensor-memory lane quadrant this warp may read
-        const int half = (warp - 2) >> 2;      // which 32 k of each 64-k block / which columns in the epilogue
+        const int half = (warp - 2) >> 2;      // parity of the k-blocks this warp dequantises / which columns in the epilogue
         const int row = quad * 32 + lane;      // row of the tile = TMEM lane
         const int n = n0 + row;
         const size_t sc_row = (size_t)min(n, p.N - 1) * p.G;
-        // generic pointer to shared-window address 0: the tile loads/stores below are ordinary
-        // C++ accesses, so the compiler may interleave the four chunks of a k-block
-        unsigned char* const gen = smem_raw - s_u32(smem_raw);
+        // byte offset of 16-byte chunk c inside this row's 128-byte line, after the 128-byte swizzle
+        uint32_t xoff[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) xoff[c] = (uint32_t)((c ^ (row & 7)) << 4);
+        // k-blocks per quantisation group as a shift when it is a power of two (it almost always is)
+        const int kbg = (p.group_size >= p.K) ? 1 : p.group_size / BK;
+        const int kbg_shift = (kbg & (kbg - 1)) == 0 ? 31 - __clz(kbg) : -1;
         const bool one_group = p.group_size >= p.K;
         const int g_first = one_group ? 0 : (kb_begin * BK) / p.group_size;
         {   // scale | zero << 16 of every (row, group) this CTA touches, [group][row]
@@ -336,51 +558,88 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
             const int g_last = one_group ? 0 : ((kb_begin + num_kb) * BK - 1) / p.group_size;
             const int gc = g_last - g_first + 1;          // <= p.table_groups
-            for (int idx = tid - 64; idx < BN * gc; idx += 256) {
-                const int rr = idx / gc;
-                const int gi = idx - rr * gc;
-                const size_t src = (size_t)min(n0 + rr, p.N - 1) * p.G + g_first + gi;
-                uint32_t v = __ldg(sc16 + src);
-                if (zr16) v |= (uint32_t)__ldg(zr16 + src) << 16;
-                asm volatile("st.shared.u32 [%0], %1;" ::"r"(tbl0 + (gi * BN + rr) * 4), "r"(v) : "memory");
+            // eight entries per thread and pass, all loads issued before the first store: the whole
+            // table costs one or two global round trips instead of one per entry
+            // Two threads per weight row, each taking half of the row's groups as one contiguous
+            // run: sixteen groups per pass with every load issued before the first store, so the
+            // table costs a global round trip or two.  Indices past the end are clamped (the load
+            // is harmless, the store is skipped): no branch separates the loads.
+            constexpr int TU = 16;
+            const int rr = (tid - 64) >> 1, hp = (tid - 64) & 1;
+            const int gh = (gc + 1) >> 1;
+            const int gbeg = hp * gh, gend = min(gc, gbeg + gh);
+            const size_t rowsrc = (size_t)min(n0 + rr, p.N - 1) * p.G + g_first;
+            const unsigned short* zsrc = zr16 ? zr16 : sc16;
+            for (int g0 = gbeg; g0 < gend; g0 += TU) {
+                uint32_t sv[TU], zv[TU];
+#pragma unroll
+                for (int u = 0; u < TU; ++u) {
+                    const int g = min(g0 + u, gend - 1);
+                    sv[u] = __ldg(sc16 + rowsrc + g);
+                    zv[u] = __ldg(zsrc + rowsrc + g);
+                }
+#pragma unroll
+                for (int u = 0; u < TU; ++u)
+                    if (g0 + u < gend)
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(tbl0 + (uint32_t)(((g0 + u) * BN + rr) * 4)),
+                                     "r"(sv[u] | (zr16 ? zv[u] << 16 : 0u)) : "memory");
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight dequantise warps only
         }
 
-        int s = 0; uint32_t ph = 0;
+        const uint32_t ready_at = PAIR ? map_to_rank(ready0, 0) : ready0;   // the leader's barriers
+        // This warp takes every other k-block of the CTA's k order (whole 64-k rows of its 32 weight rows),
+        // so it pays for the barrier traffic of a k-block only every other k-block.
+        int s = half, d = half;                 // kb % S and kb % D of this warp's next k-block (S, D >= 2)
+        int wd = (S ^ half) & 1; uint32_t wph = 0;   // done[(kb - S) % D] and its phase, from this warp's first kb >= S
         int r = 0; uint32_t rph = 0;
+        int seq = 0;                            // position of the next k-block in this CTA's k order
         for (int j = 0; j < num_raw && !failed; ++j) {
             if (!bar_wait(rfull0 + 8 * r, rph)) { failed = true; break; }
-            const uint32_t raw_row = raw0 + r * RAW_BYTES + row * 128;
+            const int jj = st + j < num_raw ? st + j : st + j - num_raw;
+            for (int u = 0; u < NSEG && !failed; ++u) {
+            const uint32_t raw_row = raw0 + (r * NSEG + u) * RAW_BYTES + row * 128;
 #pragma unroll
             for (int q = 0; q < KPR; ++q) {
-                const int kb = j * KPR + q;
+                const int kb = (jj * NSEG + u) * KPR + q;
                 if (kb >= num_kb || failed) break;
-                uint32_t w[WPK * 4];
+                const int i = seq++;
+                if ((i & 1) != half) continue;
+                uint32_t w[WPK * 8];
 #pragma unroll
-                for (int i = 0; i < WPK; ++i) {
-                    const int chunk = q * (8 / KPR) + half * WPK + i;   // 16-byte chunk of the 128-byte raw row
-                    const uint4 pk = *reinterpret_cast<const uint4*>(gen + (raw_row + ((chunk ^ (row & 7)) << 4)));
+                for (int i = 0; i < 2 * WPK; ++i) {
+                    const int chunk = q * (8 / KPR) + i;   // 16-byte chunk of the 128-byte raw row
+                    const uint4 pk = lds128(raw_row + xoff[chunk]);
                     w[4 * i] = pk.x; w[4 * i + 1] = pk.y; w[4 * i + 2] = pk.z; w[4 * i + 3] = pk.w;
                 }
-                const int gi = one_group ? 0 : ((kb_begin + kb) * BK) / p.group_size - g_first;
-                const uint32_t sz = *reinterpret_cast<const uint32_t*>(gen + (tbl0 + (gi * BN + row) * 4));
+                const int gi = one_group ? 0
+                               : (kbg_shift >= 0 ? (kb_begin + kb) >> kbg_shift : (kb_begin + kb) / kbg) - g_first;
+                const uint32_t sz = lds32(tbl0 + (uint32_t)(gi * BN + row) * 4u);
                 __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
                 // -z with the sign flipped in place (exact)
                 __half2 nz2 = __half2half2(__ushort_as_half((unsigned short)((sz >> 16) ^ 0x8000u)));
-                if (!bar_wait(empty0 + 8 * s, ph ^ 1u)) { failed = true; break; }
+                if (i >= S) {   // the MMAs that read this ring slot S k-blocks ago are done
+                    if (!bar_wait(done0 + 8 * wd, wph)) { failed = true; break; }
+                    wd += 2;
+                    if (wd >= D) { wd -= D; wph ^= 1u; }
+                }
                 const uint32_t a_row = tiles + s * A_BYTES + row * 128;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const int c = half * 4 + c4;
-                    const uint4 o = TileChunk<QUANT, T>::run(&w[c4 * TileChunk<QUANT, T>::WORDS], s2, nz2);
-                    const uint32_t dst = a_row + ((c ^ (row & 7)) << 4);
-                    *reinterpret_cast<uint4*>(gen + dst) = o;
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
+                    sts128(a_row + xoff[c], o);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) bar_arrive(full0 + 8 * s);
-                if (++s == S) { s = 0; ph ^= 1u; }
+                if (lane == 0) {
+                    if (PAIR) bar_arrive_cluster(ready_at + 8 * d);   // the leader waits for both CTAs' tiles
+                    else bar_arrive(ready0 + 8 * d);
+                }
+                s += 2;
+                if (s >= S) s -= S;
+                d += 2;
+                if (d >= D) d -= D;
+            }
             }
             __syncwarp();
             if (lane == 0) bar_arrive(rempty0 + 8 * r);   // this warp is done with the raw stage
@@ -390,44 +649,44 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         // epilogue: accumulator row `row` holds out[m0 .. m0+tok, n]; this warp takes the
         // 32-column chunks with chunk index % 2 == half
         if (!failed && !bar_wait(accum, 0)) failed = true;
+        // The epilogue synchronises the eight warps with each other, so they all take it or none
+        // does: every thread arrives here, failed or not, and learns whether any of them failed.
+        {
+            uint32_t any;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(any) : "r"((uint32_t)failed) : "memory");
+            if (any && !failed) failed = true;
+        }
         if (!failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float scale = 1.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
-            T* out = static_cast<T*>(p.out);
-            // with K split, this CTA's result goes to its [M][N] plane of the workspace instead
-            float* mine = p.splits > 1 ? p.partial + (size_t)blockIdx.z * p.M * p.N : nullptr;
-            for (int c0 = half * 32; c0 < p.tok; c0 += 64) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.N) {
-                    if (mine) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int m = m0 + c0 + i;
-                            if (c0 + i < p.tok && m < p.M) __stcg(mine + (size_t)m * p.N + n, __uint_as_float(v[i]) * scale);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int m = m0 + c0 + i;
-                            if (c0 + i < p.tok && m < p.M)
-                                out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(__uint_as_float(v[i]) * scale);
-                        }
-                    }
-                }
-            }
+            // with K split, this CTA's result goes to its [M][N] plane of the workspace instead;
+            // the rings are idle now (every MMA has completed), so their memory stages the tile
+            if (p.splits > 1)
+                epilogue_tile<float>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
+                                     p.partial + (size_t)blockIdx.z * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
+                                     (p.vec_store & 2) != 0);
+            else
+                epilogue_tile<T>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale, static_cast<T*>(p.out),
+                                 (size_t)p.ldc, n0, p.N, m0, p.M, (p.vec_store & 1) != 0);
         }
     }
-
     if (failed && lane == 0) atomicOr(&g_gemm_status, 2u);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    // a pair releases its tensor memory, and lets go of each other's shared memory, together
+    if (PAIR) cluster_sync();
+    else __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
-                     : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                         : "memory");
     }
 }
 
@@ -475,7 +734,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 }
 
 struct GemmPlan {
-    int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, table_groups, tmem_cols, splits, kb_per_split;
+    int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, raw_segs, table_groups, tmem_cols, splits, kb_per_split;
+    int pair;       // 1: clusters of two CTAs sharing each activation tile
+    int tiles_n;    // CTAs along N (even when pair)
     size_t smem;
 };
 
@@ -502,6 +763,34 @@ inline size_t split_workspace_bytes(int splits, int64_t M, int64_t N)
     return kCounterBytes + static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * 4;
 }
 
+// Token tiling and CTA pairing: up to 512 tokens per CTA as two accumulators of up to 256;
+// CTA pairs (variant 0: for tiles of more than 256 tokens, where activation tiles dominate the
+// L2 -> SM traffic and no longer fit three stages deep otherwise; 1: never; 2: always).
+bool tile_plan(int64_t M, int64_t N, int variant, GemmPlan* out)
+{
+    GemmPlan& pl = *out;
+    pl.tiles_m = static_cast<int>((M + 511) / 512);
+    const int64_t per_tile = (M + pl.tiles_m - 1) / pl.tiles_m;
+    if (per_tile > 256) {
+        pl.nh = 2;
+        pl.tokh = static_cast<int>((((per_tile + 1) / 2 + 31) / 32) * 32);
+    } else {
+        pl.nh = 1;
+        pl.tokh = static_cast<int>(((per_tile + 15) / 16) * 16);
+    }
+    if (pl.tokh > 256) pl.tokh = 256;
+    pl.tok = pl.nh * pl.tokh;
+    pl.tiles_m = static_cast<int>((M + pl.tok - 1) / pl.tok);
+    if (pl.tiles_m > 65535) return false;
+    int cols = 32;
+    while (cols < pl.tok) cols <<= 1;
+    pl.tmem_cols = cols;
+    pl.pair = variant == 1 ? 0 : variant == 2 ? 1 : (pl.tok > 256 && N > BN);
+    pl.tiles_n = static_cast<int>((N + BN - 1) / BN);
+    if (pl.pair) pl.tiles_n = (pl.tiles_n + 1) & ~1;
+    return true;
+}
+
 bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
 {
     if (a.M < 1 || a.N < 1 || a.K < BK || a.K % BK) return false;
@@ -514,26 +803,10 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
         if (a.group_size < a.K || a.zeros != nullptr) return false;   // bf16: scale in the epilogue only
     }
     GemmPlan pl{};
-    // token tile: up to 512 tokens per CTA as two accumulators of up to 256
-    pl.tiles_m = static_cast<int>((a.M + 511) / 512);
-    const int64_t per_tile = (a.M + pl.tiles_m - 1) / pl.tiles_m;
-    if (per_tile > 256) {
-        pl.nh = 2;
-        pl.tokh = static_cast<int>((((per_tile + 1) / 2 + 31) / 32) * 32);
-    } else {
-        pl.nh = 1;
-        pl.tokh = static_cast<int>(((per_tile + 15) / 16) * 16);
-    }
-    if (pl.tokh > 256) pl.tokh = 256;
-    pl.tok = pl.nh * pl.tokh;
-    pl.tiles_m = static_cast<int>((a.M + pl.tok - 1) / pl.tok);
-    if (pl.tiles_m > 65535) return false;
-    int cols = 32;
-    while (cols < pl.tok) cols <<= 1;
-    pl.tmem_cols = cols;
+    if (!tile_plan(a.M, a.N, tuning ? tuning->gemv_variant : 0, &pl)) return false;
 
     const int num_kb = static_cast<int>(a.K / BK);
-    const int64_t tiles = static_cast<int64_t>((a.N + BN - 1) / BN) * pl.tiles_m;
+    const int64_t tiles = static_cast<int64_t>(pl.tiles_n) * pl.tiles_m;
     int best = (tuning && tuning->split_k > 0) ? tuning->split_k : choose_splits(tiles, num_kb, a.sm_count, 4.0 * a.M * a.N);
     if (best > kMaxSplits) best = kMaxSplits;
     if (best > num_kb) best = num_kb;
@@ -551,38 +824,61 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
                           ? 1
                           : static_cast<int>((static_cast<int64_t>(pl.kb_per_split) * BK + a.group_size - 1) / a.group_size + 1);
 
-    // shared memory: packed ring, scale table, then weight tiles (>= 2) and activation tiles (>= 2, ideally 4)
-    pl.raw_stages = 3;
-    const size_t b_tile = static_cast<size_t>(pl.tokh) * 128;
-    const size_t ring = static_cast<size_t>(pl.raw_stages) * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
-    const size_t budget = 226 * 1024 - 1024 - ring;
-    int ast = 3, bst = static_cast<int>((budget - 3 * A_BYTES) / b_tile);
-    if (bst < 4) {
-        ast = 2;
-        bst = static_cast<int>((budget - 2 * A_BYTES) / b_tile);
+    // shared memory: packed ring, scale table, then activation stages (one stage = the nh tiles
+    // of a k-block; about 60 % of what is left, they have the longer latency to hide) and weight tiles
+    const size_t b_stage = static_cast<size_t>(pl.nh) * (pl.pair ? pl.tokh / 2 : pl.tokh) * 128;
+    size_t ring = 0, budget = 0;
+    int bst = 0;
+    pl.raw_segs = 1;
+    // big activation stages leave room for two packed stages (8 k-blocks of int4 ahead), small ones for three
+    for (pl.raw_stages = b_stage >= 24 * 1024 ? 2 : 3; pl.raw_stages >= 1; --pl.raw_stages) {
+        ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
+        if (ring + 1024 + 4 * A_BYTES > 226 * 1024) continue;
+        budget = 226 * 1024 - 1024 - ring;
+        bst = static_cast<int>(budget * 6 / 10 / b_stage);
+        if (bst < 2) bst = 2;
+        if (bst > 8) bst = 8;
+        if (budget >= b_stage * bst + 2 * A_BYTES) break;
     }
-    if (bst > 8) bst = 8;
-    if (bst < 2) return false;
-    ast = static_cast<int>((budget - b_tile * bst) / A_BYTES);
-    if (ast > 6) ast = 6;
+    if (pl.raw_stages < 1) return false;
+    int ast = static_cast<int>((budget - b_stage * bst) / A_BYTES);
+    if (ast > 8) ast = 8;
     pl.b_stages = bst;
     pl.stages = ast;
-    pl.smem = 1024 + ring + b_tile * bst + static_cast<size_t>(ast) * A_BYTES;
+    pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * A_BYTES;
+    if (pl.smem < 1024 + 2 * 64 * BN * 4) pl.smem = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
     *out = pl;
     return true;
 }
 
 template <int QUANT, typename T>
 int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensorMap& wmap, dim3 grid, size_t smem,
-                    cudaStream_t stream)
+                    bool pair, cudaStream_t stream)
 {
-    auto* kern = &gemm_tcgen05_kernel<QUANT, T>;
+    auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, true> : &gemm_tcgen05_kernel<QUANT, T, false>;
     if (smem > 48 * 1024) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
         if (rc) return rc;
     }
-    kern<<<grid, 352, smem, stream>>>(p, xmap, wmap);
+    if (pair) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(352);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const int rcl = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, xmap, wmap), "gemm_tcgen05 pair launch");
+        if (rcl) return rcl;
+    } else {
+        kern<<<grid, 352, smem, stream>>>(p, xmap, wmap);
+    }
     const int rc = check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
     if (rc || p.splits <= 1) return rc;
     // second launch: add the splits' planes and write the output
@@ -625,7 +921,9 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
     // What plan_gemm asks for on a 148-SM part (B200).  On a device where it would split
     // further, the plan falls back to the number of splits the given workspace can hold.
     if (M <= 32 || N < 1 || K < BK || K % BK) return 0;
-    const int64_t tiles = ((N + BN - 1) / BN) * ((M + 511) / 512);
+    GemmPlan pl{};
+    if (!tile_plan(M, N, 0, &pl)) return 0;
+    const int64_t tiles = static_cast<int64_t>(pl.tiles_n) * pl.tiles_m;
     int splits = choose_splits(tiles, static_cast<int>(K / BK), 148, 4.0 * M * N);
     const int64_t total_groups = group_size >= K ? 1 : (K + group_size - 1) / group_size;
     const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
@@ -648,20 +946,22 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.row_bytes = static_cast<int>(a.quant == MNQ_INT4 ? a.K / 2 : a.K);
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
-    p.raw_stages = pl.raw_stages; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
+    p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
     p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+    p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0);
     if (pl.splits > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
 
-    // activations as a [M, K] tensor of 16-bit elements; box = 64 k x tok rows, 128-byte swizzle
+    // activations as a [M, K] tensor of 16-bit elements; box = 64 k x the tokens one CTA loads, 128-byte swizzle
     CUtensorMap xmap;
     const int rc = encode_tensor_map_2d(&xmap, a.x, a.act_dtype == MNQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                         2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
-                                        static_cast<uint64_t>(a.lda) * 2, BK, static_cast<uint32_t>(pl.tokh),
+                                        static_cast<uint64_t>(a.lda) * 2, BK,
+                                        static_cast<uint32_t>(pl.pair ? pl.tokh / 2 : pl.tokh),
                                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     // packed weights as a [N, row_bytes / 4] tensor of 32-bit words; box = 128 bytes x 128 rows,
@@ -671,14 +971,15 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
                                          static_cast<uint64_t>(p.row_bytes) / 4, static_cast<uint64_t>(a.N),
                                          static_cast<uint64_t>(p.row_bytes), 32, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc2) return rc2;
-    dim3 grid(static_cast<unsigned>((a.N + BN - 1) / BN), static_cast<unsigned>(pl.tiles_m),
+    dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m),
               static_cast<unsigned>(pl.splits));
     if (a.quant == MNQ_INT4) {
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, wmap, grid, pl.smem, a.stream);
-        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
     }
-    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, wmap, grid, pl.smem, a.stream);
-    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, a.stream);
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
 }
 
 }  // namespace mnq
+

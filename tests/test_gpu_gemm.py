@@ -58,6 +58,41 @@ def test_gemm_shapes(mn, quant, M, N, K, g, asym, adt, sdt):
     assert bool((chk == 777.0).all()), "kernel wrote outside its [M, N] output block"
 
 
+PAIR_CASES = [
+    # quant, M, N, K, g, act dtype, split
+    ("int4", 64, 256, 256, 128, torch.float16, 1),      # forced pairs on a 64-token tile (32 tokens per CTA)
+    ("int4", 48, 384, 512, 64, torch.float16, 1),       # three 128-row tiles: the last pair has an idle CTA
+    ("int4", 200, 200, 1024, 128, torch.float16, 1),    # ragged N inside the second CTA of the pair
+    ("int4", 512, 512, 1280, 128, torch.float16, 1),    # two accumulators, more k-blocks than stages
+    ("int4", 300, 256, 1024, 128, torch.float16, 3),    # two token tiles, K split
+    ("int8", 160, 512, 768, 768, torch.bfloat16, 1),    # integer tile, scale in the epilogue
+    ("int8", 128, 256, 512, 128, torch.float16, 2),
+]
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("quant,M,N,K,g,adt,split", PAIR_CASES)
+def test_gemm_single_cta_and_cta_pairs(mn, quant, M, N, K, g, adt, split, variant):
+    """The same problems through single-CTA tiles (variant 1) and through clusters of two CTAs
+    sharing each activation tile (variant 2): both match the oracle, and they agree with
+    each other bit for bit (same products, same accumulation order)."""
+    from metal_native import workloads
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             asymmetric=adt == torch.float16, seed=N + K + M)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    t = _gemm_tuning(mn)
+    t.split_k = split
+    t.gemv_variant = variant
+    out = mn._C.dequant_matmul(*d.args(), tuning=t)
+    t.gemv_variant = 3 - variant
+    other = mn._C.dequant_matmul(*d.args(), tuning=t)
+    mn._C.synchronize()
+    assert mn._C.device_status() == 0
+    H.assert_close_to_oracle(out, ref, f"gemm variant {variant} {quant} {M}x{N}x{K}")
+    assert torch.equal(out, other)
+
+
 @pytest.mark.parametrize("split", [1, 2, 3, 5])
 def test_gemm_split_k_is_deterministic_and_reuses_workspace(mn, split):
     from metal_native import workloads
