@@ -304,8 +304,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     const int per_warp = ring_bytes + sc_floats * 8 + 128;
     unsigned char* xs = smem;                                                  // [M][xs_stride]
     float* xsum = reinterpret_cast<float*>(smem + xsum_off);                   // [segs][NT*8]
-    // the same sums as exact 2^-24 fixed point: integer adds commute, so the shared-memory
-    // atomics below give the same bits whatever order the threads arrive in
+    // the same sums in 2^-24 fixed point: integer adds commute, so the shared-memory atomics
+    // below give the same bits whatever order the warps arrive in
     unsigned long long* xsumi = reinterpret_cast<unsigned long long*>(smem + xsumi_off);
     unsigned char* my = smem + warp0_off + warp * per_warp;
     unsigned char* ring = my;                                                  // [stages][16][CH]
@@ -352,7 +352,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     if (CONVERT_X && tid == 0) x_max_bits = 0u;
     float x_down = 1.f, x_up = 1.f;       // 2^-x_shift and 2^x_shift
 
-    constexpr int SCB = 8;                         // scale pairs in flight per lane (32 groups per row)
+    constexpr int SCB = 16;                        // scale entries in flight per lane (one batch = 32 groups of each of 16 rows)
     constexpr int XB = (NT == 1) ? 2 : 4;          // activation loads in flight per thread
     const int blocks_per_row = nsteps * (STEP / 8);
     const int x_count = p.M * blocks_per_row;
@@ -377,7 +377,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             }
         }
     };
+    // Called by all 32 lanes of a warp together; lanes without a block pass m = -1.
     auto store_x_block = [&](uint32_t (&v)[4], int m, int b, int k) {
+        const bool valid = m >= 0;
+        if (!valid) { v[0] = v[1] = v[2] = v[3] = 0u; m = 0; b = 0; k = k_begin; }
         if (CONVERT_X) {   // bf16 -> fp16, times 2^-x_shift (exact unless the result is subnormal)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -386,15 +389,32 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 v[e] = h2_as_u32(__floats2half2_rn(lo, hi));
             }
         }
-        long long sum = 0;   // exact: every fp16 value is an integer multiple of 2^-24
+        // Sum of the block's eight staged values, in a fixed order.
+        float sum = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float2 f = __half22float2(u32_as_h2(v[e]));
-            sum += __float2ll_rn(f.x * 16777216.f) + __float2ll_rn(f.y * 16777216.f);
+            sum += f.x;
+            sum += f.y;
         }
         const int sg = (p.group_size == INT_MAX) ? 0
                      : (p.group_shift >= 0 ? (k >> p.group_shift) : k / p.group_size) - seg0;
-        atomicAdd(&xsumi[sg * (NT * 8) + m], static_cast<unsigned long long>(sum));
+        // Lanes hold consecutive 8-blocks, so the blocks of one (group, token) sit in a run of
+        // adjacent lanes: the run is added up with shuffles (a fixed tree, so the same bits every
+        // time) and its first lane adds the total to the group's sum in shared memory.  Several
+        // warps may contribute to one group; their totals are rounded to a 2^-24 grid and added
+        // as 64-bit integers, which commute, so the result does not depend on arrival order.
+        const int key = valid ? sg * (NT * 8) + m : -1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float other = __shfl_down_sync(0xffffffffu, sum, d);
+            const int okey = __shfl_down_sync(0xffffffffu, key, d);
+            if (lane + d < 32 && okey == key) sum += other;
+        }
+        const int pkey = __shfl_up_sync(0xffffffffu, key, 1);
+        if (valid && (lane == 0 || pkey != key))
+            atomicAdd(&xsumi[key], static_cast<unsigned long long>(__float2ll_rn(sum * 16777216.f)));
+        if (!valid) return;
         int pos;
         uint4 o;
         if (QUANT == MNQ_INT4) {
@@ -419,66 +439,60 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
         *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
     };
-    // Scales / zeros of one row block: lane = (row, half); each lane owns segs/2 consecutive
-    // groups of its row, fetched as 32-bit pairs where the address allows.  `batch` selects
-    // which SCB pairs of the lane's share (one batch covers 4*SCB groups per row).
-    const int sc_row = lane >> 1;
-    const int sc_col0 = (lane & 1) * (p.segs >> 1);
-    auto load_scale_pairs = [&](int rbi, int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
-        const int n = (rb_first + rbi) * 16 + sc_row;
-        const size_t e0 = (size_t)n * p.G + seg0 + sc_col0;
-        const bool row_ok = (rbi < nrb) && (n < p.N);
-        const bool even = ((e0 & 1) == 0);
+    // Scales / zeros of one row block (16 rows x segs groups): entry e = row * segs + group goes
+    // to lane e % 32, so a warp-wide load covers 32 consecutive entries, i.e. a contiguous run of
+    // groups of one or two rows (a cache line or two per load instead of one per lane).  A batch
+    // is SCB entries per lane; nothing in the load phase uses a loaded value, so a batch's loads
+    // are all in flight together.
+    const int sc_entries = 16 * p.segs;
+    const int sc_q32 = 32 / p.segs, sc_r32 = 32 - sc_q32 * p.segs;   // (row, group) step of 32 entries
+    auto load_scale_batch = [&](int rbi, int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
+        const int e0 = batch * SCB * 32 + lane;
+        int row = e0 / p.segs;
+        int g = e0 - row * p.segs;
 #pragma unroll
         for (int u = 0; u < SCB; ++u) {
-            const int c = (batch * SCB + u) * 2;           // column inside the lane's share
-            const int g = seg0 + sc_col0 + c;
-            const bool in_share = c < (p.segs >> 1);
-            const bool ok0 = row_ok && in_share && g < p.G;
-            const bool ok1 = row_ok && in_share && g + 1 < p.G;
-            uint32_t sv = 0, zv = 0;
-            if (ok1 && even) {
-                sv = __ldg(reinterpret_cast<const uint32_t*>(sc16 + e0 + c));
-                if (has_zero) zv = __ldg(reinterpret_cast<const uint32_t*>(zr16 + e0 + c));
-            } else if (ok0) {
-                sv = __ldg(sc16 + e0 + c);
-                if (has_zero) zv = __ldg(zr16 + e0 + c);
-                if (ok1) {
-                    sv |= (uint32_t)__ldg(sc16 + e0 + c + 1) << 16;
-                    if (has_zero) zv |= (uint32_t)__ldg(zr16 + e0 + c + 1) << 16;
-                }
+            const int n = (rb_first + rbi) * 16 + row;
+            sp[u] = 0; zp[u] = 0;
+            if (rbi < nrb && row < 16 && n < p.N && seg0 + g < p.G) {
+                const size_t at = (size_t)n * p.G + seg0 + g;
+                sp[u] = __ldg(sc16 + at);
+                if (has_zero) zp[u] = __ldg(zr16 + at);
             }
-            sp[u] = sv; zp[u] = zv;
+            row += sc_q32;
+            g += sc_r32;
+            if (g >= p.segs) { g -= p.segs; ++row; }
         }
     };
-    auto fold_scale_pairs = [&](int rbi, int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
-        float* dS = sS + (rbi * 16 + sc_row) * p.segs + sc_col0;
-        float* dZ = sZ + (rbi * 16 + sc_row) * p.segs + sc_col0;
+    auto fold_scale_batch = [&](int rbi, int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
 #pragma unroll
         for (int u = 0; u < SCB; ++u) {
-            const int c = (batch * SCB + u) * 2;
-            if (rbi < nrb && c < (p.segs >> 1)) {
-                float s0, s1, z0, z1;
+            const int e = (batch * SCB + u) * 32 + lane;
+            if (rbi < nrb && e < sc_entries) {
+                float s0, z0;
                 if (p.scale_dtype == MNQ_BF16) {
-                    s0 = __uint_as_float(sp[u] << 16); s1 = __uint_as_float(sp[u] & 0xFFFF0000u);
-                    z0 = __uint_as_float(zp[u] << 16); z1 = __uint_as_float(zp[u] & 0xFFFF0000u);
+                    s0 = __uint_as_float(sp[u] << 16);
+                    z0 = __uint_as_float(zp[u] << 16);
                 } else {
-                    const float2 sf = __half22float2(u32_as_h2(sp[u]));
-                    const float2 zf = __half22float2(u32_as_h2(zp[u]));
-                    s0 = sf.x; s1 = sf.y; z0 = zf.x; z1 = zf.y;
+                    s0 = __half2float(__ushort_as_half((unsigned short)sp[u]));
+                    z0 = __half2float(__ushort_as_half((unsigned short)zp[u]));
                 }
-                *reinterpret_cast<float2*>(dS + c) =
-                    make_float2(s0 * Enc<QUANT, MT>::inv_alpha, s1 * Enc<QUANT, MT>::inv_alpha);
-                *reinterpret_cast<float2*>(dZ + c) =
-                    make_float2(fmaf(Enc<QUANT, MT>::offset, s0, z0), fmaf(Enc<QUANT, MT>::offset, s1, z1));
+                sS[rbi * sc_entries + e] = s0 * Enc<QUANT, MT>::inv_alpha;
+                sZ[rbi * sc_entries + e] = fmaf(Enc<QUANT, MT>::offset, s0, z0);
             }
         }
     };
-    const int sc_batches = ((p.segs >> 2) + SCB - 1) / SCB;   // pairs per lane = segs / 4
+    const int sc_batches = (sc_entries + 32 * SCB - 1) / (32 * SCB);
 
     // first batch of small loads (the only one for the benchmark shapes)
+    // With a programmatic dependent launch this CTA may have started while the previous kernel
+    // in the stream was still running.  Everything above touched only this CTA's shared memory;
+    // every global read below (activations, but also weights and scales, which an earlier
+    // kernel in the stream may have produced) comes after that kernel and its writes completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     uint32_t sreg[SCB], zreg[SCB];
-    load_scale_pairs(0, 0, sreg, zreg);
+    load_scale_batch(0, 0, sreg, zreg);
     uint32_t xv[XB][4];
     int xm[XB], xb[XB], xk[XB];
 #pragma unroll
@@ -501,12 +515,17 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mx = max(mx, max(xv[u][e] & 0x7FFFu, (xv[u][e] >> 16) & 0x7FFFu));
             }
-        for (int i = XB * blockDim.x + tid; i < x_count; i += blockDim.x) {   // blocks beyond the first batch
-            uint32_t t4[4];
+        // blocks beyond the first batch, eight loads in flight per thread (a clamped index
+        // re-reads the last block, which leaves the maximum unchanged)
+        for (int i0 = XB * blockDim.x + tid; i0 < x_count; i0 += 8 * blockDim.x) {
+            uint32_t t4[8][4];
             int a, b, c;
-            load_x_block(i, t4, a, b, c);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) mx = max(mx, max(t4[e] & 0x7FFFu, (t4[e] >> 16) & 0x7FFFu));
+            for (int u = 0; u < 8; ++u) load_x_block(min(i0 + u * (int)blockDim.x, x_count - 1), t4[u], a, b, c);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx = max(mx, max(t4[u][e] & 0x7FFFu, (t4[u][e] >> 16) & 0x7FFFu));
         }
         mx = __reduce_max_sync(0xffffffffu, mx);
         if (lane == 0 && mx) atomicMax(&x_max_bits, mx);
@@ -519,31 +538,39 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
 
     // consume the small loads
-    fold_scale_pairs(0, 0, sreg, zreg);
+    fold_scale_batch(0, 0, sreg, zreg);
 #pragma unroll
     for (int u = 0; u < XB; ++u)
-        if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
+        if (__any_sync(0xffffffffu, xm[u] >= 0)) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     // whatever did not fit in the first batch (several row blocks per warp, many groups, M > 8)
     for (int rbi = 0; rbi < nrb; ++rbi)
         for (int batch = (rbi == 0 ? 1 : 0); batch < sc_batches; ++batch) {
-            load_scale_pairs(rbi, batch, sreg, zreg);
-            fold_scale_pairs(rbi, batch, sreg, zreg);
+            load_scale_batch(rbi, batch, sreg, zreg);
+            fold_scale_batch(rbi, batch, sreg, zreg);
         }
-    for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB * blockDim.x) {
+    {
+        constexpr int XB2 = 8;   // deeper batches for the bulk of a many-token activation block
+        for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB2 * blockDim.x) {
+            uint32_t yv[XB2][4];
+            int ym[XB2], yb[XB2], yk[XB2];
 #pragma unroll
-        for (int u = 0; u < XB; ++u) {
-            const int i = i0 + tid + u * blockDim.x;
-            xm[u] = -1;
-            if (i < x_count) load_x_block(i, xv[u], xm[u], xb[u], xk[u]);
+            for (int u = 0; u < XB2; ++u) {
+                const int i = i0 + tid + u * blockDim.x;
+                load_x_block(min(i, x_count - 1), yv[u], ym[u], yb[u], yk[u]);
+                if (i >= x_count) ym[u] = -1;
+            }
+#pragma unroll
+            for (int u = 0; u < XB2; ++u)
+                if (__any_sync(0xffffffffu, ym[u] >= 0)) store_x_block(yv[u], ym[u], yb[u], yk[u]);
         }
-#pragma unroll
-        for (int u = 0; u < XB; ++u)
-            if (xm[u] >= 0) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     }
     __syncthreads();
     for (int i = tid; i < p.segs * NT * 8; i += blockDim.x)
         xsum[i] = static_cast<float>(static_cast<long long>(xsumi[i])) * (1.f / 16777216.f);
     __syncthreads();
+
+    // the next kernel in the stream may start its own prologue now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- main loop ----------------------------------------------------------------------------
     // this lane's position inside a staged activation row: 16 bytes per 8-block at lane t (int4),
@@ -680,19 +707,25 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         arrival = __shfl_sync(0xffffffffu, arrival, 0);
         if (arrival != (unsigned int)(p.num_chunks - 1)) continue;
         __threadfence();
+        // Last chunk to arrive: add the chunks in index order (deterministic).  One output per
+        // lane and pass, its loads issued together (indices past the last chunk are clamped and
+        // their values dropped), so the whole reduction costs one round trip to L2 per pass.
+        for (int o = lane; o < 16 * p.M; o += 32) {
+            const int m = o >> 4;
+            const int n = rb * 16 + (o & 15);
+            const float* src = p.partial + (size_t)m * p.N + min(n, p.N - 1);
+            const size_t plane = (size_t)p.M * p.N;
+            float v = 0.f;
+            for (int c0 = 0; c0 < p.num_chunks; c0 += 8) {
+                float part[8];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+                for (int c = 0; c < 8; ++c) part[c] = __ldcg(src + (size_t)min(c0 + c, p.num_chunks - 1) * plane);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int m = nt * 8 + 2 * t + (i & 1);
-                const int n = (i & 2) ? n1 : n0;
-                if (m < p.M && n < p.N) {
-                    float v = 0.f;
-                    for (int c = 0; c < p.num_chunks; ++c)
-                        v += __ldcg(&p.partial[((size_t)c * p.M + m) * p.N + n]);
-                    out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(v);
-                }
+                for (int c = 0; c < 8; ++c)
+                    if (c0 + c < p.num_chunks) v += part[c];
             }
+            if (n < p.N) out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(v);
+        }
         __syncwarp();
         if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
     }
@@ -829,8 +862,20 @@ int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, dim3 grid,
             "cudaFuncSetAttribute(gemv_stream)");
         if (rc) return rc;
     }
-    kern<<<grid, threads, smem, stream>>>(p, wmap);
-    return check_cuda(cudaGetLastError(), "gemv_stream launch");
+    // Programmatic dependent launch: the CTAs of this kernel may be scheduled while the previous
+    // kernel in the stream is still draining (that hides the launch gap and the cold start);
+    // they touch nothing but their own shared memory before `griddepcontrol.wait`.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, wmap), "gemv_stream launch");
 }
 
 template <int QUANT, typename T>
