@@ -465,6 +465,11 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
     bool failed = false;
+    // Launched programmatically dependent: the set-up above may have run while the previous
+    // kernel in the stream was finishing; nothing global is read or written before it is done.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // and the next kernel in the stream may begin its own set-up
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- activation tiles by TMA ----------------
@@ -696,6 +701,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, T* __restrict__ out, int M,
                                                             int N, int64_t ldc, int splits)
 {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the planes are the previous kernel's output
     const size_t plane = (size_t)M * N;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     if (VEC) {
@@ -861,23 +867,24 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
         if (rc) return rc;
     }
-    if (pair) {
+    {
+        // programmatic dependent launch (see the kernel); CTA pairs are clusters of two along x
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(352);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        const int rcl = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, xmap, wmap), "gemm_tcgen05 pair launch");
+        cfg.numAttrs = pair ? 2 : 1;
+        const int rcl = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, xmap, wmap), "gemm_tcgen05 launch");
         if (rcl) return rcl;
-    } else {
-        kern<<<grid, 352, smem, stream>>>(p, xmap, wmap);
     }
     const int rc = check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
     if (rc || p.splits <= 1) return rc;
@@ -887,11 +894,18 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     const size_t work = vec ? (size_t)p.M * p.N / 8 : (size_t)p.M * p.N;
     size_t blocks = (work + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (vec)
-        splitk_reduce_kernel<T, true><<<(unsigned)blocks, 256, 0, stream>>>(p.partial, out, p.M, p.N, p.ldc, p.splits);
-    else
-        splitk_reduce_kernel<T, false><<<(unsigned)blocks, 256, 0, stream>>>(p.partial, out, p.M, p.N, p.ldc, p.splits);
-    return check_cuda(cudaGetLastError(), "splitk_reduce launch");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* partial = p.partial;
+    auto* red = vec ? &splitk_reduce_kernel<T, true> : &splitk_reduce_kernel<T, false>;
+    return check_cuda(cudaLaunchKernelEx(&cfg, red, partial, out, p.M, p.N, p.ldc, p.splits), "splitk_reduce launch");
 }
 
 }  // namespace
