@@ -52,7 +52,10 @@ FALLBACK_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (one capture per kernel and workload)
 TRAFFIC = {
-    "qwen7b-decode:qwen2.5-7b.gate_up": 72_213_504 + 945_920,   # profiles/gemv_stream_qwen7b_gate_up.md
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
+    # profiles/gemv_stream_qwen7b_gate_up.md and profiles/gemm_tcgen05_qwen7b_prefill_up.md
+    "qwen7b-decode:qwen2.5-7b.gate_up": 72_224_256 + 705_792,
+    "qwen7b-prefill:qwen2.5-7b.up.prefill": 39_830_016 + 378_368,
 }
 
 
@@ -70,6 +73,8 @@ def parse_args():
                     help="auto | qwen7b-decode | llama8b-decode-m{4,16,32} | qwen7b-prefill | "
                          "llama70b-int8-m{1,64}")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: all-gather inside the decode kernel (peer stores) or NCCL after it")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     return ap.parse_args()
 
@@ -286,15 +291,39 @@ def run_ours(args):
                            for i, L in enumerate(layers_cpu)])
     outs = [torch.empty((L.M, L.N), dtype=L.x.dtype, device=dev) for L in layers_cpu]
     gathered = None
+    fused = None      # per layer: PeerGather when the all-gather runs inside the decode kernel
+    collective = None
     if world > 1:
         from metal_native import sharded
         gathered = [sharded.GatherBuffer(L.M, L.N, world, L.x.dtype, dev) for L in layers_cpu]
+        want_fused = args.gather != "nccl" and all(
+            L.M <= 32 and _C.select_path(L.M, L.N, L.K, L.group_size, L.quant_type, L.x.dtype,
+                                         zeros=L.zeros is not None) == "gemv" for L in layers_cpu)
+        ok = torch.tensor([1 if want_fused else 0], device=dev)
+        if want_fused:
+            try:
+                fused = [sharded.PeerGather(L.M, L.N, world, L.x.dtype, dev) for L in layers_cpu]
+            except Exception as e:   # no peer-mapped symmetric memory on this box
+                print(f"[bench] rank {rank}: fused gather unavailable ({type(e).__name__}: {e})", file=sys.stderr)
+                ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)     # all ranks take the same route
+        if int(ok.item()) == 0:
+            if args.gather == "fused":
+                raise SystemExit("--gather fused: not available for this workload / on this box")
+            fused = None
+        collective = ("peer stores from the decode kernel's epilogue + arrival flags (one kernel per projection)"
+                      if fused else "NCCL all_gather_into_tensor after each projection")
+
+    def run_layer(j, L, x):
+        """One projection; returns the full [M, N] result on this rank."""
+        if fused is not None:
+            return fused[j].matmul(x, L.wq, L.scales, L.zeros, L.group_size, L.quant_type)
+        o = _C.dequant_matmul(x, L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs[j])
+        return gathered[j].all_gather(o) if world > 1 else o
 
     def step(i):
         for j, L in enumerate(dev_layers[i % copies]):
-            _C.dequant_matmul(L.x, L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs[j])
-            if world > 1:
-                gathered[j].all_gather(outs[j])
+            run_layer(j, L, L.x)
 
     def launches(L):
         # one kernel per projection; the tensor-core path with K split adds its reduce kernel
@@ -392,9 +421,7 @@ def run_ours(args):
     def e2e_step(i):
         for j, L in enumerate(dev_layers[i % copies]):
             xs_dev[j].copy_(xs_host[j], non_blocking=True)
-            o = _C.dequant_matmul(xs_dev[j], L.wq, L.scales, L.zeros, L.group_size, L.quant_type)
-            if world > 1:
-                o = gathered[j].all_gather(o)
+            o = run_layer(j, L, xs_dev[j])
             outs_host[j].copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -418,7 +445,8 @@ def run_ours(args):
            "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in xs_host),
            "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs_host),
            "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-           "call": "metal_native._C.dequant_matmul per projection, eager; weights resident"}
+           "call": ("metal_native.sharded.PeerGather.matmul per projection, eager; weights resident" if fused
+                    else "metal_native._C.dequant_matmul per projection, eager; weights resident")}
 
     # ---- keep the load on for the clock sampler, then read it ----------------------------
     # every rank replays the same number of times (the graph may hold collectives): about one
@@ -451,6 +479,7 @@ def run_ours(args):
                        "l2_policy": f"inputs larger than L2: {copies} weight copies x {wbytes_rank / 1e6:.1f} MB "
                                     f"rotate, L2 = {l2 / 1e6:.0f} MB",
                        "launch": f"{args.steps} steps replayed from one CUDA graph",
+                       "collective": collective,
                        "weight_bytes_per_step": total_wbytes,
                        "frac_of_measured_hbm": None if prefill else value / (peak * world),
                        "frac_of_nominal_8TBs": None if prefill else value / (8000.0 * world)},

@@ -184,6 +184,36 @@ MNQ_API int mnq_dequant_matmul_static(const void* activations, const void* weigh
                               int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
                               int32_t scale_dtype, void* stream);
 
+/* Column-sharded fused operator with the all-gather folded into the kernel.  No counterpart in
+ * the reference (it drives one device); this is the N-sharded form of mnq_dequant_matmul for
+ * `world` GPUs of one node, one process per GPU, each holding rows [n_offset, n_offset + N_local)
+ * of the weights, scales and zeros and the whole activation block.
+ *
+ * out_peers and flag_peers are HOST arrays of `world` device pointers, the same on every rank:
+ * out_peers[g] is rank g's gathered output [M, ldc] (ldc >= the full N) and flag_peers[g] points to
+ * MNQ_GATHER_FLAG_WORDS 32-bit words on rank g, zero before the first call and never touched by
+ * the caller afterwards; all of them must be addressable from this GPU (peer-mapped, e.g. torch
+ * symmetric memory or cudaIpc handles).  The kernel stores every output element of this rank's
+ * slice into all `world` buffers (after each rank has announced, through the flag words, that it
+ * has begun the same call and so no longer reads the previous result), and its last CTA
+ * publishes the call's number in every rank's flag block and waits, with a bounded spin, until
+ * every rank has done the same here: when the call's work completes on `stream`, the gathered
+ * [M, N] output is complete in out_peers[rank].  A rank that never shows up makes the waits give
+ * up (bit 2 of mnq_device_status); they never hang the GPU.
+ *
+ * Rules for the caller: every rank makes the same sequence of calls on a given set of buffers;
+ * whatever reads the gathered output is enqueued on `stream` before this rank's next call on it.
+ * The call numbers live in the flag blocks, so the calls may be captured in a CUDA graph and
+ * replayed.  Only problems the streaming decode kernel takes (M <= 32 among others) are accepted;
+ * others return MNQ_NOT_IMPLEMENTED and are gathered with a collective instead. */
+#define MNQ_GATHER_FLAG_WORDS 32
+MNQ_API int mnq_dequant_matmul_gather(const void* activations, const void* weights_packed, const void* scales,
+                                      const void* zeros, void* const* out_peers, uint32_t* const* flag_peers,
+                                      int32_t world, int32_t rank, int64_t n_offset, int64_t M,
+                                      int64_t N_local, int64_t K, int64_t lda, int64_t ldc, int32_t group_size,
+                                      int32_t quant_type, int32_t act_dtype, int32_t scale_dtype, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
 /* Library version, "major.minor.patch". */
 MNQ_API const char* mnq_version(void);
 

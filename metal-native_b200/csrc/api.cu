@@ -134,6 +134,7 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
     a.workspace = workspace; a.workspace_bytes = workspace ? workspace_bytes : 0;
     a.stream = static_cast<cudaStream_t>(stream);
     a.sm_count = 148;
+    a.gather = GatherArgs{};
 }
 
 int choose_path(const MatmulArgs& a)
@@ -245,6 +246,47 @@ int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, c
         case MNQ_PATH_GENERIC: return launch_generic(a);
         default: return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: unknown path %d", path);
     }
+}
+
+int mnq_dequant_matmul_gather(const void* activations, const void* weights_packed, const void* scales,
+                              const void* zeros, void* const* out_peers, uint32_t* const* flag_peers,
+                              int32_t world, int32_t rank, int64_t n_offset, int64_t M,
+                              int64_t N_local, int64_t K, int64_t lda, int64_t ldc, int32_t group_size,
+                              int32_t quant_type, int32_t act_dtype, int32_t scale_dtype, void* workspace,
+                              size_t workspace_bytes, void* stream)
+{
+    if (world < 1 || world > kMaxGatherRanks || rank < 0 || rank >= world)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_gather: world must be 1..%d and 0 <= rank < world", kMaxGatherRanks);
+    if (!out_peers || !flag_peers) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_gather: null pointer table");
+    for (int g = 0; g < world; ++g)
+        if (!out_peers[g] || !flag_peers[g])
+            return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_gather: null buffer for rank %d", g);
+    if (n_offset < 0 || n_offset + N_local > ldc)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_gather: columns [n_offset, n_offset + N_local) must lie inside ldc");
+    int rc = validate_matmul(activations, weights_packed, scales, out_peers[rank], true, M, N_local, K, lda, N_local,
+                             group_size, quant_type, act_dtype, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N_local == 0 || K == 0)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_gather: empty problems are not gathered (every rank must launch)");
+
+    MatmulArgs a;
+    fill_args(a, activations, weights_packed, scales, zeros, out_peers[rank], M, N_local, K, lda, ldc, group_size,
+              quant_type, act_dtype, scale_dtype, workspace, workspace_bytes, stream);
+    rc = current_sm_count(&a.sm_count);
+    if (rc) return rc;
+    a.gather.world = world;
+    a.gather.rank = rank;
+    a.gather.n_offset = n_offset;
+    for (int g = 0; g < world; ++g) {
+        a.gather.out_peer[g] = out_peers[g];
+        a.gather.flag_peer[g] = flag_peers[g];
+    }
+    // the peer stores live in the streaming decode kernel's epilogue
+    if (M > 32 || !gemv_stream_supported(a, nullptr))
+        return fail(MNQ_NOT_IMPLEMENTED,
+                    "dequant_matmul_gather: only problems the streaming decode kernel takes (M <= 32, rows a multiple "
+                    "of 16 bytes, group_size a multiple of the k step); gather other shapes with a collective");
+    return launch_gemv_stream(a, nullptr);
 }
 
 int mnq_dequant_matmul(const void* activations, const void* weights_packed, const void* scales,

@@ -80,6 +80,7 @@ struct StreamParams {
     int rbw;              // row blocks per warp
     int stages;
     int row_blocks;       // ceil(N / 16)
+    GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -491,6 +492,21 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // kernel in the stream may have produced) comes after that kernel and its writes completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    // Sharded call: number of this call (the same on every rank), and the announcement that this
+    // rank has begun it: whatever read its gathered output of the previous call came earlier
+    // in the stream, so peers may overwrite that buffer from now on.
+    unsigned int call_no = 0;
+    bool peers_ready = false;
+    if (p.gather.world > 0) {
+        unsigned int* mine = p.gather.flag_peer[p.gather.rank];
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(call_no) : "l"(mine + kGatherEpochWord) : "memory");
+        call_no += 1u;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
+            for (int g = 0; g < p.gather.world; ++g)
+                asm volatile("st.release.sys.global.u32 [%0], %1;"
+                             ::"l"(p.gather.flag_peer[g] + kGatherReadyBase + p.gather.rank), "r"(call_no) : "memory");
+    }
+
     uint32_t sreg[SCB], zreg[SCB];
     load_scale_batch(0, 0, sreg, zreg);
     uint32_t xv[XB][4];
@@ -581,6 +597,33 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     for (int nt = 0; nt < NT; ++nt)
         xrow[nt] = xs + (size_t)min(nt * 8 + r, p.M - 1) * p.xs_stride + x_lane_off;
     T* out = static_cast<T*>(p.out);
+    bool gather_failed = false;
+    // Plain call: one store.  Sharded call: the same element goes to every rank's gathered buffer
+    // (peer-mapped device pointers; the local rank is one of them).
+    auto store_out = [&](int m, int n, T v) {
+        if (p.gather.world == 0) {
+            out[(size_t)m * p.ldc + n] = v;
+        } else {
+            if (!peers_ready) {   // once per thread: every rank has begun this call (bounded wait)
+                const unsigned int* mine = p.gather.flag_peer[p.gather.rank] + kGatherReadyBase;
+                bool ok = true;
+                for (int g = 0; g < p.gather.world && ok; ++g) {
+                    bool in = false;
+                    for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
+                        unsigned int r;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(r) : "l"(mine + g) : "memory");
+                        in = static_cast<int>(r - call_no) >= 0;
+                        if (!in) __nanosleep(100);
+                    }
+                    ok = in;
+                }
+                if (!ok) { gather_failed = true; return; }
+                peers_ready = true;
+            }
+            for (int g = 0; g < p.gather.world; ++g)
+                static_cast<T*>(p.gather.out_peer[g])[(size_t)m * p.ldc + p.gather.n_offset + n] = v;
+        }
+    };
     bool gave_up = false;
 
     int stage = 0;
@@ -687,7 +730,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     const int m = nt * 8 + 2 * t + (i & 1);
                     const int n = (i & 2) ? n1 : n0;
                     if (m < p.M && n < p.N)
-                        out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]);
+                        store_out(m, n, F16Traits<T>::from_float(CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]));
                 }
             continue;
         }
@@ -724,10 +767,44 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 for (int c = 0; c < 8; ++c)
                     if (c0 + c < p.num_chunks) v += part[c];
             }
-            if (n < p.N) out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(v);
+            if (n < p.N) store_out(m, n, F16Traits<T>::from_float(v));
         }
         __syncwarp();
         if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
+    }
+
+    if (p.gather.world > 0) {
+        // Every thread's peer stores become visible system-wide, then the CTA reports in; the last
+        // CTA of the grid tells every rank that this rank's slice of this call is complete and
+        // waits (bounded) until every rank has said the same here, so that the kernel's completion
+        // means "the gathered output is complete on this rank".
+        if (gather_failed) atomicOr(&g_device_status, 4u);
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned int* mine = p.gather.flag_peer[p.gather.rank];
+            const unsigned int total = gridDim.x * gridDim.y;
+            if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
+                mine[kGatherCounterWord] = 0u;   // ready for the next call
+                __threadfence_system();
+                for (int g = 0; g < p.gather.world; ++g)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
+                                 "r"(call_no) : "memory");
+                bool all_in = true;
+                for (int src = 0; src < p.gather.world && all_in; ++src) {
+                    bool in = false;
+                    for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
+                        in = static_cast<int>(v - call_no) >= 0;
+                        if (!in) __nanosleep(200);
+                    }
+                    all_in = in;
+                }
+                if (!all_in) atomicOr(&g_device_status, 4u);   // a rank never reported: give up, do not hang
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine + kGatherEpochWord), "r"(call_no) : "memory");
+            }
+        }
     }
 
     if (gave_up) {
@@ -939,6 +1016,7 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.x_vec_ok = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && (a.lda % 8 == 0);
     p.rbw = pl.rbw; p.stages = pl.stages;
     p.row_blocks = static_cast<int>((a.N + 15) / 16);
+    p.gather = a.gather;
     if (pl.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);

@@ -196,6 +196,27 @@ __device__ __forceinline__ void mma_16x8x16<__nv_bfloat16>(float (&d)[4], uint32
 // ---------------------------------------------------------------------------
 // Launch-argument bundles
 // ---------------------------------------------------------------------------
+// Column-sharded call: this rank's [M, N] result is stored into the gathered [M, ldc] buffer of
+// every rank at column n_offset, through peer-mapped pointers, and the kernel returns only when
+// every rank's slice has arrived in this rank's buffer.  Each rank owns a block of
+// kGatherFlagWords 32-bit words, zero before the first call, written by its peers:
+//   [0, 8)   arrival: word s = number of the last call whose slice from rank s is complete here
+//   [8]      CTA counter of the running call (local use)      [9] number of completed calls (local)
+//   [16, 24) ready: word s = number of the call rank s has begun, i.e. rank s no longer reads
+//            the previous call's gathered output and its buffer may be overwritten
+constexpr int kMaxGatherRanks = 8;
+constexpr int kGatherFlagWords = 32;
+constexpr int kGatherCounterWord = 8;
+constexpr int kGatherEpochWord = 9;
+constexpr int kGatherReadyBase = 16;
+struct GatherArgs {
+    int32_t world;                         // 0: plain call
+    int32_t rank;
+    int64_t n_offset;
+    void* out_peer[kMaxGatherRanks];       // gathered output buffer of each rank
+    uint32_t* flag_peer[kMaxGatherRanks];  // kGatherFlagWords words on each rank
+};
+
 struct MatmulArgs {
     const void* x;        // [M, K] act dtype
     const void* wq;       // packed weights
@@ -212,6 +233,7 @@ struct MatmulArgs {
     size_t workspace_bytes;
     cudaStream_t stream;
     int32_t sm_count;
+    GatherArgs gather;    // world == 0 unless called through mnq_dequant_matmul_gather
 };
 
 // Split-K workspace layout, the same for every kernel and every problem shape: arrival

@@ -71,6 +71,9 @@ def _load() -> ctypes.CDLL:
     L.mnq_dequantize_flat.argtypes = [vp, vp, vp, i64, i32, i32, vp]
     L.mnq_device_status.restype = ctypes.c_int
     L.mnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), i32]
+    L.mnq_dequant_matmul_gather.restype = ctypes.c_int
+    L.mnq_dequant_matmul_gather.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64,
+                                            i64, i64, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
     return L
 
 
@@ -231,6 +234,34 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
     return out
 
 
+GATHER_FLAG_WORDS = 32   # MNQ_GATHER_FLAG_WORDS of include/mnq.h
+
+
+def dequant_matmul_gather(activations, weights_shard, scales_shard, zeros_shard, group_size, quant_type,
+                          out_ptrs, flag_ptrs, rank, n_offset, ldc):
+    """Column-sharded fused operator with the all-gather folded into the kernel
+    (``mnq_dequant_matmul_gather``): this rank's [M, N_local] slice is stored at column
+    ``n_offset`` of every rank's gathered [M, ldc] buffer (``out_ptrs``: one device address per
+    rank, peer-mapped) and the call completes on the current stream only when every rank's
+    slice has arrived here.  ``flag_ptrs``: one address per rank of GATHER_FLAG_WORDS zeroed
+    int32 words.  See metal_native.sharded.PeerGather for the buffers."""
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_shard, scales_shard, zeros_shard, group_size,
+                                              quant_type)
+    dev = x.device
+    world = len(out_ptrs)
+    if len(flag_ptrs) != world:
+        raise _invalid("dequant_matmul_gather: out_ptrs and flag_ptrs must have one entry per rank")
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nbytes = _lib.mnq_workspace_bytes(M, N, K, g, q)
+    ws = _workspace(dev, stream, nbytes)
+    outs = (ctypes.c_void_p * world)(*[int(v) for v in out_ptrs])
+    flags = (ctypes.c_void_p * world)(*[int(v) for v in flag_ptrs])
+    _check(_lib.mnq_dequant_matmul_gather(
+        x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, outs, flags, world,
+        int(rank), int(n_offset), M, N, K, lda, int(ldc), g, q, _DT[x.dtype], _DT[s.dtype],
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream))
+
+
 def select_path(M, N, K, group_size, quant_type, dtype=torch.float16, lda=None, alignment=256,
                 zeros=True) -> str:
     """Kernel family the library picks for a problem: 'gemv', 'gemm' or 'generic'.
@@ -337,4 +368,4 @@ def exported_symbols() -> list[str]:
     """Entry points declared in include/mnq.h that this module binds."""
     return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
-            "mnq_dequantize_flat", "mnq_device_status"]
+            "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather"]

@@ -3,10 +3,13 @@
 The reference is single-GPU; this is the multi-GPU form the B200 build adds.  Rank r of G
 holds rows [r*N/G, (r+1)*N/G) of weights_packed, scales and zeros -- contiguous row blocks
 of the reference layout, so sharding is a view, not a re-pack.  Activations are replicated.
-Each rank computes out[:, slice] with the ordinary operator and one all-gather along N
-(NCCL over NVLink through torch.distributed) gives every rank the full [M, N].
+Each rank computes out[:, slice]; the full [M, N] reaches every rank either by one all-gather
+along N (NCCL over NVLink through torch.distributed: GatherBuffer) or, for decode-sized
+problems, inside the kernel itself, whose epilogue stores the slice into every rank's output
+buffer over NVLink (PeerGather, peer-mapped symmetric memory).
 
-One process per GPU (torchrun).  Nothing here reads another GPU's memory directly.
+One process per GPU (torchrun).  Nothing here *reads* another GPU's memory: peers are only
+written to, and polled flags live in local memory.
 """
 from __future__ import annotations
 
@@ -65,3 +68,38 @@ def dequant_matmul_sharded(activations, weights_shard, scales_shard, zeros_shard
     if gather is None:
         gather = GatherBuffer(local.shape[0], local.shape[1], world, local.dtype, local.device, group)
     return gather.all_gather(local)
+
+
+class PeerGather:
+    """Buffers of the fused operator + all-gather (``_C.dequant_matmul_gather``): one gathered
+    [M, N] output per rank and one block of flag words per rank, allocated as torch symmetric
+    memory so that every rank holds device addresses of all of them.
+
+    Collective: construct on every rank of ``group`` at the same point.  ``matmul`` is stream
+    ordered like any other op; every rank must make the same sequence of calls, and whatever
+    reads the returned tensor must be enqueued before this rank's next ``matmul``."""
+
+    def __init__(self, M: int, n_local: int, world_size: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _C
+        self.M, self.n_local, self.world = M, n_local, world_size
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.N = world_size * n_local
+        self.out = symm_mem.empty((M, self.N), dtype=dtype, device=device)
+        self.flags = symm_mem.empty((_C.GATHER_FLAG_WORDS,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        out_hdl = symm_mem.rendezvous(self.out, self.group)
+        flag_hdl = symm_mem.rendezvous(self.flags, self.group)
+        self.out_ptrs = [int(p) for p in out_hdl.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in flag_hdl.buffer_ptrs]
+        if len(self.out_ptrs) != world_size or len(self.flag_ptrs) != world_size:
+            raise RuntimeError("symmetric memory rendezvous returned a different world size")
+        dist.barrier(self.group)   # every rank's flag words are zero before anyone's first call
+
+    def matmul(self, activations, weights_shard, scales_shard, zeros_shard, group_size, quant_type) -> torch.Tensor:
+        from . import _C
+        _C.dequant_matmul_gather(activations, weights_shard, scales_shard, zeros_shard, group_size, quant_type,
+                                 self.out_ptrs, self.flag_ptrs, self.rank, self.rank * self.n_local, self.N)
+        return self.out

@@ -110,3 +110,21 @@ def test_workspace_bytes(C):
     small = wb(1, 3584, 18944, 128, 0)
     assert 3584 * 4 * 2 < small < 4 << 20
     assert wb(32, 57344, 8192, 8192, 1) < 64 << 20
+
+
+def test_gather_entry_point_validates_before_any_cuda_call(C):
+    """mnq_dequant_matmul_gather rejects a bad rank table without touching a device."""
+    import ctypes
+    vp = ctypes.c_void_p
+    one = (vp * 1)(vp(4096))
+    none = (vp * 1)(vp(None))
+    call = C._lib.mnq_dequant_matmul_gather
+    base = (vp(4096), vp(4096), vp(4096), None)
+    tail = (0, 1, 64, 128, 128, 64, 128, C.INT4, C.FP16, C.FP16, None, 0, None)
+    assert call(*base, one, one, 0, 0, *tail) == 4          # world 0
+    assert call(*base, one, one, 9, 0, *tail) == 4          # world too large
+    assert call(*base, one, one, 1, 1, *tail) == 4          # rank outside the world
+    assert call(*base, none, one, 1, 0, *tail) == 4         # null output buffer
+    assert call(*base, one, one, 1, 0, 32, 1, 64, 128, 128, 64, 128, C.INT4, C.FP16, C.FP16, None, 0, None) \
+        == 4                                                # columns past ldc
+    assert b"ldc" in C._lib.mnq_last_error()
