@@ -81,6 +81,7 @@ struct StreamParams {
     int stages;
     int row_blocks;       // ceil(N / 16)
     GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
+    int gather_vec;       // the gathered buffers allow 16-byte stores at every column this call writes
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -350,6 +351,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // pieces are requested; only then are the small loads consumed.
     for (int i = tid; i < p.segs * NT * 8; i += blockDim.x) xsumi[i] = 0ull;
     __shared__ unsigned int x_max_bits;   // largest |activation| of this CTA's chunk, as bf16 bits
+    __shared__ volatile int peers_ready_cta;   // sharded call: every rank has begun this call
     if (CONVERT_X && tid == 0) x_max_bits = 0u;
     float x_down = 1.f, x_up = 1.f;       // 2^-x_shift and 2^x_shift
 
@@ -498,6 +500,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     unsigned int call_no = 0;
     bool peers_ready = false;
     if (p.gather.world > 0) {
+        if (tid == 0) peers_ready_cta = 0;
         unsigned int* mine = p.gather.flag_peer[p.gather.rank];
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(call_no) : "l"(mine + kGatherEpochWord) : "memory");
         call_no += 1u;
@@ -598,28 +601,34 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         xrow[nt] = xs + (size_t)min(nt * 8 + r, p.M - 1) * p.xs_stride + x_lane_off;
     T* out = static_cast<T*>(p.out);
     bool gather_failed = false;
+    // Every rank has begun this call, i.e. no rank still reads the previous call's gathered
+    // output.  Looked up once per CTA (the first thread to need it polls the local flag words,
+    // bounded; the words are written by the peers, nothing is read through them, so plain
+    // volatile loads do) and remembered in shared memory for the rest.
+    auto wait_peers_ready = [&]() -> bool {
+        if (peers_ready) return true;
+        if (!peers_ready_cta) {
+            const volatile unsigned int* mine = p.gather.flag_peer[p.gather.rank] + kGatherReadyBase;
+            for (int g = 0; g < p.gather.world; ++g) {
+                bool in = false;
+                for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
+                    in = static_cast<int>(mine[g] - call_no) >= 0;
+                    if (!in) __nanosleep(100);
+                }
+                if (!in) { gather_failed = true; return false; }
+            }
+            peers_ready_cta = 1;
+        }
+        peers_ready = true;
+        return true;
+    };
     // Plain call: one store.  Sharded call: the same element goes to every rank's gathered buffer
     // (peer-mapped device pointers; the local rank is one of them).
     auto store_out = [&](int m, int n, T v) {
         if (p.gather.world == 0) {
             out[(size_t)m * p.ldc + n] = v;
         } else {
-            if (!peers_ready) {   // once per thread: every rank has begun this call (bounded wait)
-                const unsigned int* mine = p.gather.flag_peer[p.gather.rank] + kGatherReadyBase;
-                bool ok = true;
-                for (int g = 0; g < p.gather.world && ok; ++g) {
-                    bool in = false;
-                    for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
-                        unsigned int r;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(r) : "l"(mine + g) : "memory");
-                        in = static_cast<int>(r - call_no) >= 0;
-                        if (!in) __nanosleep(100);
-                    }
-                    ok = in;
-                }
-                if (!ok) { gather_failed = true; return; }
-                peers_ready = true;
-            }
+            if (!wait_peers_ready()) return;
             for (int g = 0; g < p.gather.world; ++g)
                 static_cast<T*>(p.gather.out_peer[g])[(size_t)m * p.ldc + p.gather.n_offset + n] = v;
         }
@@ -628,6 +637,12 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
     int stage = 0;
     uint32_t parity = 0;
+    // Sharded call, few tokens, no K split: a warp keeps the outputs of its (at most two) row
+    // blocks in registers; after the loop the CTA lays them out as [token][column] in the
+    // activation staging area and copies whole 16-byte pieces to every rank (one store
+    // instruction covers 512 contiguous bytes of a peer's row instead of 16).
+    const bool stage_out = (NT == 1) && p.gather.world > 0 && p.num_chunks == 1 && p.rbw <= 2 && p.gather_vec;
+    float keep[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     for (int rbi = 0; rbi < nrb && !gave_up; ++rbi) {
         float acc[NT][4], tot[NT][4];
 #pragma unroll
@@ -723,6 +738,11 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         const int n0 = rb * 16 + wr;
         const int n1 = n0 + 8;
         if (p.num_chunks == 1) {
+            if (stage_out) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) keep[rbi & 1][i] = CONVERT_X ? tot[0][i] * x_up : tot[0][i];
+                continue;
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -778,10 +798,45 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         // CTA of the grid tells every rank that this rank's slice of this call is complete and
         // waits (bounded) until every rank has said the same here, so that the kernel's completion
         // means "the gathered output is complete on this rank".
+        if (stage_out) {
+            __syncthreads();   // every warp is done reading the staged activations
+            T* st = reinterpret_cast<T*>(xs);                       // [M][cols]
+            const int cols = warps * p.rbw * 16;                    // columns of this CTA, contiguous in N
+            for (int rbi = 0; rbi < nrb; ++rbi)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int m = 2 * t + (i & 1);
+                    const int c = (warp * p.rbw + rbi) * 16 + ((i & 2) ? wr + 8 : wr);
+                    if (m < p.M) st[m * cols + c] = F16Traits<T>::from_float(keep[rbi & 1][i]);
+                }
+            if (tid == 0) wait_peers_ready();
+            __syncthreads();
+            if (peers_ready_cta) {
+                const int n_cta = blockIdx.x * cols;
+                const int vpr = cols / 8;                           // 16-byte pieces per token row
+                const int per_rank = p.M * vpr;
+                for (int idx = tid; idx < per_rank * p.gather.world; idx += blockDim.x) {
+                    const int g = idx / per_rank;
+                    const int r = idx - g * per_rank;
+                    const int m = r / vpr;
+                    const int v = r - m * vpr;
+                    const int n = n_cta + v * 8;
+                    T* dst = static_cast<T*>(p.gather.out_peer[g]) + (size_t)m * p.ldc + p.gather.n_offset + n;
+                    if (n + 8 <= p.N) {
+                        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(st + m * cols + v * 8);
+                    } else {
+                        for (int k = 0; k < 8; ++k)
+                            if (n + k < p.N) dst[k] = st[m * cols + v * 8 + k];
+                    }
+                }
+            }
+        }
         if (gather_failed) atomicOr(&g_device_status, 4u);
-        __threadfence_system();
+        // One system-scope fence by the thread that reports for the CTA covers every thread's
+        // peer stores: they are ordered before it by the barrier.
         __syncthreads();
         if (tid == 0) {
+            __threadfence_system();
             unsigned int* mine = p.gather.flag_peer[p.gather.rank];
             const unsigned int total = gridDim.x * gridDim.y;
             if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
@@ -1017,6 +1072,13 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.rbw = pl.rbw; p.stages = pl.stages;
     p.row_blocks = static_cast<int>((a.N + 15) / 16);
     p.gather = a.gather;
+    p.gather_vec = 0;
+    if (a.gather.world > 0) {
+        const size_t es = 2;   // fp16 / bf16 output
+        bool ok = (a.ldc * es) % 16 == 0 && (a.gather.n_offset * es) % 16 == 0;
+        for (int g = 0; g < a.gather.world; ++g) ok = ok && reinterpret_cast<uintptr_t>(a.gather.out_peer[g]) % 16 == 0;
+        p.gather_vec = ok ? 1 : 0;
+    }
     if (pl.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);
