@@ -504,9 +504,11 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         unsigned int* mine = p.gather.flag_peer[p.gather.rank];
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(call_no) : "l"(mine + kGatherEpochWord) : "memory");
         call_no += 1u;
+        // (plain system-scope stores, all in flight together: nothing is published through this
+        // word, it only has to come after the stream's earlier work, which the launch ensures)
         if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
             for (int g = 0; g < p.gather.world; ++g)
-                asm volatile("st.release.sys.global.u32 [%0], %1;"
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;"
                              ::"l"(p.gather.flag_peer[g] + kGatherReadyBase + p.gather.rank), "r"(call_no) : "memory");
     }
 
@@ -841,21 +843,24 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             const unsigned int total = gridDim.x * gridDim.y;
             if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
                 mine[kGatherCounterWord] = 0u;   // ready for the next call
+                // one fence orders every CTA's peer stores before the arrival words, which then go
+                // out together; the polls are plain loads, with one fence after the last of them
                 __threadfence_system();
                 for (int g = 0; g < p.gather.world; ++g)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
                                  "r"(call_no) : "memory");
                 bool all_in = true;
                 for (int src = 0; src < p.gather.world && all_in; ++src) {
                     bool in = false;
                     for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
                         unsigned int v;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
+                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
                         in = static_cast<int>(v - call_no) >= 0;
-                        if (!in) __nanosleep(200);
+                        if (!in) __nanosleep(100);
                     }
                     all_in = in;
                 }
+                __threadfence_system();
                 if (!all_in) atomicOr(&g_device_status, 4u);   // a rank never reported: give up, do not hang
                 asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine + kGatherEpochWord), "r"(call_no) : "memory");
             }
