@@ -420,9 +420,13 @@ def run_ours(args):
 
     def e2e_step(i):
         for j, L in enumerate(dev_layers[i % copies]):
-            xs_dev[j].copy_(xs_host[j], non_blocking=True)
-            o = run_layer(j, L, xs_dev[j])
-            outs_host[j].copy_(o, non_blocking=True)
+            if world == 1:
+                # host activations in, host result out: the operator enqueues both copies itself
+                _C.dequant_matmul(xs_host[j], L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs_host[j])
+            else:
+                xs_dev[j].copy_(xs_host[j], non_blocking=True)
+                o = run_layer(j, L, xs_dev[j])
+                outs_host[j].copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(args.steps, 400)
@@ -445,8 +449,11 @@ def run_ours(args):
            "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in xs_host),
            "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs_host),
            "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-           "call": ("metal_native.sharded.PeerGather.matmul per projection, eager; weights resident" if fused
-                    else "metal_native._C.dequant_matmul per projection, eager; weights resident")}
+           "call": ("metal_native.sharded.PeerGather.matmul per projection between torch copies, eager; weights resident"
+                    if fused else
+                    "metal_native._C.dequant_matmul(host activations, out=host tensor) per projection, eager: the "
+                    "operator enqueues the host->device and device->host copies; weights resident" if world == 1 else
+                    "metal_native._C.dequant_matmul per projection between torch copies, eager; weights resident")}
 
     # ---- keep the load on for the clock sampler, then read it ----------------------------
     # every rank replays the same number of times (the graph may hold collectives): about one

@@ -184,6 +184,22 @@ MNQ_API int mnq_dequant_matmul_static(const void* activations, const void* weigh
                               int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
                               int32_t scale_dtype, void* stream);
 
+/* The fused operator for activations and output in HOST memory (pinned for the copies to be
+ * asynchronous), weights, scales and zeros resident on the device.  The reference's tensors live in
+ * memory both the CPU and the GPU address (MTLStorageModeShared, src/core/tensor_helpers.mm:13-48), so
+ * its callers hand `dequant_matmul` buffers they filled on the CPU and read the result on the CPU
+ * after `synchronize()`; on a discrete GPU the same calling pattern needs the two copies, and this
+ * entry point enqueues them with the kernel: host -> device of [M, K] activations (contiguous),
+ * the operator, device -> host of the [M, N] output (contiguous), all on `stream`, returning
+ * without synchronising.  `workspace` must hold mnq_host_workspace_bytes(...) bytes: the operator's
+ * scratch (zero-filled once, as for mnq_dequant_matmul) followed by the device copies of the
+ * activations and the output. */
+MNQ_API size_t mnq_host_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type);
+MNQ_API int mnq_dequant_matmul_host(const void* activations_host, const void* weights_packed, const void* scales,
+                                    const void* zeros, void* out_host, int64_t M, int64_t N, int64_t K,
+                                    int32_t group_size, int32_t quant_type, int32_t act_dtype, int32_t scale_dtype,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+
 /* Column-sharded fused operator with the all-gather folded into the kernel.  No counterpart in
  * the reference (it drives one device); this is the N-sharded form of mnq_dequant_matmul for
  * `world` GPUs of one node, one process per GPU, each holding rows [n_offset, n_offset + N_local)

@@ -289,6 +289,46 @@ int mnq_dequant_matmul_gather(const void* activations, const void* weights_packe
     return launch_gemv_stream(a, nullptr);
 }
 
+static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+size_t mnq_host_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
+{
+    if (M <= 0 || N <= 0 || K < 0) return 0;
+    return align256(mnq_workspace_bytes(M, N, K, group_size, quant_type)) + align256(static_cast<size_t>(M) * K * 2) +
+           align256(static_cast<size_t>(M) * N * 2);
+}
+
+int mnq_dequant_matmul_host(const void* activations_host, const void* weights_packed, const void* scales,
+                            const void* zeros, void* out_host, int64_t M, int64_t N, int64_t K,
+                            int32_t group_size, int32_t quant_type, int32_t act_dtype, int32_t scale_dtype,
+                            void* workspace, size_t workspace_bytes, void* stream)
+{
+    int rc = validate_matmul(activations_host, weights_packed, scales, out_host, true, M, N, K, K, N, group_size,
+                             quant_type, act_dtype, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return MNQ_SUCCESS;
+    const size_t need = mnq_host_workspace_bytes(M, N, K, group_size, quant_type);
+    if (!workspace || workspace_bytes < need)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_host: workspace of %zu bytes needed (mnq_host_workspace_bytes), got %zu",
+                    need, workspace ? workspace_bytes : static_cast<size_t>(0));
+    // workspace: [operator scratch][activations][output]
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    const size_t scratch = align256(mnq_workspace_bytes(M, N, K, group_size, quant_type));
+    unsigned char* x_dev = ws + scratch;
+    unsigned char* out_dev = x_dev + align256(static_cast<size_t>(M) * K * 2);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K > 0) {
+        rc = check_cuda(cudaMemcpyAsync(x_dev, activations_host, static_cast<size_t>(M) * K * 2, cudaMemcpyHostToDevice, st),
+                        "cudaMemcpyAsync(activations to device)");
+        if (rc) return rc;
+    }
+    rc = mnq_dequant_matmul(x_dev, weights_packed, scales, zeros, out_dev, M, N, K, K, N, group_size, quant_type, act_dtype,
+                            scale_dtype, scratch ? ws : nullptr, scratch, stream);
+    if (rc) return rc;
+    return check_cuda(cudaMemcpyAsync(out_host, out_dev, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, st),
+                      "cudaMemcpyAsync(output to host)");
+}
+
 int mnq_dequant_matmul(const void* activations, const void* weights_packed, const void* scales,
                        const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
                        int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,

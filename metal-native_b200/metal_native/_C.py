@@ -71,6 +71,10 @@ def _load() -> ctypes.CDLL:
     L.mnq_dequantize_flat.argtypes = [vp, vp, vp, i64, i32, i32, vp]
     L.mnq_device_status.restype = ctypes.c_int
     L.mnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), i32]
+    L.mnq_host_workspace_bytes.restype = sz
+    L.mnq_host_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
+    L.mnq_dequant_matmul_host.restype = ctypes.c_int
+    L.mnq_dequant_matmul_host.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
     L.mnq_dequant_matmul_gather.restype = ctypes.c_int
     L.mnq_dequant_matmul_gather.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64,
                                             i64, i64, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
@@ -151,10 +155,14 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor |
     return ws
 
 
-def _prepare(activations, weights_packed, scales, zeros, group_size, quant_type):
+def _prepare(activations, weights_packed, scales, zeros, group_size, quant_type, host_x=False):
     q = _quant_code(quant_type)
-    _require_cuda("activations", activations)
-    dev = activations.device
+    if host_x:   # activations in host memory, everything else on the device
+        _require_cuda("weights_packed", weights_packed)
+        dev = weights_packed.device
+    else:
+        _require_cuda("activations", activations)
+        dev = activations.device
     _require_cuda("weights_packed", weights_packed, dev)
     _require_cuda("scales", scales, dev)
     if zeros is not None:
@@ -209,6 +217,8 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
     enqueued on the current CUDA stream; like the reference op it returns before the
     GPU has finished (``synchronize()`` or any torch sync waits for it).
     """
+    if isinstance(activations, torch.Tensor) and not activations.is_cuda:
+        return _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out)
     x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
     dev = x.device
     if out is None:
@@ -231,6 +241,33 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
         _check(_lib.mnq_dequant_matmul(*args))
     else:
         _check(_lib.mnq_dequant_matmul_ex(*args, ctypes.byref(tuning)))
+    return out
+
+
+def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out):
+    """Host-memory activations and output (``mnq_dequant_matmul_host``): the reference's callers
+    fill tensors on the CPU and read results on the CPU after ``synchronize()`` because its
+    memory is shared between CPU and GPU; here the two copies are enqueued with the kernel.
+    Pinned tensors make them asynchronous.  ``out`` (host, [M, N]) is allocated pinned when not
+    given; it holds the result once the stream has been synchronised."""
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type,
+                                              host_x=True)
+    if lda != K:
+        x = x.contiguous()
+    dev = w.device
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, pin_memory=True)
+    elif out.is_cuda or out.shape != (M, N) or out.dtype != x.dtype or not out.is_contiguous():
+        raise _invalid("dequant_matmul: with host activations, out must be a contiguous host [M, N] tensor "
+                       "in the dtype of activations")
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        nbytes = _lib.mnq_host_workspace_bytes(M, N, K, g, q)
+        ws = _workspace(dev, stream, nbytes)
+        _check(_lib.mnq_dequant_matmul_host(
+            x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
+            M, N, K, g, q, _DT[x.dtype], _DT[s.dtype], ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, stream))
     return out
 
 
@@ -368,4 +405,5 @@ def exported_symbols() -> list[str]:
     """Entry points declared in include/mnq.h that this module binds."""
     return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
-            "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather"]
+            "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather", "mnq_host_workspace_bytes",
+            "mnq_dequant_matmul_host"]

@@ -298,8 +298,8 @@ def test_errors_are_raised_before_any_launch(mn):
         mn._C.dequant_matmul(L.x, L.wq, L.scales, L.zeros, 128, "fp4")
     with pytest.raises(E, match="scales must be contiguous"):
         mn._C.dequant_matmul(L.x, L.wq, L.scales[:16], L.zeros, 128, "int4")
-    with pytest.raises(E, match="must be a CUDA tensor"):
-        mn._C.dequant_matmul(L.x.cpu(), L.wq, L.scales, L.zeros, 128, "int4")
+    with pytest.raises(E, match="must be a CUDA tensor"):      # weights never live on the host: no CPU path
+        mn._C.dequant_matmul(L.x, L.wq.cpu(), L.scales, L.zeros, 128, "int4")
     assert E(6, "x").code_name == "TimeoutError"
     # the context is still healthy
     out = mn._C.dequant_matmul(*L.args())
@@ -316,3 +316,28 @@ def test_empty_inputs(mn):
     # K == 0: an empty sum
     out = mn._C.dequant_matmul(x1[:, :0], wq[:, :0], s[:, :0], None, 128, "int4")
     assert out.shape == (3, 32) and bool((out == 0).all())
+
+
+@pytest.mark.parametrize("M,K,N,quant,g,adt", [(1, 1024, 512, "int4", 128, torch.float16),
+                                                (4, 2048, 384, "int8", 2048, torch.bfloat16),
+                                                (64, 256, 256, "int4", 128, torch.float16)])
+def test_host_activations_and_output(mn, M, K, N, quant, g, adt):
+    """Activations filled on the CPU, result read on the CPU after synchronize(), as the reference's
+    callers do with its shared-memory tensors; the two copies are enqueued with the kernel
+    (mnq_dequant_matmul_host).  Same bits as the device-tensor call."""
+    from metal_native import workloads
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             asymmetric=adt == torch.float16, seed=M + K)
+    d = L.to("cuda")
+    want = mn._C.dequant_matmul(*d.args()).cpu()
+    x_host = L.x.clone().pin_memory()
+    out_host = torch.empty((M, N), dtype=adt).pin_memory()
+    for _ in range(3):   # successive calls share the cached workspace and its staging area
+        out_host.zero_()
+        got = mn._C.dequant_matmul(x_host, d.wq, d.scales, d.zeros, g, quant, out=out_host)
+        mn._C.synchronize()
+        assert got is out_host and torch.equal(out_host, want)
+    fresh = mn._C.dequant_matmul(L.x, d.wq, d.scales, d.zeros, g, quant)      # pageable input, output allocated
+    mn._C.synchronize()
+    assert not fresh.is_cuda and torch.equal(fresh, want)
+    assert mn._C.device_status() == 0
