@@ -80,6 +80,7 @@ struct GemmParams {
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
     int raw_stages;     // stages of the packed-weight ring
     int raw_segs;       // 128-byte-wide boxes per stage (consecutive along k)
+    int commit_every;   // k-blocks per tcgen05.commit (1 or 2)
     int table_groups;   // quantisation groups per row held in the shared-memory scale table
     int splits;         // K splits (grid.z)
     int kb_per_split;   // 64-k blocks per split
@@ -418,10 +419,14 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     // Synchronisation is per k-block, on D = max(S, SB) barrier pairs indexed kb % D:
     // ready[kb % D] completes when the k-block's weight tile is dequantised (one arrival per
     // dequantise warp that works on it: four per CTA) and its activation tiles have landed (one arrival with the byte count);
-    // done[kb % D] completes when the MMAs of that k-block have read their operands (one commit).
-    // A producer refilling ring slot kb % S (or kb % SB) waits for done of k-block kb - S (kb - SB).
-    // So the MMA thread does one wait and one commit per k-block.
+    // done[(kb / CE) % (D / CE)] completes when the MMAs of the CE consecutive k-blocks around kb have
+    // read their operands: with CE = 2 there is one commit per pair of k-blocks, because a commit
+    // costs the issuing thread a few hundred cycles and at small token counts that thread sets the
+    // pace.  A producer refilling ring slot kb % S (or kb % SB) waits for the barrier that covers
+    // k-block kb - S (kb - SB).  So the MMA thread does one wait per k-block and one commit per CE.
     const int S = p.stages, SB = p.b_stages, D = max(S, SB);
+    const int CE = p.commit_every;   // k-blocks per commit: 2 when both rings are deep enough (then S, SB are even), else 1
+    const int H = D / CE;            // `done` barriers
     const uint32_t rank = PAIR ? cluster_rank() : 0u;   // 0: leader (issues the MMAs), 1: peer
     const int b_rows = PAIR ? p.tokh / 2 : p.tokh;       // tokens of each activation tile this CTA loads
     const int b_bytes = b_rows * 128;
@@ -443,7 +448,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 
     if (tid == 0) {
         // ready: the dequantise warps of every CTA feeding the MMA, plus the thread that announces the bytes
-        for (int d = 0; d < D; ++d) { bar_init(ready0 + 8 * d, (PAIR ? 8 : 4) + 1); bar_init(done0 + 8 * d, 1); }
+        for (int d = 0; d < D; ++d) bar_init(ready0 + 8 * d, (PAIR ? 8 : 4) + 1);
+        for (int h = 0; h < H; ++h) bar_init(done0 + 8 * h, 1);
         bar_init(accum, 1);
         for (int r = 0; r < R; ++r) { bar_init(rfull0 + 8 * r, 1); bar_init(rempty0 + 8 * r, 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -477,12 +483,12 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             const uint32_t ready_at = PAIR ? map_to_rank(ready0, 0) : ready0;   // the leader's barriers
             const uint32_t stage_bytes = (uint32_t)(p.nh * b_bytes);
             int sb = 0, d = 0;
-            int wd = 0; uint32_t wph = 0;   // done[(kb - SB) % D] and its phase
+            int wd = 0; uint32_t wph = 0;   // pair barrier of k-block i - SB and its phase
             for (int i = 0; i < num_kb; ++i) {
                 const int kb = i + k_rot < num_kb ? i + k_rot : i + k_rot - num_kb;
-                if (i >= SB) {
+                if (i >= SB && (CE == 1 || !((i - SB) & 1))) {   // CE = 2: the second k-block of a pair is free with the first
                     if (!bar_wait(done0 + 8 * wd, wph)) { failed = true; break; }
-                    if (++wd == D) { wd = 0; wph ^= 1u; }
+                    if (++wd == H) { wd = 0; wph ^= 1u; }
                 }
                 // one arrival announcing all the bytes of the k-block (both CTAs' halves for a pair)
                 if (rank == 0) bar_expect_tx(ready0 + 8 * d, PAIR ? 2u * stage_bytes : stage_bytes);
@@ -519,6 +525,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = instr_desc(p.tokh, IS_BF16, PAIR ? 2 * BN : BN);
             int s = 0, sb = 0, d = 0; uint32_t dph = 0;
+            int hp = 0;                             // pair barrier of this k-block
             for (int kb = 0; kb < num_kb; ++kb) {   // kb: position in this CTA's k order
                 if (!(PAIR ? bar_wait_cluster(ready0 + 8 * d, dph) : bar_wait(ready0 + 8 * d, dph))) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -533,8 +540,11 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     }
                 }
                 // operands of this k-block are free once these MMAs have read them
-                if (PAIR) umma_commit_pair(done0 + 8 * d);
-                else umma_commit(done0 + 8 * d);
+                if (CE == 1 || (kb & 1) || kb == num_kb - 1) {
+                    if (PAIR) umma_commit_pair(done0 + 8 * hp);
+                    else umma_commit(done0 + 8 * hp);
+                    if (++hp == H) hp = 0;
+                }
                 if (++s == S) s = 0;
                 if (++sb == SB) sb = 0;
                 if (++d == D) { d = 0; dph ^= 1u; }
@@ -596,7 +606,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         // This warp takes every other k-block of the CTA's k order (whole 64-k rows of its 32 weight rows),
         // so it pays for the barrier traffic of a k-block only every other k-block.
         int s = half, d = half;                 // kb % S and kb % D of this warp's next k-block (S, D >= 2)
-        int wd = (S ^ half) & 1; uint32_t wph = 0;   // done[(kb - S) % D] and its phase, from this warp's first kb >= S
+        // barrier covering k-block i - S, and its phase, from this warp's first i >= S: the warp takes
+        // every other k-block, so it meets every pair barrier once (CE = 2) or every other barrier (CE = 1)
+        int wd = CE == 1 ? ((S ^ half) & 1) : 0; uint32_t wph = 0;
+        const int wstep = CE == 1 ? 2 : 1;
         int r = 0; uint32_t rph = 0;
         int seq = 0;                            // position of the next k-block in this CTA's k order
         for (int j = 0; j < num_raw && !failed; ++j) {
@@ -625,8 +638,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 __half2 nz2 = __half2half2(__ushort_as_half((unsigned short)((sz >> 16) ^ 0x8000u)));
                 if (i >= S) {   // the MMAs that read this ring slot S k-blocks ago are done
                     if (!bar_wait(done0 + 8 * wd, wph)) { failed = true; break; }
-                    wd += 2;
-                    if (wd >= D) { wd -= D; wph ^= 1u; }
+                    wd += wstep;
+                    if (wd >= H) { wd -= H; wph ^= 1u; }
                 }
                 const uint32_t a_row = tiles + s * A_BYTES + row * 128;
 #pragma unroll
@@ -740,7 +753,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 }
 
 struct GemmPlan {
-    int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, raw_segs, table_groups, tmem_cols, splits, kb_per_split;
+    int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, raw_segs, commit_every, table_groups, tmem_cols, splits, kb_per_split;
     int pair;       // 1: clusters of two CTAs sharing each activation tile
     int tiles_n;    // CTAs along N (even when pair)
     size_t smem;
@@ -849,6 +862,13 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (pl.raw_stages < 1) return false;
     int ast = static_cast<int>((budget - b_stage * bst) / A_BYTES);
     if (ast > 8) ast = 8;
+    // deep rings: release operands a pair of k-blocks at a time (needs even stage counts)
+    pl.commit_every = 1;
+    if (bst >= 4 && ast >= 4) {
+        pl.commit_every = 2;
+        bst &= ~1;
+        ast &= ~1;
+    }
     pl.b_stages = bst;
     pl.stages = ast;
     pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * A_BYTES;
@@ -960,7 +980,7 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.row_bytes = static_cast<int>(a.quant == MNQ_INT4 ? a.K / 2 : a.K);
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
-    p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
+    p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.commit_every = pl.commit_every; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
     p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0);
