@@ -326,10 +326,12 @@ def run_ours(args):
             run_layer(j, L, L.x)
 
     def launches(L):
-        # one kernel per projection; the tensor-core path with K split adds its reduce kernel
+        # one kernel per projection; with K split, the tensor-core path and the many-token (M > 8)
+        # decode path add a reduce kernel
         path = _C.select_path(L.M, L.N, L.K, L.group_size, L.quant_type, L.x.dtype, zeros=L.zeros is not None)
         q = 0 if L.quant_type == "int4" else 1
-        split = path == "gemm" and _C._lib.mnq_workspace_bytes(L.M, L.N, L.K, int(L.group_size), q) > 0
+        split = ((path == "gemm" or (path == "gemv" and L.M > 8 and fused is None)) and
+                 _C._lib.mnq_workspace_bytes(L.M, L.N, L.K, int(L.group_size), q) > 0)
         return 2 if split else 1
 
     kernels_per_step = sum(launches(L) for L in layers_cpu)

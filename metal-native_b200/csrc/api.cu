@@ -291,10 +291,19 @@ int mnq_dequant_matmul_gather(const void* activations, const void* weights_packe
 
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+// Operator scratch at the front of a host-call workspace.  Never shorter than the counter region:
+// a workspace is shared by successive calls of any kind, and the device copies of activations and
+// output that follow the scratch must not land where a later split-K call expects zeroed counters.
+static size_t host_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
+{
+    const size_t need = align256(mnq_workspace_bytes(M, N, K, group_size, quant_type));
+    return need > mnq::kCounterBytes ? need : mnq::kCounterBytes;
+}
+
 size_t mnq_host_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
     if (M <= 0 || N <= 0 || K < 0) return 0;
-    return align256(mnq_workspace_bytes(M, N, K, group_size, quant_type)) + align256(static_cast<size_t>(M) * K * 2) +
+    return host_scratch_bytes(M, N, K, group_size, quant_type) + align256(static_cast<size_t>(M) * K * 2) +
            align256(static_cast<size_t>(M) * N * 2);
 }
 
@@ -313,7 +322,8 @@ int mnq_dequant_matmul_host(const void* activations_host, const void* weights_pa
                     need, workspace ? workspace_bytes : static_cast<size_t>(0));
     // workspace: [operator scratch][activations][output]
     unsigned char* ws = static_cast<unsigned char*>(workspace);
-    const size_t scratch = align256(mnq_workspace_bytes(M, N, K, group_size, quant_type));
+    const size_t scratch = host_scratch_bytes(M, N, K, group_size, quant_type);
+    const size_t op_scratch = mnq_workspace_bytes(M, N, K, group_size, quant_type);
     unsigned char* x_dev = ws + scratch;
     unsigned char* out_dev = x_dev + align256(static_cast<size_t>(M) * K * 2);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -323,7 +333,7 @@ int mnq_dequant_matmul_host(const void* activations_host, const void* weights_pa
         if (rc) return rc;
     }
     rc = mnq_dequant_matmul(x_dev, weights_packed, scales, zeros, out_dev, M, N, K, K, N, group_size, quant_type, act_dtype,
-                            scale_dtype, scratch ? ws : nullptr, scratch, stream);
+                            scale_dtype, op_scratch ? ws : nullptr, op_scratch ? scratch : 0, stream);
     if (rc) return rc;
     return check_cuda(cudaMemcpyAsync(out_host, out_dev, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, st),
                       "cudaMemcpyAsync(output to host)");

@@ -721,20 +721,24 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
         const size_t total = plane / 8;
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
             const size_t e = i * 8;
-            float4 lo[kMaxSplits], hi[kMaxSplits];
+            // planes in batches of six: every load of a batch is issued before the first add
+            // (indices past the last plane are clamped and their values dropped)
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            for (int z0 = 0; z0 < splits; z0 += 6) {
+                float4 lo[6], hi[6];
 #pragma unroll
-            for (int z = 0; z < kMaxSplits; ++z)
-                if (z < splits) {
-                    lo[z] = __ldcs(reinterpret_cast<const float4*>(partial + z * plane + e));
-                    hi[z] = __ldcs(reinterpret_cast<const float4*>(partial + z * plane + e + 4));
+                for (int z = 0; z < 6; ++z) {
+                    const size_t at = (size_t)min(z0 + z, splits - 1) * plane + e;
+                    lo[z] = __ldcs(reinterpret_cast<const float4*>(partial + at));
+                    hi[z] = __ldcs(reinterpret_cast<const float4*>(partial + at + 4));
                 }
-            float4 a = lo[0], b = hi[0];
 #pragma unroll
-            for (int z = 1; z < kMaxSplits; ++z)
-                if (z < splits) {
-                    a.x += lo[z].x; a.y += lo[z].y; a.z += lo[z].z; a.w += lo[z].w;
-                    b.x += hi[z].x; b.y += hi[z].y; b.z += hi[z].z; b.w += hi[z].w;
-                }
+                for (int z = 0; z < 6; ++z)
+                    if (z0 + z < splits) {
+                        a.x += lo[z].x; a.y += lo[z].y; a.z += lo[z].z; a.w += lo[z].w;
+                        b.x += hi[z].x; b.y += hi[z].y; b.z += hi[z].z; b.w += hi[z].w;
+                    }
+            }
             const size_t m = e / N, n = e % N;
             union { T h[8]; uint4 u; } pk;
             pk.h[0] = F16Traits<T>::from_float(a.x); pk.h[1] = F16Traits<T>::from_float(a.y);
@@ -909,11 +913,21 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     const int rc = check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
     if (rc || p.splits <= 1) return rc;
     // second launch: add the splits' planes and write the output
-    T* out = static_cast<T*>(p.out);
-    const bool vec = p.N % 8 == 0 && p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
-    const size_t work = vec ? (size_t)p.M * p.N / 8 : (size_t)p.M * p.N;
+    return launch_splitk_reduce(p.partial, p.out, p.M, p.N, p.ldc, p.splits,
+                                std::is_same<T, __nv_bfloat16>::value ? MNQ_BF16 : MNQ_FP16, stream);
+}
+
+}  // namespace
+
+template <typename T>
+static int launch_reduce_t(const float* partial, void* out_v, int M, int N, int64_t ldc, int splits, cudaStream_t stream)
+{
+    T* out = static_cast<T*>(out_v);
+    const bool vec = N % 8 == 0 && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const size_t work = vec ? (size_t)M * N / 8 : (size_t)M * N;
     size_t blocks = (work + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(256);
@@ -923,12 +937,16 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const float* partial = p.partial;
     auto* red = vec ? &splitk_reduce_kernel<T, true> : &splitk_reduce_kernel<T, false>;
-    return check_cuda(cudaLaunchKernelEx(&cfg, red, partial, out, p.M, p.N, p.ldc, p.splits), "splitk_reduce launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, red, partial, out, M, N, (long long)ldc, splits), "splitk_reduce launch");
 }
 
-}  // namespace
+int launch_splitk_reduce(const float* partial, void* out, int M, int N, int64_t ldc, int splits, int32_t act_dtype,
+                         cudaStream_t stream)
+{
+    if (act_dtype == MNQ_BF16) return launch_reduce_t<__nv_bfloat16>(partial, out, M, N, ldc, splits, stream);
+    return launch_reduce_t<__half>(partial, out, M, N, ldc, splits, stream);
+}
 
 int read_gemm_status(unsigned int* out, bool clear)
 {

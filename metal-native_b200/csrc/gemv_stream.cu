@@ -82,6 +82,7 @@ struct StreamParams {
     int row_blocks;       // ceil(N / 16)
     GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
     int gather_vec;       // the gathered buffers allow 16-byte stores at every column this call writes
+    int defer_reduce;     // K chunks are added by a reduce kernel launched after this one: only store the partial sums
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -442,22 +443,23 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
         *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
     };
-    // Scales / zeros of one row block (16 rows x segs groups): entry e = row * segs + group goes
-    // to lane e % 32, so a warp-wide load covers 32 consecutive entries, i.e. a contiguous run of
-    // groups of one or two rows (a cache line or two per load instead of one per lane).  A batch
-    // is SCB entries per lane; nothing in the load phase uses a loaded value, so a batch's loads
-    // are all in flight together.
-    const int sc_entries = 16 * p.segs;
+    // Scales / zeros of this warp's row blocks (nrb x 16 consecutive rows x segs groups): entry
+    // e = row * segs + group goes to lane e % 32, so a warp-wide load covers 32 consecutive
+    // entries, i.e. a contiguous run of groups of one or a few rows (a cache line or two per load
+    // instead of one per lane), and the folded values land at sS[e], sZ[e].  A batch is SCB
+    // entries per lane; nothing in the load phase uses a loaded value, so a batch's loads are all
+    // in flight together, across row blocks too.
+    const int sc_entries = nrb * 16 * p.segs;
     const int sc_q32 = 32 / p.segs, sc_r32 = 32 - sc_q32 * p.segs;   // (row, group) step of 32 entries
-    auto load_scale_batch = [&](int rbi, int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
+    auto load_scale_batch = [&](int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
         const int e0 = batch * SCB * 32 + lane;
         int row = e0 / p.segs;
         int g = e0 - row * p.segs;
 #pragma unroll
         for (int u = 0; u < SCB; ++u) {
-            const int n = (rb_first + rbi) * 16 + row;
+            const int n = rb_first * 16 + row;
             sp[u] = 0; zp[u] = 0;
-            if (rbi < nrb && row < 16 && n < p.N && seg0 + g < p.G) {
+            if (row < nrb * 16 && n < p.N && seg0 + g < p.G) {
                 const size_t at = (size_t)n * p.G + seg0 + g;
                 sp[u] = __ldg(sc16 + at);
                 if (has_zero) zp[u] = __ldg(zr16 + at);
@@ -467,11 +469,11 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             if (g >= p.segs) { g -= p.segs; ++row; }
         }
     };
-    auto fold_scale_batch = [&](int rbi, int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
+    auto fold_scale_batch = [&](int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
 #pragma unroll
         for (int u = 0; u < SCB; ++u) {
             const int e = (batch * SCB + u) * 32 + lane;
-            if (rbi < nrb && e < sc_entries) {
+            if (e < sc_entries) {
                 float s0, z0;
                 if (p.scale_dtype == MNQ_BF16) {
                     s0 = __uint_as_float(sp[u] << 16);
@@ -480,8 +482,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     s0 = __half2float(__ushort_as_half((unsigned short)sp[u]));
                     z0 = __half2float(__ushort_as_half((unsigned short)zp[u]));
                 }
-                sS[rbi * sc_entries + e] = s0 * Enc<QUANT, MT>::inv_alpha;
-                sZ[rbi * sc_entries + e] = fmaf(Enc<QUANT, MT>::offset, s0, z0);
+                sS[e] = s0 * Enc<QUANT, MT>::inv_alpha;
+                sZ[e] = fmaf(Enc<QUANT, MT>::offset, s0, z0);
             }
         }
     };
@@ -513,7 +515,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
 
     uint32_t sreg[SCB], zreg[SCB];
-    load_scale_batch(0, 0, sreg, zreg);
+    load_scale_batch(0, sreg, zreg);
     uint32_t xv[XB][4];
     int xm[XB], xb[XB], xk[XB];
 #pragma unroll
@@ -559,16 +561,15 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
 
     // consume the small loads
-    fold_scale_batch(0, 0, sreg, zreg);
+    fold_scale_batch(0, sreg, zreg);
 #pragma unroll
     for (int u = 0; u < XB; ++u)
         if (__any_sync(0xffffffffu, xm[u] >= 0)) store_x_block(xv[u], xm[u], xb[u], xk[u]);
     // whatever did not fit in the first batch (several row blocks per warp, many groups, M > 8)
-    for (int rbi = 0; rbi < nrb; ++rbi)
-        for (int batch = (rbi == 0 ? 1 : 0); batch < sc_batches; ++batch) {
-            load_scale_batch(rbi, batch, sreg, zreg);
-            fold_scale_batch(rbi, batch, sreg, zreg);
-        }
+    for (int batch = 1; batch < sc_batches; ++batch) {
+        load_scale_batch(batch, sreg, zreg);
+        fold_scale_batch(batch, sreg, zreg);
+    }
     {
         constexpr int XB2 = 8;   // deeper batches for the bulk of a many-token activation block
         for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB2 * blockDim.x) {
@@ -765,6 +766,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 const int n = (i & 2) ? n1 : n0;
                 if (m < p.M && n < p.N) __stcg(&mine[(size_t)m * p.N + n], CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]);
             }
+        if (p.defer_reduce) continue;   // a second kernel adds the chunks
         __threadfence();
         __syncwarp();
         unsigned int arrival = 0;
@@ -909,7 +911,9 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     pl.piece_bytes = (tuning && tuning->piece_bytes > 0) ? tuning->piece_bytes : 256;
     if (pl.piece_bytes != 256 && pl.piece_bytes != 512) return false;
     if (pl.nt > 1) pl.piece_bytes = 256;
-    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : 2;
+    // more than 8 tokens: chunks are short and there are fewer warps, so each warp keeps more
+    // pieces in flight (the loop below takes stages away again if shared memory runs out)
+    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : (pl.nt >= 2 ? 4 : 2);
     if (pl.stages > 8) pl.stages = 8;
     if (pl.stages < 2) pl.stages = 2;
     const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : 1;
@@ -920,15 +924,30 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     // that minimises that, i.e. fills the warp slots without spilling into a nearly empty
     // second pass.
     int chunks = 1, rbw = 1;
+    // More than 8 tokens: every CTA converts and stages its K chunk of the whole activation
+    // block, which costs about 0.2 step-times per token and step and dwarfs the streaming if the
+    // chunk is long.  Short chunks with many row blocks per warp stage little and reuse it a
+    // lot, so the model below also charges the staging, and a warp may take up to 8 row blocks.
+    const bool many_tokens = pl.nt >= 2;
+    int rbw_cap = many_tokens ? 8 : 2;
     if (tuning && tuning->split_k > 0) {
         chunks = tuning->split_k;
     } else if (row_blocks <= kMaxCounters) {
         double best_cost = 1e30;
         for (int c = 1; c <= kMaxSplitK && c <= pl.total_steps; ++c) {
-            const int spc = (pl.total_steps + c - 1) / c;
+            int spc = (pl.total_steps + c - 1) / c;
             if (c > 1 && spc < 4) break;
-            const int64_t passes = (row_blocks * c + slots - 1) / slots;
-            const double cost = static_cast<double>(passes) * (spc + 8) + (c > 1 ? 0.25 * c : 0.0);
+            if (many_tokens && c > 1) spc = (spc + 3) & ~3;   // whole 256-byte pieces: the unrolled path
+            double cost;
+            if (many_tokens) {
+                const int64_t per_warp = (row_blocks * c + slots - 1) / slots;           // units per warp
+                const int64_t waves = (per_warp + rbw_cap - 1) / rbw_cap;                // CTAs per SM, one after the other
+                cost = static_cast<double>(per_warp) * (spc + 8) + static_cast<double>(waves) * 0.2 * a.M * spc +
+                       (c > 1 ? 10.0 : 0.0);
+            } else {
+                const int64_t passes = (row_blocks * c + slots - 1) / slots;
+                cost = static_cast<double>(passes) * (spc + 8) + (c > 1 ? 0.25 * c : 0.0);
+            }
             if (cost < best_cost - 1e-9) { best_cost = cost; chunks = c; }
         }
     }
@@ -936,9 +955,9 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     if (chunks > pl.total_steps) chunks = pl.total_steps;
     if (chunks < 1 || row_blocks > kMaxCounters) chunks = 1;
 
-    int rbw_cap = 2;
     for (;;) {
         pl.steps_per_chunk = (pl.total_steps + chunks - 1) / chunks;
+        if (many_tokens && chunks > 1) pl.steps_per_chunk = (pl.steps_per_chunk + 3) & ~3;
         pl.num_chunks = (pl.total_steps + pl.steps_per_chunk - 1) / pl.steps_per_chunk;
         const int64_t units = row_blocks * pl.num_chunks;
         // a warp takes at most rbw_cap consecutive row blocks (their scales are all staged up
@@ -966,7 +985,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
             // too much shared memory: fewer stages, then shorter chunks (less staged
             // activation), then fewer warps
             if (pl.stages > 2) { --pl.stages; continue; }
-            if (rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap = 1; continue; }
+            if (rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap >>= 1; continue; }
             if (chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
                 !(tuning && tuning->split_k > 0)) {
                 ++chunks;
@@ -1077,6 +1096,10 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.rbw = pl.rbw; p.stages = pl.stages;
     p.row_blocks = static_cast<int>((a.N + 15) / 16);
     p.gather = a.gather;
+    // many tokens: the chunk planes are big and every unit would pay a fence and an atomic round
+    // trip; a separate coalesced kernel adds them instead (not with the fused gather, whose peer
+    // stores live in this kernel)
+    p.defer_reduce = (pl.num_chunks > 1 && pl.nt >= 2 && a.gather.world == 0) ? 1 : 0;
     p.gather_vec = 0;
     if (a.gather.world > 0) {
         const size_t es = 2;   // fp16 / bf16 output
@@ -1098,14 +1121,18 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     if (rc) return rc;
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
-#define MNQ_GS(Q, T) return launch_stream_nt<Q, T>(p, wmap, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
+#define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
+    int rcl;
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_GS(MNQ_INT4, __half);
-        MNQ_GS(MNQ_INT4, __nv_bfloat16);
+        else MNQ_GS(MNQ_INT4, __nv_bfloat16);
+    } else {
+        if (a.act_dtype == MNQ_FP16) MNQ_GS(MNQ_INT8, __half);
+        else MNQ_GS(MNQ_INT8, __nv_bfloat16);
     }
-    if (a.act_dtype == MNQ_FP16) MNQ_GS(MNQ_INT8, __half);
-    MNQ_GS(MNQ_INT8, __nv_bfloat16);
 #undef MNQ_GS
+    if (rcl || !p.defer_reduce) return rcl;
+    return launch_splitk_reduce(p.partial, a.out, p.M, p.N, a.ldc, pl.num_chunks, a.act_dtype, a.stream);
 }
 
 int read_gemm_status(unsigned int* out, bool clear);

@@ -258,6 +258,9 @@ bool gemv_supported(const MatmulArgs& a);
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
 bool gemv_stream_supported(const MatmulArgs& a, const mnq_tuning* tuning);
 int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning);
+// out[m, n] = sum over splits of partial[split][m][n] (fp32 planes, index order), as fp16 / bf16
+int launch_splitk_reduce(const float* partial, void* out, int M, int N, int64_t ldc, int splits, int32_t act_dtype,
+                         cudaStream_t stream);
 int read_device_status(unsigned int* out, bool clear);
 size_t gemv_stream_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant, bool* supported);
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);

@@ -330,6 +330,10 @@ def test_host_activations_and_output(mn, M, K, N, quant, g, adt):
                              asymmetric=adt == torch.float16, seed=M + K)
     d = L.to("cuda")
     want = mn._C.dequant_matmul(*d.args()).cpu()
+    # a K-split problem that shares the cached workspace: its arrival counters sit at the front of
+    # the workspace and must survive the host calls' staging copies
+    S = workloads.make_layer("s", 1, 4096, 256, seed=5).to("cuda")
+    split_want = mn._C.dequant_matmul(*S.args()).clone()
     x_host = L.x.clone().pin_memory()
     out_host = torch.empty((M, N), dtype=adt).pin_memory()
     for _ in range(3):   # successive calls share the cached workspace and its staging area
@@ -340,4 +344,5 @@ def test_host_activations_and_output(mn, M, K, N, quant, g, adt):
     fresh = mn._C.dequant_matmul(L.x, d.wq, d.scales, d.zeros, g, quant)      # pageable input, output allocated
     mn._C.synchronize()
     assert not fresh.is_cuda and torch.equal(fresh, want)
+    assert torch.equal(mn._C.dequant_matmul(*S.args()), split_want)
     assert mn._C.device_status() == 0
