@@ -23,9 +23,9 @@
 //               (fma(q-8, s, -z) on exact integers) and write the 128-byte-swizzled K-major
 //               tile the MMA reads; afterwards they read the accumulator back with tcgen05.ld
 //               and store out[m, n].
-// bf16 activations take this path only with one scale per row and no zeros: the tile then
-// holds the exact integers and the scale is applied to the fp32 accumulator (rounding
-// dequantised weights to bf16 would cost 1.6e-3 relative error by itself).
+// bf16 activations: with one scale per row and no zeros the tile holds the exact integers and
+// the scale is applied to the fp32 accumulator; otherwise every weight is kept as two bf16
+// values (BSplit below) and every MMA is issued twice.
 //
 // Few tiles (a long-K, narrow-N layer) leave SMs idle, so K can be split over grid.z: every
 // split writes its fp32 partial result to the workspace as [split][M][N], and a second small
@@ -308,6 +308,61 @@ template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
     }
 };
 
+// bf16 activations with group-wise scales (or zeros): a dequantised weight does not fit bf16's
+// 8 significant bits (rounding it would cost 1.6e-3 relative error by itself), and the MMA wants
+// both operands in one format.  So the weight w = fma(q, s, -z), computed in fp32, is split into
+// two bf16 values, hi = RN(w) and lo = RN(w - hi) (together good to 2^-16 relative), kept as
+// two tiles, and every MMA is issued twice, once per tile, into the same accumulator.
+struct BSplit {};
+
+template <int QUANT> struct SplitChunk;
+template <> struct SplitChunk<MNQ_INT4> {
+    static constexpr int WORDS = 1;
+    // q - 8 of the chunk's eight weights as floats, in k order
+    static __device__ __forceinline__ void ints(const uint32_t* w, float (&q)[8])
+    {
+        uint32_t P[4];
+        UnpackInt4<__nv_bfloat16>::run(w[0], P);   // (q0,q4) (q1,q5) (q2,q6) (q3,q7) as exact bf16 pairs
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            q[i] = __uint_as_float(P[i] << 16);
+            q[i + 4] = __uint_as_float(P[i] & 0xFFFF0000u);
+        }
+    }
+};
+template <> struct SplitChunk<MNQ_INT8> {
+    static constexpr int WORDS = 2;
+    static __device__ __forceinline__ void ints(const uint32_t* w, float (&q)[8])
+    {
+        constexpr float BIAS = 8388736.0f;   // 2^23 + 128
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t u = w[h] ^ 0x80808080u;
+            q[4 * h + 0] = __uint_as_float(prmt(u, 0x4B000000u, 0x7440u)) - BIAS;
+            q[4 * h + 1] = __uint_as_float(prmt(u, 0x4B000000u, 0x7441u)) - BIAS;
+            q[4 * h + 2] = __uint_as_float(prmt(u, 0x4B000000u, 0x7442u)) - BIAS;
+            q[4 * h + 3] = __uint_as_float(prmt(u, 0x4B000000u, 0x7443u)) - BIAS;
+        }
+    }
+};
+template <int QUANT>
+__device__ __forceinline__ void split_chunk(const uint32_t* w, float s, float nz, uint4& hi, uint4& lo)
+{
+    float q[8];
+    SplitChunk<QUANT>::ints(w, q);
+    uint32_t H[4], L[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = fmaf(q[2 * i], s, nz), b = fmaf(q[2 * i + 1], s, nz);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+        H[i] = b2_as_u32(h2);
+        const float ra = a - __uint_as_float(H[i] << 16), rb = b - __uint_as_float(H[i] & 0xFFFF0000u);
+        L[i] = b2_as_u32(__floats2bfloat162_rn(ra, rb));
+    }
+    hi = make_uint4(H[0], H[1], H[2], H[3]);
+    lo = make_uint4(L[0], L[1], L[2], L[3]);
+}
+
 // Staged element stores for the epilogue.
 template <typename E> struct StageIO;
 template <> struct StageIO<float> {
@@ -392,7 +447,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
 // of activation tiles.  Both CTAs run the same stage sequence; "tile ready" barriers live in
 // the leader (the peer's dequantise warps and TMA signal them remotely), "tile free" barriers
 // in each CTA (the leader commits to both).
-template <int QUANT, typename T, bool PAIR>
+// T: activation and output type.  TT: what the weight ring holds -- T itself (fp16: scale and zero
+// folded in; bf16: the exact integers, one scale per row applied to the accumulator), or BSplit
+// (bf16 activations, group-wise scales: two bf16 tiles per k-block, see above).
+template <int QUANT, typename T, typename TT, bool PAIR>
 __global__ void __launch_bounds__(352, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                     const __grid_constant__ CUtensorMap wmap)
@@ -402,6 +460,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr int KPR = 128 / KB_BYTES;                 // k-blocks covered by one raw stage (128 packed bytes per row)
     constexpr int RAW_BYTES = BN * 128;
     constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
+    constexpr bool SPLIT = std::is_same<TT, BSplit>::value;
+    constexpr int A_STAGE = SPLIT ? 2 * A_BYTES : A_BYTES;   // bytes of one weight-ring slot
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
@@ -431,7 +491,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const int b_rows = PAIR ? p.tokh / 2 : p.tokh;       // tokens of each activation tile this CTA loads
     const int b_bytes = b_rows * 128;
     const uint32_t tiles = (s_u32(smem_raw) + 1023u) & ~1023u;   // 1024-byte aligned: weight-tile ring
-    const uint32_t btiles = tiles + S * A_BYTES;                  // activation-tile ring
+    const uint32_t btiles = tiles + S * A_STAGE;                  // activation-tile ring
     const uint32_t raw0 = btiles + SB * p.nh * b_bytes;           // packed-weight ring
     const int R = p.raw_stages;
     const int NSEG = p.raw_segs;
@@ -529,7 +589,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             for (int kb = 0; kb < num_kb; ++kb) {   // kb: position in this CTA's k order
                 if (!(PAIR ? bar_wait_cluster(ready0 + 8 * d, dph) : bar_wait(ready0 + 8 * d, dph))) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = smem_desc_sw128(tiles + s * A_BYTES);
+                const uint64_t adesc = smem_desc_sw128(tiles + s * A_STAGE);
+                const uint64_t adesc_lo = smem_desc_sw128(tiles + s * A_STAGE + A_BYTES);   // SPLIT only
                 for (int h = 0; h < p.nh; ++h) {
                     const uint64_t bdesc = smem_desc_sw128(btiles + (uint32_t)(sb * p.nh + h) * (uint32_t)b_bytes);
                     const uint32_t acc = tmem_base + (uint32_t)(h * p.tokh);
@@ -537,6 +598,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     for (int j = 0; j < BK / 16; ++j) {   // 32 bytes along k = 2 descriptor address units
                         if (PAIR) umma_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         else umma(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if (SPLIT) {   // the low halves of the weights, same activations, same accumulator
+                            if (PAIR) umma_pair(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
+                            else umma(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
+                        }
                     }
                 }
                 // operands of this k-block are free once these MMAs have read them
@@ -641,11 +706,30 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     wd += wstep;
                     if (wd >= H) { wd -= H; wph ^= 1u; }
                 }
-                const uint32_t a_row = tiles + s * A_BYTES + row * 128;
+                const uint32_t a_row = tiles + s * A_STAGE + row * 128;
+                if constexpr (SPLIT) {
+                    // scale and -zero as fp32, from whichever 16-bit type the table holds
+                    float s32, nz32;
+                    if (p.scale_dtype == MNQ_BF16) {
+                        s32 = __uint_as_float(sz << 16);
+                        nz32 = -__uint_as_float(sz & 0xFFFF0000u);
+                    } else {
+                        s32 = __half2float(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
+                        nz32 = -__half2float(__ushort_as_half((unsigned short)(sz >> 16)));
+                    }
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
-                    sts128(a_row + xoff[c], o);
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 hi, lo;
+                        split_chunk<QUANT>(&w[c * SplitChunk<QUANT>::WORDS], s32, nz32, hi, lo);
+                        sts128(a_row + xoff[c], hi);
+                        sts128(a_row + A_BYTES + xoff[c], lo);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
+                        sts128(a_row + xoff[c], o);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
@@ -820,11 +904,10 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (a.K > (1 << 28) || a.N > (1 << 30) || a.M > (1 << 24)) return false;
     if (reinterpret_cast<uintptr_t>(a.wq) % 16 || reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8) return false;
     if (a.group_size < a.K && a.group_size % BK) return false;
-    if (a.act_dtype == MNQ_FP16) {
-        if (a.scale_dtype != MNQ_FP16) return false;            // the tile math is fp16 x fp16
-    } else {
-        if (a.group_size < a.K || a.zeros != nullptr) return false;   // bf16: scale in the epilogue only
-    }
+    if (a.act_dtype == MNQ_FP16 && a.scale_dtype != MNQ_FP16) return false;   // the fp16 tile math is fp16 x fp16
+    // bf16 activations: integer tile when one scale per row and no zeros, else two bf16 tiles per k-block
+    const bool split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    const size_t a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
     GemmPlan pl{};
     if (!tile_plan(a.M, a.N, tuning ? tuning->gemv_variant : 0, &pl)) return false;
 
@@ -856,15 +939,15 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     // big activation stages leave room for two packed stages (8 k-blocks of int4 ahead), small ones for three
     for (pl.raw_stages = b_stage >= 24 * 1024 ? 2 : 3; pl.raw_stages >= 1; --pl.raw_stages) {
         ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
-        if (ring + 1024 + 4 * A_BYTES > 226 * 1024) continue;
+        if (ring + 1024 + 2 * a_stage + 2 * A_BYTES > 226 * 1024) continue;
         budget = 226 * 1024 - 1024 - ring;
         bst = static_cast<int>(budget * 6 / 10 / b_stage);
         if (bst < 2) bst = 2;
         if (bst > 8) bst = 8;
-        if (budget >= b_stage * bst + 2 * A_BYTES) break;
+        if (budget >= b_stage * bst + 2 * a_stage) break;
     }
     if (pl.raw_stages < 1) return false;
-    int ast = static_cast<int>((budget - b_stage * bst) / A_BYTES);
+    int ast = static_cast<int>((budget - b_stage * bst) / a_stage);
     if (ast > 8) ast = 8;
     // deep rings: release operands a pair of k-blocks at a time (needs even stage counts)
     pl.commit_every = 1;
@@ -875,17 +958,17 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     }
     pl.b_stages = bst;
     pl.stages = ast;
-    pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * A_BYTES;
+    pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * a_stage;
     if (pl.smem < 1024 + 2 * 64 * BN * 4) pl.smem = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
     *out = pl;
     return true;
 }
 
-template <int QUANT, typename T>
+template <int QUANT, typename T, typename TT>
 int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensorMap& wmap, dim3 grid, size_t smem,
                     bool pair, cudaStream_t stream)
 {
-    auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, true> : &gemm_tcgen05_kernel<QUANT, T, false>;
+    auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, TT, true> : &gemm_tcgen05_kernel<QUANT, T, TT, false>;
     if (smem > 48 * 1024) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
@@ -989,8 +1072,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     GemmPlan pl;
     if (!plan_gemm(a, tuning, &pl))
         return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: the tensor-core kernel cannot take this problem "
-                                          "(needs K % 64 == 0, 16-byte aligned operands, group_size % 64 == 0 or >= K; "
-                                          "bf16 only with one scale per row and no zeros)");
+                                          "(needs K % 64 == 0, 16-byte aligned operands, group_size % 64 == 0 or >= K, "
+                                          "fp16 scales with fp16 activations)");
     GemmParams p{};
     p.wq = static_cast<const uint8_t*>(a.wq); p.scales = a.scales; p.zeros = a.zeros; p.out = a.out;
     p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
@@ -999,7 +1082,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
     p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.commit_every = pl.commit_every; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
-    p.epilogue_scale = (a.act_dtype == MNQ_BF16) ? 1 : 0;
+    const bool split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0);
     if (pl.splits > 1) {
@@ -1025,12 +1109,15 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     if (rc2) return rc2;
     dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m),
               static_cast<unsigned>(pl.splits));
+    const bool pair = pl.pair != 0;
     if (a.quant == MNQ_INT4) {
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
-        return launch_gemm_one<MNQ_INT4, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+        if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
     }
-    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
-    return launch_gemm_one<MNQ_INT8, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pl.pair != 0, a.stream);
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+    if (split_tiles) return launch_gemm_one<MNQ_INT8, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
 }
 
 }  // namespace mnq

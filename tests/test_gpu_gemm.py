@@ -36,6 +36,12 @@ CASES = [
     ("int8", 96, 160, 512, 64, False, torch.float16, torch.float16),
     ("int8", 64, 256, 512, 512, False, torch.bfloat16, torch.float16),    # config 4 style: scale in epilogue
     ("int4", 80, 128, 256, 256, False, torch.bfloat16, torch.bfloat16),
+    # bf16 activations with group-wise scales (and zeros): every weight as two bf16 values, two MMAs
+    ("int4", 64, 256, 512, 128, False, torch.bfloat16, torch.bfloat16),   # config 2 style
+    ("int4", 200, 384, 1024, 128, True, torch.bfloat16, torch.bfloat16),
+    ("int8", 96, 128, 256, 64, True, torch.bfloat16, torch.float16),
+    ("int4", 512, 512, 640, 128, True, torch.bfloat16, torch.bfloat16),   # CTA pairs
+    ("int8", 64, 128, 256, 256, True, torch.bfloat16, torch.bfloat16),    # one group per row, but zeros
 ]
 
 
@@ -114,6 +120,7 @@ def test_gemm_is_selected_for_prefill_shapes(mn):
     assert sp(512, 3584, 18944, 128, "int4") == "gemm"
     assert sp(64, 57344, 8192, 8192, "int8", torch.bfloat16, zeros=False) == "gemm"
     assert sp(64, 8192, 28672, 28672, "int8", torch.bfloat16, zeros=False) == "gemm"
+    assert sp(128, 14336, 4096, 128, "int4", torch.bfloat16, zeros=False) == "gemm"   # bf16, group-wise
     assert sp(40, 70, 96, 32, "int4") == "generic"        # K % 64 != 0
 
 
