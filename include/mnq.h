@@ -72,7 +72,8 @@ typedef struct mnq_tuning {
     int32_t split_k;             /* GEMV: number of K chunks */
     int32_t warps_per_cta;       /* GEMV: 16 output rows per warp at a time */
     int32_t gemv_variant;        /* kernel variant, 0 auto.  GEMV path: 1 register-prefetch kernel, 2 shared-memory
-                                    streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2) */
+                                    streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2),
+                                    3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it */
     int32_t piece_bytes;         /* streaming GEMV: packed bytes per row per stage (multiple of 64) */
     int32_t stages;              /* streaming GEMV: stages per warp (2..8) */
     int32_t ctas_per_sm;         /* streaming GEMV: resident CTAs per SM the plan assumes */

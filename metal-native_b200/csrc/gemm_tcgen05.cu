@@ -450,8 +450,11 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
 // T: activation and output type.  TT: what the weight ring holds -- T itself (fp16: scale and zero
 // folded in; bf16: the exact integers, one scale per row applied to the accumulator), or BSplit
 // (bf16 activations, group-wise scales: two bf16 tiles per k-block, see above).
-template <int QUANT, typename T, typename TT, bool PAIR>
-__global__ void __launch_bounds__(352, 1)
+// OCC2: tiles of at most 256 tokens leave half of the SM's shared memory, tensor memory and
+// registers unused, and a CTA of this kernel spends most of its time waiting (on loads, on the
+// MMA, on its own barriers): two CTAs per SM, each planned for half the shared memory.
+template <int QUANT, typename T, typename TT, bool PAIR, bool OCC2>
+__global__ void __launch_bounds__(352, OCC2 ? 2 : 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                     const __grid_constant__ CUtensorMap wmap)
 {
@@ -843,6 +846,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 struct GemmPlan {
     int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, raw_segs, commit_every, table_groups, tmem_cols, splits, kb_per_split;
     int pair;       // 1: clusters of two CTAs sharing each activation tile
+    int occ2;       // 1: planned for two CTAs per SM (at most half the shared memory, <= 256 tensor-memory columns)
     int tiles_n;    // CTAs along N (even when pair)
     size_t smem;
 };
@@ -851,18 +855,36 @@ constexpr int kMaxTableGroups = 64;   // 32 KB of scale table at most
 
 // K splits: the count that minimises waves x (k-blocks per split + fixed per-CTA cost) plus
 // the cost of writing and re-reading one fp32 result plane per split and of the second
-// launch, all in units of one k-block time (a little under a microsecond).
-int choose_splits(int64_t tiles, int num_kb, int sm_count, double plane_bytes)
+// launch (about 12 k-block times plus the plane traffic), all in units of one k-block time
+// (around half a microsecond).
+int choose_splits(int64_t tiles, int num_kb, int sm_count, double plane_bytes, int ctas_per_sm = 1,
+                  double* cost_out = nullptr)
 {
+    // two CTAs sharing an SM each run slower (about 1.35x: together they get ~1.5x the throughput)
+    const double slow = ctas_per_sm > 1 ? 1.35 : 1.0;
     int best = 1;
     double best_cost = 1e30;
     for (int sp = 1; sp <= kMaxSplits && sp <= num_kb; ++sp) {
-        const int64_t waves = (tiles * sp + sm_count - 1) / sm_count;
-        const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) +
-                            (sp > 1 ? 4.0 + sp * plane_bytes / 2.5e6 : 0.0);
+        const int64_t waves = (tiles * sp + static_cast<int64_t>(sm_count) * ctas_per_sm - 1) /
+                              (static_cast<int64_t>(sm_count) * ctas_per_sm);
+        const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) * slow +
+                            (sp > 1 ? 12.0 + sp * plane_bytes / 1.5e6 : 0.0);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
     }
+    if (cost_out) *cost_out = best_cost;
     return best;
+}
+
+// One or two CTAs per SM, and how many K splits: whichever the model above makes cheaper.
+int choose_occupancy_and_splits(bool occ2_ok, int64_t tiles, int num_kb, int sm_count, double plane_bytes, int* occ2)
+{
+    double c1 = 0, c2 = 0;
+    const int s1 = choose_splits(tiles, num_kb, sm_count, plane_bytes, 1, &c1);
+    *occ2 = 0;
+    if (!occ2_ok) return s1;
+    const int s2 = choose_splits(tiles, num_kb, sm_count, plane_bytes, 2, &c2);
+    if (c2 < c1) { *occ2 = 1; return s2; }
+    return s1;
 }
 
 inline size_t split_workspace_bytes(int splits, int64_t M, int64_t N)
@@ -913,7 +935,12 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
 
     const int num_kb = static_cast<int>(a.K / BK);
     const int64_t tiles = static_cast<int64_t>(pl.tiles_n) * pl.tiles_m;
-    int best = (tuning && tuning->split_k > 0) ? tuning->split_k : choose_splits(tiles, num_kb, a.sm_count, 4.0 * a.M * a.N);
+    // two CTAs per SM where a CTA needs at most half of everything (variant 3 forbids it)
+    const bool occ2_ok = !pl.pair && pl.tmem_cols <= 256 && !split_tiles && !(tuning && tuning->gemv_variant == 3);
+    int want_occ2 = 0;
+    int best = choose_occupancy_and_splits(occ2_ok, tiles, num_kb, a.sm_count, 4.0 * a.M * a.N, &want_occ2);
+    if (tuning && tuning->split_k > 0) best = tuning->split_k;
+    if (tuning && tuning->gemv_variant == 4) want_occ2 = occ2_ok ? 1 : 0;   // variant 4: two CTAs per SM whenever possible
     if (best > kMaxSplits) best = kMaxSplits;
     if (best > num_kb) best = num_kb;
     while (best > 1 && split_workspace_bytes(best, a.M, a.N) > (a.workspace ? a.workspace_bytes : 0))
@@ -933,42 +960,52 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     // shared memory: packed ring, scale table, then activation stages (one stage = the nh tiles
     // of a k-block; about 60 % of what is left, they have the longer latency to hide) and weight tiles
     const size_t b_stage = static_cast<size_t>(pl.nh) * (pl.pair ? pl.tokh / 2 : pl.tokh) * 128;
-    size_t ring = 0, budget = 0;
-    int bst = 0;
     pl.raw_segs = 1;
-    // big activation stages leave room for two packed stages (8 k-blocks of int4 ahead), small ones for three
-    for (pl.raw_stages = b_stage >= 24 * 1024 ? 2 : 3; pl.raw_stages >= 1; --pl.raw_stages) {
-        ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
-        if (ring + 1024 + 2 * a_stage + 2 * A_BYTES > 226 * 1024) continue;
-        budget = 226 * 1024 - 1024 - ring;
-        bst = static_cast<int>(budget * 6 / 10 / b_stage);
-        if (bst < 2) bst = 2;
-        if (bst > 8) bst = 8;
-        if (budget >= b_stage * bst + 2 * a_stage) break;
-    }
-    if (pl.raw_stages < 1) return false;
-    int ast = static_cast<int>((budget - b_stage * bst) / a_stage);
-    if (ast > 8) ast = 8;
-    // deep rings: release operands a pair of k-blocks at a time (needs even stage counts)
-    pl.commit_every = 1;
-    if (bst >= 4 && ast >= 4) {
-        pl.commit_every = 2;
-        bst &= ~1;
-        ast &= ~1;
-    }
-    pl.b_stages = bst;
-    pl.stages = ast;
-    pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * a_stage;
-    if (pl.smem < 1024 + 2 * 64 * BN * 4) pl.smem = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
+    const size_t epilogue_min = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
+    auto size_rings = [&](size_t total) -> bool {
+        size_t ring = 0, budget = 0;
+        int bst = 0;
+        // big activation stages leave room for two packed stages (8 k-blocks of int4 ahead), small ones for three
+        for (pl.raw_stages = b_stage >= 24 * 1024 ? 2 : 3; pl.raw_stages >= 1; --pl.raw_stages) {
+            ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
+            if (ring + 1024 + 2 * a_stage + 2 * b_stage > total) continue;
+            budget = total - 1024 - ring;
+            bst = static_cast<int>(budget * 6 / 10 / b_stage);
+            if (bst < 2) bst = 2;
+            if (bst > 8) bst = 8;
+            if (budget >= b_stage * bst + 2 * a_stage) break;
+        }
+        if (pl.raw_stages < 1) return false;
+        int ast = static_cast<int>((budget - b_stage * bst) / a_stage);
+        if (ast > 8) ast = 8;
+        // deep rings: release operands a pair of k-blocks at a time (needs even stage counts)
+        pl.commit_every = 1;
+        if (bst >= 4 && ast >= 4) {
+            pl.commit_every = 2;
+            bst &= ~1;
+            ast &= ~1;
+        }
+        pl.b_stages = bst;
+        pl.stages = ast;
+        pl.smem = 1024 + ring + b_stage * bst + static_cast<size_t>(ast) * a_stage;
+        if (pl.smem < epilogue_min) pl.smem = epilogue_min;
+        return pl.smem <= total;
+    };
+    pl.occ2 = 0;
+    if (want_occ2 && size_rings(112 * 1024)) pl.occ2 = 1;
+    else if (!size_rings(226 * 1024)) return false;
     *out = pl;
     return true;
 }
 
 template <int QUANT, typename T, typename TT>
 int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensorMap& wmap, dim3 grid, size_t smem,
-                    bool pair, cudaStream_t stream)
+                    bool pair, bool occ2, cudaStream_t stream)
 {
-    auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, TT, true> : &gemm_tcgen05_kernel<QUANT, T, TT, false>;
+    auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, TT, true, false> : &gemm_tcgen05_kernel<QUANT, T, TT, false, false>;
+    if constexpr (!std::is_same<TT, BSplit>::value) {
+        if (occ2 && !pair) kern = &gemm_tcgen05_kernel<QUANT, T, TT, false, true>;
+    }
     if (smem > 48 * 1024) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
@@ -1059,7 +1096,9 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
     GemmPlan pl{};
     if (!tile_plan(M, N, 0, &pl)) return 0;
     const int64_t tiles = static_cast<int64_t>(pl.tiles_n) * pl.tiles_m;
-    int splits = choose_splits(tiles, static_cast<int>(K / BK), 148, 4.0 * M * N);
+    int occ2 = 0;   // as plan_gemm
+    int splits = choose_occupancy_and_splits(!pl.pair && pl.tmem_cols <= 256, tiles, static_cast<int>(K / BK), 148,
+                                             4.0 * M * N, &occ2);
     const int64_t total_groups = group_size >= K ? 1 : (K + group_size - 1) / group_size;
     const int min_splits = static_cast<int>((total_groups + kMaxTableGroups - 1) / kMaxTableGroups);
     if (splits < min_splits) splits = min_splits;
@@ -1111,13 +1150,13 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
               static_cast<unsigned>(pl.splits));
     const bool pair = pl.pair != 0;
     if (a.quant == MNQ_INT4) {
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
-        if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
-        return launch_gemm_one<MNQ_INT4, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+        if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
     }
-    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
-    if (split_tiles) return launch_gemm_one<MNQ_INT8, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
-    return launch_gemm_one<MNQ_INT8, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, a.stream);
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+    if (split_tiles) return launch_gemm_one<MNQ_INT8, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
 }
 
 }  // namespace mnq
