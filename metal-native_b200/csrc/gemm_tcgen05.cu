@@ -868,7 +868,7 @@ int choose_splits(int64_t tiles, int num_kb, int sm_count, double plane_bytes, i
         const int64_t waves = (tiles * sp + static_cast<int64_t>(sm_count) * ctas_per_sm - 1) /
                               (static_cast<int64_t>(sm_count) * ctas_per_sm);
         const double cost = static_cast<double>(waves) * ((num_kb + sp - 1) / sp + 8) * slow +
-                            (sp > 1 ? 12.0 + sp * plane_bytes / 1.5e6 : 0.0);
+                            (sp > 1 ? 12.0 + sp * plane_bytes / 2.5e6 : 0.0);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
     }
     if (cost_out) *cost_out = best_cost;
