@@ -185,6 +185,20 @@ MNQ_API int mnq_dequant_matmul_static(const void* activations, const void* weigh
                               int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
                               int32_t scale_dtype, void* stream);
 
+/* Fused gate+up projection with the SwiGLU activation in the epilogue (decode sizes):
+ *   out[m, j] = silu(g) * u,  g = x[m,:] . W[j,:],  u = x[m,:] . W[H + j,:],  silu(g) = g / (1 + exp(-g))
+ * for the fused weight matrix W = [gate rows; up rows] of shape [2H, K] (scales and zeros [2H, G]).
+ * The reference computes the two projections with dequant_matmul and applies fast::swiglu(gate, up)
+ * as a separate kernel (include/metal_native/future/fast_ops.h:86-90, shaders/fused_swiglu.metal:48-84:
+ * fp32 math, 16-bit store); here a 16-row MMA tile holds 8 gate rows and their 8 up rows, so both
+ * sums of an output sit in one thread's accumulators and the [M, 2H] intermediate is never written.
+ * out is [M, H] in the activation dtype.  Takes what the streaming decode kernel takes with K unsplit
+ * (M <= 32 among others); otherwise MNQ_NOT_IMPLEMENTED. */
+MNQ_API int mnq_dequant_matmul_swiglu(const void* activations, const void* weights_packed, const void* scales,
+                                      const void* zeros, void* out, int64_t M, int64_t H, int64_t K, int64_t lda,
+                                      int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                                      int32_t scale_dtype, void* stream);
+
 /* The fused operator for activations and output in HOST memory (pinned for the copies to be
  * asynchronous), weights, scales and zeros resident on the device.  The reference's tensors live in
  * memory both the CPU and the GPU address (MTLStorageModeShared, src/core/tensor_helpers.mm:13-48), so

@@ -135,6 +135,7 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
     a.stream = static_cast<cudaStream_t>(stream);
     a.sm_count = 148;
     a.gather = GatherArgs{};
+    a.swiglu_h = 0;
 }
 
 int choose_path(const MatmulArgs& a)
@@ -286,6 +287,33 @@ int mnq_dequant_matmul_gather(const void* activations, const void* weights_packe
         return fail(MNQ_NOT_IMPLEMENTED,
                     "dequant_matmul_gather: only problems the streaming decode kernel takes (M <= 32, rows a multiple "
                     "of 16 bytes, group_size a multiple of the k step); gather other shapes with a collective");
+    return launch_gemv_stream(a, nullptr);
+}
+
+int mnq_dequant_matmul_swiglu(const void* activations, const void* weights_packed, const void* scales,
+                              const void* zeros, void* out, int64_t M, int64_t H, int64_t K, int64_t lda,
+                              int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                              int32_t scale_dtype, void* stream)
+{
+    if (H < 0) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_swiglu: negative dimension");
+    // the weights are the fused [2H, K] matrix; validate it as such, with an output of H columns
+    int rc = validate_matmul(activations, weights_packed, scales, out, true, M, 2 * H, K, lda, 2 * H, group_size,
+                             quant_type, act_dtype, scale_dtype);
+    if (rc) return rc;
+    if (ldc < H) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_swiglu: ldc must be >= H");
+    if (M == 0 || H == 0) return MNQ_SUCCESS;
+    if (K == 0) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_swiglu: K must be positive");
+    MatmulArgs a;
+    fill_args(a, activations, weights_packed, scales, zeros, out, M, 2 * H, K, lda, ldc, group_size, quant_type,
+              act_dtype, scale_dtype, nullptr, 0, stream);
+    rc = current_sm_count(&a.sm_count);
+    if (rc) return rc;
+    a.swiglu_h = H;
+    if (M > 32 || !gemv_stream_supported(a, nullptr))
+        return fail(MNQ_NOT_IMPLEMENTED,
+                    "dequant_matmul_swiglu: only problems the streaming decode kernel takes without splitting K "
+                    "(M <= 32, rows a multiple of 16 bytes, the activation block fits shared memory); "
+                    "use dequant_matmul and apply the activation separately");
     return launch_gemv_stream(a, nullptr);
 }
 

@@ -83,6 +83,7 @@ struct StreamParams {
     GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
     int gather_vec;       // the gathered buffers allow 16-byte stores at every column this call writes
     int defer_reduce;     // K chunks are added by a reduce kernel launched after this one: only store the partial sums
+    int swiglu_h;         // > 0: fused SwiGLU -- a 16-row tile is 8 gate rows (j) and the 8 up rows (H + j); out is [M, H]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -264,7 +265,8 @@ __device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&a
 // weights and keeps every product exact.
 template <int QUANT, typename T, int NT, int CH>
 __global__ void __launch_bounds__(NT >= 4 ? 256 : 512)
-gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap)
+gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap,
+                   const __grid_constant__ CUtensorMap wmap8)
 {
     using MT = __half;                                     // MMA element type
     constexpr bool CONVERT_X = !std::is_same<T, __half>::value;
@@ -337,8 +339,16 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         if (lane == 0) {
             const uint32_t bar = smem_u32(&bars[iss_stage]);
             mbar_expect_tx(bar, 16u * CH);
-            tma_load_2d(smem_u32(ring + iss_stage * STAGE_BYTES), &wmap, (byte_begin + iss_pc * CH) >> 2,
-                        (rb_first + iss_rbi) * 16, bar);
+            if (p.swiglu_h > 0) {
+                // stage rows 0..7: gate rows of this 8-row block; rows 8..15: the matching up rows
+                const int j0 = (rb_first + iss_rbi) * 8;
+                tma_load_2d(smem_u32(ring + iss_stage * STAGE_BYTES), &wmap8, (byte_begin + iss_pc * CH) >> 2, j0, bar);
+                tma_load_2d(smem_u32(ring + iss_stage * STAGE_BYTES + 8 * RS), &wmap8, (byte_begin + iss_pc * CH) >> 2,
+                            p.swiglu_h + j0, bar);
+            } else {
+                tma_load_2d(smem_u32(ring + iss_stage * STAGE_BYTES), &wmap, (byte_begin + iss_pc * CH) >> 2,
+                            (rb_first + iss_rbi) * 16, bar);
+            }
         }
         ++iss_count;
         if (++iss_stage == p.stages) iss_stage = 0;
@@ -457,9 +467,15 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         int g = e0 - row * p.segs;
 #pragma unroll
         for (int u = 0; u < SCB; ++u) {
-            const int n = rb_first * 16 + row;
+            int n = rb_first * 16 + row;
+            bool n_ok = n < p.N;
+            if (p.swiglu_h > 0) {   // tile row -> weight row: 8 gate rows, then their 8 up rows
+                const int lr = row & 15, j = (rb_first + (row >> 4)) * 8 + (lr & 7);
+                n = (lr < 8 ? 0 : p.swiglu_h) + j;
+                n_ok = j < p.swiglu_h;
+            }
             sp[u] = 0; zp[u] = 0;
-            if (row < nrb * 16 && n < p.N && seg0 + g < p.G) {
+            if (row < nrb * 16 && n_ok && seg0 + g < p.G) {
                 const size_t at = (size_t)n * p.G + seg0 + g;
                 sp[u] = __ldg(sc16 + at);
                 if (has_zero) zp[u] = __ldg(zr16 + at);
@@ -740,6 +756,22 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         const int rb = rb_first + rbi;
         const int n0 = rb * 16 + wr;
         const int n1 = n0 + 8;
+        if (p.swiglu_h > 0) {
+            // accumulators 0,1 are gate row j (tokens 2t, 2t+1), 2,3 the up row H + j: out = silu(gate) * up
+            const int j = rb * 8 + wr;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int m = nt * 8 + 2 * t + i;
+                    if (m < p.M && j < p.swiglu_h) {
+                        const float gte = CONVERT_X ? tot[nt][i] * x_up : tot[nt][i];
+                        const float upv = CONVERT_X ? tot[nt][i + 2] * x_up : tot[nt][i + 2];
+                        out[(size_t)m * p.ldc + j] = F16Traits<T>::from_float(gte / (1.f + __expf(-gte)) * upv);
+                    }
+                }
+            continue;
+        }
         if (p.num_chunks == 1) {
             if (stage_out) {
 #pragma unroll
@@ -899,7 +931,10 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     StreamPlan pl{};
     pl.nt = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
     pl.total_steps = static_cast<int>((row_bytes + kStepBytes - 1) / kStepBytes);
-    const int64_t row_blocks = (a.N + 15) / 16;
+    // fused SwiGLU: a 16-row tile is 8 gate rows plus their 8 up rows, and K is never split (the
+    // activation function needs the complete sums)
+    const bool swiglu = a.swiglu_h > 0;
+    const int64_t row_blocks = swiglu ? (a.swiglu_h + 7) / 8 : (a.N + 15) / 16;
 
     // 16 warps per CTA (measured: always better than 8 at equal work); the widest activation
     // tile is compiled for 256 threads
@@ -930,7 +965,9 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     // lot, so the model below also charges the staging, and a warp may take up to 8 row blocks.
     const bool many_tokens = pl.nt >= 2;
     int rbw_cap = many_tokens ? 8 : 2;
-    if (tuning && tuning->split_k > 0) {
+    if (swiglu) {
+        chunks = 1;
+    } else if (tuning && tuning->split_k > 0) {
         chunks = tuning->split_k;
     } else if (row_blocks <= kMaxCounters) {
         double best_cost = 1e30;
@@ -986,7 +1023,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
             // activation), then fewer warps
             if (pl.stages > 2) { --pl.stages; continue; }
             if (rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap >>= 1; continue; }
-            if (chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
+            if (!swiglu && chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
                 !(tuning && tuning->split_k > 0)) {
                 ++chunks;
                 continue;
@@ -1008,8 +1045,8 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
 }
 
 template <int QUANT, typename T, int NT, int CH>
-int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, dim3 grid, int threads, size_t smem,
-                      cudaStream_t stream)
+int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap8, dim3 grid, int threads,
+                      size_t smem, cudaStream_t stream)
 {
     auto* kern = &gemv_stream_kernel<QUANT, T, NT, CH>;
     if (smem > 48 * 1024) {
@@ -1031,18 +1068,18 @@ int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, dim3 grid,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, wmap), "gemv_stream launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, wmap, wmap8), "gemv_stream launch");
 }
 
 template <int QUANT, typename T>
-int launch_stream_nt(const StreamParams& p, const CUtensorMap& wmap, int nt, int ch, dim3 grid, int threads,
-                     size_t smem, cudaStream_t stream)
+int launch_stream_nt(const StreamParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap8, int nt, int ch, dim3 grid,
+                     int threads, size_t smem, cudaStream_t stream)
 {
     // 512-byte pieces only for NT == 1: wider activation tiles run out of registers
-    if (nt == 1 && ch == 512) return launch_stream_one<QUANT, T, 1, 512>(p, wmap, grid, threads, smem, stream);
-    if (nt == 1) return launch_stream_one<QUANT, T, 1, 256>(p, wmap, grid, threads, smem, stream);
-    if (nt == 2) return launch_stream_one<QUANT, T, 2, 256>(p, wmap, grid, threads, smem, stream);
-    return launch_stream_one<QUANT, T, 4, 256>(p, wmap, grid, threads, smem, stream);
+    if (nt == 1 && ch == 512) return launch_stream_one<QUANT, T, 1, 512>(p, wmap, wmap8, grid, threads, smem, stream);
+    if (nt == 1) return launch_stream_one<QUANT, T, 1, 256>(p, wmap, wmap8, grid, threads, smem, stream);
+    if (nt == 2) return launch_stream_one<QUANT, T, 2, 256>(p, wmap, wmap8, grid, threads, smem, stream);
+    return launch_stream_one<QUANT, T, 4, 256>(p, wmap, wmap8, grid, threads, smem, stream);
 }
 
 }  // namespace
@@ -1094,7 +1131,8 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.segs = pl.segs; p.xs_stride = pl.xs_stride;
     p.x_vec_ok = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && (a.lda % 8 == 0);
     p.rbw = pl.rbw; p.stages = pl.stages;
-    p.row_blocks = static_cast<int>((a.N + 15) / 16);
+    p.row_blocks = static_cast<int>(a.swiglu_h > 0 ? (a.swiglu_h + 7) / 8 : (a.N + 15) / 16);
+    p.swiglu_h = static_cast<int>(a.swiglu_h);
     p.gather = a.gather;
     // many tokens: the chunk planes are big and every unit would pay a fence and an atomic round
     // trip; a separate coalesced kernel adds them instead (not with the fused gather, whose peer
@@ -1119,9 +1157,18 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
                                         static_cast<uint64_t>(p.row_bytes), pl.piece_bytes / 4, 16,
                                         CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
+    // fused SwiGLU: the same tensor with 8-row boxes (a stage is filled by two copies)
+    CUtensorMap wmap8 = wmap;
+    if (a.swiglu_h > 0) {
+        const int rc8 = encode_tensor_map_2d(&wmap8, a.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4,
+                                             static_cast<uint64_t>(p.row_bytes) / 4, static_cast<uint64_t>(a.N),
+                                             static_cast<uint64_t>(p.row_bytes), pl.piece_bytes / 4, 8,
+                                             CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc8) return rc8;
+    }
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
-#define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
+#define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, wmap8, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
     int rcl;
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_GS(MNQ_INT4, __half);

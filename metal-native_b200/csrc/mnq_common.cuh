@@ -234,6 +234,7 @@ struct MatmulArgs {
     cudaStream_t stream;
     int32_t sm_count;
     GatherArgs gather;    // world == 0 unless called through mnq_dequant_matmul_gather
+    int64_t swiglu_h;     // > 0: weights are [2H, K] (gate rows, then up rows) and out is [M, H] = silu(gate) * up
 };
 
 // Split-K workspace layout, the same for every kernel and every problem shape: arrival

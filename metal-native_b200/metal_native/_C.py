@@ -71,6 +71,8 @@ def _load() -> ctypes.CDLL:
     L.mnq_dequantize_flat.argtypes = [vp, vp, vp, i64, i32, i32, vp]
     L.mnq_device_status.restype = ctypes.c_int
     L.mnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), i32]
+    L.mnq_dequant_matmul_swiglu.restype = ctypes.c_int
+    L.mnq_dequant_matmul_swiglu.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32, i32, vp]
     L.mnq_host_workspace_bytes.restype = sz
     L.mnq_host_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.mnq_dequant_matmul_host.restype = ctypes.c_int
@@ -271,6 +273,30 @@ def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size,
     return out
 
 
+def dequant_matmul_swiglu(activations, weights_packed, scales, zeros, group_size, quant_type, out=None):
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` for the fused weight matrix ``[Wg; Wu]`` of shape [2H, K]
+    (``mnq_dequant_matmul_swiglu``): the gate+up projection of an MLP with the reference's
+    ``fast::swiglu`` (``include/metal_native/future/fast_ops.h:86-90``) applied in the kernel's
+    epilogue.  Returns [M, H].  Decode sizes only (M <= 32); larger problems raise
+    NotImplemented: use ``dequant_matmul`` and apply the activation separately."""
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
+    if N % 2:
+        raise _invalid("dequant_matmul_swiglu: the fused weight matrix must have an even number of rows [2H, K]")
+    H = N // 2
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, H), dtype=x.dtype, device=dev)
+    elif out.shape != (M, H) or out.dtype != x.dtype or out.stride(1) != 1 or not out.is_cuda:
+        raise _invalid("dequant_matmul_swiglu: out must be a CUDA [M, H] tensor in the dtype of activations")
+    ldc = out.stride(0) if M > 1 else max(H, 1)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _check(_lib.mnq_dequant_matmul_swiglu(x.data_ptr(), w.data_ptr(), s.data_ptr(),
+                                              z.data_ptr() if z is not None else None, out.data_ptr(), M, H, K, lda,
+                                              ldc, g, q, _DT[x.dtype], _DT[s.dtype], stream))
+    return out
+
+
 GATHER_FLAG_WORDS = 32   # MNQ_GATHER_FLAG_WORDS of include/mnq.h
 
 
@@ -406,4 +432,4 @@ def exported_symbols() -> list[str]:
     return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
             "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather", "mnq_host_workspace_bytes",
-            "mnq_dequant_matmul_host"]
+            "mnq_dequant_matmul_host", "mnq_dequant_matmul_swiglu"]

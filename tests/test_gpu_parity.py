@@ -346,3 +346,37 @@ def test_host_activations_and_output(mn, M, K, N, quant, g, adt):
     assert not fresh.is_cuda and torch.equal(fresh, want)
     assert torch.equal(mn._C.dequant_matmul(*S.args()), split_want)
     assert mn._C.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K,Hd,quant,g,adt", [(1, 1024, 512, "int4", 128, torch.float16),
+                                                (1, 3584, 1000, "int4", 128, torch.float16),    # H not a multiple of 8
+                                                (4, 2048, 256, "int8", 2048, torch.bfloat16),
+                                                (16, 512, 384, "int4", 128, torch.bfloat16)])
+def test_fused_swiglu_epilogue(mn, M, K, Hd, quant, g, adt):
+    """gate+up projection with silu(gate) * up applied in the decode kernel's epilogue
+    (mnq_dequant_matmul_swiglu) against the oracle's fp32 projections followed by the reference's
+    SwiGLU formula (shaders/fused_swiglu.metal:48-84).  Two roundings of 16-bit inputs would give
+    the unfused pipeline about 2x the relative error of one projection; the fused kernel rounds
+    once, and is held to 2e-3 relative L2 (fp16) or the bf16 rounding floor."""
+    from metal_native import workloads
+    L = workloads.make_layer("t", M, K, 2 * Hd, quant_type=quant, group_size=g, act_dtype=adt,
+                             asymmetric=adt == torch.float16, seed=Hd + K)
+    ref = H.oracle_matmul(L).astype(np.float64)
+    gate, up = ref[:, :Hd], ref[:, Hd:]
+    want = gate / (1.0 + np.exp(-gate)) * up
+    d = L.to("cuda")
+    buf = torch.full((M + 2, Hd + 16), 5.0, dtype=adt, device="cuda")
+    out = buf[1:M + 1, 8:8 + Hd]
+    got = mn._C.dequant_matmul_swiglu(*d.args(), out=out)
+    mn._C.synchronize()
+    assert mn._C.device_status() == 0
+    got = got.float().cpu().numpy().astype(np.float64)
+    rel = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+    assert rel <= (2e-3 if adt == torch.float16 else 4e-3), rel
+    chk = buf.clone()
+    chk[1:M + 1, 8:8 + Hd] = 5.0
+    assert bool((chk == 5.0).all()), "kernel wrote outside its [M, H] output block"
+    # the unfused pipeline through the same library agrees to rounding
+    y = mn._C.dequant_matmul(*d.args()).float()
+    unfused = (torch.nn.functional.silu(y[:, :Hd]) * y[:, Hd:]).cpu().numpy()
+    assert np.linalg.norm(got - unfused) / np.linalg.norm(unfused) <= 6e-3
