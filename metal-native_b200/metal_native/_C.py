@@ -262,14 +262,16 @@ def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size,
     elif out.is_cuda or out.shape != (M, N) or out.dtype != x.dtype or not out.is_contiguous():
         raise _invalid("dequant_matmul: with host activations, out must be a contiguous host [M, N] tensor "
                        "in the dtype of activations")
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        nbytes = _lib.mnq_host_workspace_bytes(M, N, K, g, q)
-        ws = _workspace(dev, stream, nbytes)
-        _check(_lib.mnq_dequant_matmul_host(
-            x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
-            M, N, K, g, q, _DT[x.dtype], _DT[s.dtype], ws.data_ptr() if ws is not None else None,
-            ws.numel() if ws is not None else 0, stream))
+    if torch.cuda.current_device() != dev.index:
+        with torch.cuda.device(dev):
+            return _dequant_matmul_host(x, weights_packed, s, z, g, quant_type, out)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nbytes = _lib.mnq_host_workspace_bytes(M, N, K, g, q)
+    ws = _workspace(dev, stream, nbytes)
+    _check(_lib.mnq_dequant_matmul_host(
+        x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
+        M, N, K, g, q, _DT[x.dtype], _DT[s.dtype], ws.data_ptr() if ws is not None else None,
+        ws.numel() if ws is not None else 0, stream))
     return out
 
 
