@@ -147,19 +147,16 @@ template <> struct UnpackInt8<__half> {
 };
 
 template <> struct UnpackInt8<__nv_bfloat16> {
-    // bf16 has too few mantissa bits for 128 + (0..255); go through fp32:
-    // 0x4B0000uu = 2^23 + u, minus (2^23 + 128) = q exactly; q needs <= 8
-    // significant bits, so the top half of the fp32 is the exact bf16.
+    // bf16 has 8 significant bits: 128 + (0..127) is exact, 128 + (128..255) is not.  So a byte b
+    // becomes v = 0x4300 | (b & 0x7F) = 128 + (b mod 128) and c = 0x4300 | (b & 0x80), which is
+    // 128.0 for b >= 0 and 256.0 (0x4380) for b < 0; v - c = b exactly in both cases.
     static __device__ __forceinline__ void run(uint32_t w, uint32_t (&out)[2])
     {
-        const uint32_t u = w ^ 0x80808080u;
-        constexpr float BIAS = 8388736.0f;  // 2^23 + 128
-        const float f0 = __uint_as_float(prmt(u, 0x4B000000u, 0x7440u)) - BIAS;
-        const float f1 = __uint_as_float(prmt(u, 0x4B000000u, 0x7441u)) - BIAS;
-        const float f2 = __uint_as_float(prmt(u, 0x4B000000u, 0x7442u)) - BIAS;
-        const float f3 = __uint_as_float(prmt(u, 0x4B000000u, 0x7443u)) - BIAS;
-        out[0] = prmt(__float_as_uint(f0), __float_as_uint(f1), 0x7632u);
-        out[1] = prmt(__float_as_uint(f2), __float_as_uint(f3), 0x7632u);
+        const uint32_t lo7 = w & 0x7F7F7F7Fu, sgn = w & 0x80808080u;
+        const uint32_t v01 = prmt(lo7, 0x43434343u, 0x5140u), v23 = prmt(lo7, 0x43434343u, 0x7362u);
+        const uint32_t c01 = prmt(sgn, 0x43434343u, 0x5140u), c23 = prmt(sgn, 0x43434343u, 0x7362u);
+        out[0] = b2_as_u32(__hsub2(u32_as_b2(v01), u32_as_b2(c01)));
+        out[1] = b2_as_u32(__hsub2(u32_as_b2(v23), u32_as_b2(c23)));
     }
 };
 
