@@ -99,6 +99,32 @@ def test_gemm_single_cta_and_cta_pairs(mn, quant, M, N, K, g, adt, split, varian
     assert torch.equal(out, other)
 
 
+@pytest.mark.parametrize("quant,M,N,K,g,adt,split", [
+    ("int4", 64, 1024, 512, 128, torch.float16, 1),
+    ("int4", 200, 640, 1024, 128, torch.float16, 2),     # ragged tokens and rows, K split
+    ("int8", 96, 2048, 256, 256, torch.bfloat16, 1),     # integer tile, scale in the epilogue
+    ("int4", 256, 384, 2048, 128, torch.float16, 1),     # the largest tile that still allows two CTAs per SM
+])
+def test_gemm_one_and_two_ctas_per_sm(mn, quant, M, N, K, g, adt, split):
+    """Tiles of at most 256 tokens may run two CTAs per SM (variant 4 forces it, variant 3 forbids
+    it): same kernel body planned for half the shared memory, so the results are identical."""
+    from metal_native import workloads
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             asymmetric=adt == torch.float16, seed=N + M)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    t = _gemm_tuning(mn)
+    t.split_k = split
+    t.gemv_variant = 4
+    two = mn._C.dequant_matmul(*d.args(), tuning=t)
+    t.gemv_variant = 3
+    one = mn._C.dequant_matmul(*d.args(), tuning=t)
+    mn._C.synchronize()
+    assert mn._C.device_status() == 0
+    H.assert_close_to_oracle(two, ref, f"gemm two CTAs per SM {quant} {M}x{N}x{K}")
+    assert torch.equal(one, two)
+
+
 @pytest.mark.parametrize("split", [1, 2, 3, 5])
 def test_gemm_split_k_is_deterministic_and_reuses_workspace(mn, split):
     from metal_native import workloads
