@@ -65,6 +65,34 @@ typedef enum mnq_path {
     MNQ_PATH_GENERIC = 3  /* any shape or alignment; guarded scalar loads */
 } mnq_path;
 
+/* What is applied to the fp32 result before the store: the values of the reference's
+ * enum class MatmulEpilogue {None, Bias, BiasReLU, BiasSiLU, ResidualAdd}
+ * (include/metal_native/ops/fused_matmul.h:18-24). */
+typedef enum mnq_epilogue {
+    MNQ_EPI_NONE = 0,
+    MNQ_EPI_BIAS = 1,       /* out = x W^T + bias            bias [N], broadcast over rows */
+    MNQ_EPI_BIAS_RELU = 2,  /* out = max(0, x W^T + bias) */
+    MNQ_EPI_BIAS_SILU = 3,  /* out = silu(x W^T + bias), silu(v) = v / (1 + exp(-v)) */
+    MNQ_EPI_RESIDUAL = 4    /* out = x W^T + residual        residual [M, N] */
+} mnq_epilogue;
+
+/* Process-wide options (mnq_set_option / mnq_get_option). */
+typedef enum mnq_option {
+    /* Non-zero: the caller promises that weights_packed, scales and zeros are never written by
+     * work that is still in flight when an operator call starts (model state, loaded once).  The
+     * decode kernels then request their first weight tiles before they wait for the previous
+     * kernel in the stream to finish.  Default 0. */
+    MNQ_OPT_WEIGHTS_IMMUTABLE = 0,
+    /* Polls (of about 100 ns each) a sharded call waits for another rank before it gives up and
+     * sets bit 2 of the device status word.  Default 1 << 22 (about 0.4 s). */
+    MNQ_OPT_PEER_WAIT_POLLS = 1,
+    /* Largest token count M that takes the decode (GEMV) kernels; above it the tensor-core
+     * kernel runs.  1..32, default 32, initialised from the environment variable
+     * METAL_NATIVE_GEMV_MAX_M when set.  The reference's counterpart is the fixed
+     * `use_vecmat = (M <= 8)` (src/ops/matmul.mm:946). */
+    MNQ_OPT_GEMV_MAX_M = 2
+} mnq_option;
+
 /* Optional overrides for mnq_dequant_matmul_ex.  Zero in a field means "let the
  * library decide"; a zero-filled struct behaves like passing NULL. */
 typedef struct mnq_tuning {
@@ -133,6 +161,41 @@ MNQ_API int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_
                     int32_t quant_type, int32_t act_dtype, const void* activations,
                     const void* weights_packed, const void* scales, const void* zeros);
 
+/* Same question with the dtype of scales and zeros given (mnq_select_path assumes fp16): the
+ * tensor-core kernel multiplies fp16 activations by fp16 scales only, so fp16 activations with
+ * bf16 scales and M above the decode threshold run the any-shape kernel (MNQ_PATH_GENERIC),
+ * which is correct but slow. */
+MNQ_API int mnq_select_path_ex(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size,
+                       int32_t quant_type, int32_t act_dtype, int32_t scale_dtype, const void* activations,
+                       const void* weights_packed, const void* scales, const void* zeros);
+
+/* Sets / reads a process-wide option (mnq_option).  mnq_set_option returns MNQ_INVALID_ARGUMENT
+ * for an unknown option or a value outside its range; mnq_get_option returns -1 for an unknown
+ * option.  Thread-safe; a call already enqueued keeps the value it was launched with. */
+MNQ_API int mnq_set_option(int32_t option, int64_t value);
+MNQ_API int64_t mnq_get_option(int32_t option);
+
+/* Fused dequantise + matmul with an epilogue, and optionally an fp32 output.  Replaces
+ *   MNTensor fused_matmul(a, b, epilogue, bias, residual, ...)
+ * (include/metal_native/ops/fused_matmul.h:64-70) for the quantised operator: the reference
+ * applies its epilogues to the unquantised matmul (shaders/matmul_fused_epilogue.metal:97-124);
+ * here the same arithmetic follows the dequant-matmul's fp32 accumulation, before the only store:
+ * fp32 add of bias[n] (or residual[m, n]), the activation in fp32, one rounding to the output type.
+ *   epilogue  an mnq_epilogue value; bias is [N] and residual [M, ldr] (ldr >= N, in elements), both
+ *             in the activation dtype; the one the epilogue does not use may be NULL.  As in the
+ *             reference a missing required tensor is MNQ_INVALID_ARGUMENT.
+ *   out_dtype the activation dtype (then out is what mnq_dequant_matmul returns, with the epilogue
+ *             applied) or MNQ_FP32: out is float [M, ldc] holding the value before the final
+ *             rounding -- the accumulators themselves, for checking a 16-bit kernel against an fp32
+ *             expectation without the output rounding in the way.
+ * Other arguments as for mnq_dequant_matmul. */
+MNQ_API int mnq_dequant_matmul_fused(const void* activations, const void* weights_packed, const void* scales,
+                             const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                             int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                             int32_t scale_dtype, int32_t out_dtype, int32_t epilogue, const void* bias,
+                             const void* residual, int64_t ldr, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* Dequantise a whole weight matrix with the fused operator's formula (scale and
  * zero, [N, ceil(K/g)] indexing): out[n,k] = (q-8)*s - z  or  q*s - z, evaluated
  * in fp32 as a product then a subtraction (the product is exact), then rounded to nearest even if out_dtype is
@@ -153,10 +216,12 @@ MNQ_API int mnq_dequantize_flat(const void* input, const void* scales_fp16, void
                         int64_t num_elements, int32_t group_size, int32_t quant_type, void* stream);
 
 /* Reads (and, if `clear` is non-zero, resets) the device-side status word of the
- * current device; synchronises the device.  Bit 0: a kernel gave up a bounded wait
- * for an asynchronous copy and left its output incomplete (reported by the shim as
- * TimeoutError, the reference's MetalNativeError::TimeoutError,
- * include/metal_native/core/error.h:28).  No counterpart call in the reference. */
+ * current device; synchronises the device.  Bits 0 and 1: a decode / tensor-core kernel gave
+ * up a bounded wait for an asynchronous copy; bit 2: a sharded call gave up waiting for
+ * another rank (MNQ_OPT_PEER_WAIT_POLLS).  In each case the output of that call is incomplete
+ * (reported by the shim as TimeoutError, the reference's MetalNativeError::TimeoutError,
+ * include/metal_native/core/error.h:28); the arrival counters of the workspace are back at
+ * zero, so the workspace can be used again.  No counterpart call in the reference. */
 MNQ_API int mnq_device_status(uint32_t* status, int32_t clear);
 
 /* Fused dequantise + matmul for callers that cannot allocate device memory.

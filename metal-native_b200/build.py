@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "metal_native" / "lib"
 LIB = LIB_DIR / "libmnq.so"
-SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemv_stream.cu", "gemm_tcgen05.cu", "sharded.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemv_stream.cu", "gemm_tcgen05.cu", "no_alloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -31,7 +31,10 @@ def find_nvcc() -> str:
 
 
 def sources() -> list[Path]:
-    return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+    missing = [s for s in SOURCES if not (CSRC / s).exists()]
+    if missing:
+        raise RuntimeError(f"listed sources are missing from {CSRC}: {missing}")
+    return [CSRC / s for s in SOURCES]
 
 
 def is_stale() -> bool:
@@ -42,19 +45,23 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, out: Path | None = None, extra_flags: list[str] | None = None) -> Path:
+    """Compiles and links the library.  `out` and `extra_flags` build a variant elsewhere (for
+    example with -D switches) without touching the in-tree library."""
+    variant = out is not None or bool(extra_flags)
+    if not variant and not force and not is_stale():
         return LIB
     nvcc = find_nvcc()
-    LIB_DIR.mkdir(parents=True, exist_ok=True)
-    obj_dir = HERE / "build"
-    obj_dir.mkdir(exist_ok=True)
+    target = Path(out) if out is not None else LIB
+    target.parent.mkdir(parents=True, exist_ok=True)
+    obj_dir = HERE / "build" / ("variant_" + target.parent.name if variant else "")
+    obj_dir.mkdir(parents=True, exist_ok=True)
     procs = []
     objs = []
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *(extra_flags or []), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -68,16 +75,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    tmp = LIB.with_suffix(".so.tmp")
+    tmp = target.with_suffix(".so.tmp")
     link = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"]
     subprocess.run(link, check=True)
-    os.replace(tmp, LIB)
-    return LIB
+    os.replace(tmp, target)
+    return target
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--out", default=None, help="write the library here instead of metal_native/lib/libmnq.so")
+    ap.add_argument("--flag", action="append", default=[], help="extra nvcc flag (repeatable), e.g. --flag=-DNAME")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, Path(a.out) if a.out else None, a.flag))

@@ -6,7 +6,11 @@
 #include <cuda.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <atomic>
+#include <mutex>
 
 #include "mnq_common.cuh"
 
@@ -29,6 +33,42 @@ int fail(int status, const char* fmt, ...)
     vsnprintf(g_error, sizeof g_error, fmt, ap);
     va_end(ap);
     return status;
+}
+
+// ---------------------------------------------------------------------------
+// Process-wide options
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kNumOptions = 3;
+std::atomic<int64_t> g_options[kNumOptions] = {{0}, {int64_t(1) << 22}, {32}};
+std::once_flag g_options_env;
+
+bool option_in_range(int option, int64_t v)
+{
+    switch (option) {
+        case MNQ_OPT_WEIGHTS_IMMUTABLE: return v == 0 || v == 1;
+        case MNQ_OPT_PEER_WAIT_POLLS: return v >= 1 && v <= (int64_t(1) << 31) - 1;
+        case MNQ_OPT_GEMV_MAX_M: return v >= 1 && v <= 32;
+        default: return false;
+    }
+}
+// The decode / tensor-core threshold may come from the environment, read once; the reference
+// advertises its per-phase strategies the same way, as strings (src/inference/phase_pipeline.mm:28-40).
+void options_from_env()
+{
+    const char* e = getenv("METAL_NATIVE_GEMV_MAX_M");
+    if (!e || !*e) return;
+    char* end = nullptr;
+    const long v = strtol(e, &end, 10);
+    if (end && *end == 0 && option_in_range(MNQ_OPT_GEMV_MAX_M, v)) g_options[MNQ_OPT_GEMV_MAX_M].store(v);
+}
+}  // namespace
+
+int64_t option_value(int option)
+{
+    std::call_once(g_options_env, options_from_env);
+    if (option < 0 || option >= kNumOptions) return -1;
+    return g_options[option].load(std::memory_order_relaxed);
 }
 
 int check_cuda(cudaError_t e, const char* what)
@@ -136,22 +176,27 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
     a.sm_count = 148;
     a.gather = GatherArgs{};
     a.swiglu_h = 0;
+    a.epi = Epilogue{};
 }
 
+// Decode kernels up to the threshold (MNQ_OPT_GEMV_MAX_M, at most the 32 tokens they are built
+// for), the tensor-core kernel above it, the any-shape kernel for whatever neither takes.
 int choose_path(const MatmulArgs& a)
 {
-    if (a.M <= 32 && gemv_supported(a)) return MNQ_PATH_GEMV;
-    if (a.M > 32 && gemm_supported(a)) return MNQ_PATH_GEMM;
+    const int64_t gemv_max_m = option_value(MNQ_OPT_GEMV_MAX_M);
+    if (a.M <= gemv_max_m && gemv_supported(a)) return MNQ_PATH_GEMV;
+    if (a.M > gemv_max_m && gemm_supported(a)) return MNQ_PATH_GEMM;
+    if (a.M <= 32 && gemv_supported(a)) return MNQ_PATH_GEMV;   // e.g. K not a multiple of 64
     return MNQ_PATH_GENERIC;
 }
 
 template <typename T>
-__global__ void zero_rows_kernel(T* out, int64_t M, int64_t N, int64_t ldc)
+__global__ void zero_rows_kernel(void* out, int64_t M, int64_t N, int64_t ldc, const Epilogue epi)
 {
     const int64_t total = M * N;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x)
-        out[(i / N) * ldc + (i % N)] = T(0);
+        store_result<T>(epi, out, ldc, static_cast<int>(i / N), static_cast<int>(i % N), 0.f);
 }
 
 }  // namespace
@@ -194,30 +239,53 @@ int mnq_device_status(uint32_t* status, int32_t clear)
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
     if (M > 32) return gemm_workspace_bytes(M, N, K, group_size);
-    return gemv_workspace_bytes(M, N, K, group_size, quant_type);
+    // M <= 32 takes either family, depending on MNQ_OPT_GEMV_MAX_M: enough for both
+    const size_t a = gemv_workspace_bytes(M, N, K, group_size, quant_type);
+    const size_t b = M > option_value(MNQ_OPT_GEMV_MAX_M) ? gemm_workspace_bytes(M, N, K, group_size) : 0;
+    return a > b ? a : b;
 }
 
-int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size, int32_t quant_type,
-                    int32_t act_dtype, const void* activations, const void* weights_packed,
-                    const void* scales, const void* zeros)
+int mnq_set_option(int32_t option, int64_t value)
+{
+    option_value(option);   // the environment is read before the first explicit setting
+    if (option < 0 || option >= kNumOptions) return fail(MNQ_INVALID_ARGUMENT, "set_option: unknown option %d", option);
+    if (!option_in_range(option, value))
+        return fail(MNQ_INVALID_ARGUMENT, "set_option: value %lld is out of range for option %d", (long long)value, option);
+    g_options[option].store(value);
+    return MNQ_SUCCESS;
+}
+
+int64_t mnq_get_option(int32_t option) { return option_value(option); }
+
+int mnq_select_path_ex(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size, int32_t quant_type,
+                       int32_t act_dtype, int32_t scale_dtype, const void* activations, const void* weights_packed,
+                       const void* scales, const void* zeros)
 {
     const int rc = validate_matmul(activations, weights_packed, scales, nullptr, false, M, N, K, lda, N,
-                                   group_size, quant_type, act_dtype, MNQ_FP16);
+                                   group_size, quant_type, act_dtype, scale_dtype);
     if (rc) return -rc;
     MatmulArgs a;
     fill_args(a, activations, weights_packed, scales, zeros, nullptr, M, N, K, lda, N, group_size,
-              quant_type, act_dtype, MNQ_FP16, nullptr, 0, nullptr);
+              quant_type, act_dtype, scale_dtype, nullptr, 0, nullptr);
     // the answer must not depend on how much workspace a later call brings
     a.workspace = reinterpret_cast<void*>(uintptr_t(256));
     a.workspace_bytes = mnq_workspace_bytes(M, N, K, group_size, quant_type);
     return choose_path(a);
 }
 
-int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, const void* scales,
-                          const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
-                          int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
-                          int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream,
-                          const mnq_tuning* tuning)
+int mnq_select_path(int64_t M, int64_t N, int64_t K, int64_t lda, int32_t group_size, int32_t quant_type,
+                    int32_t act_dtype, const void* activations, const void* weights_packed,
+                    const void* scales, const void* zeros)
+{
+    return mnq_select_path_ex(M, N, K, lda, group_size, quant_type, act_dtype, MNQ_FP16, activations, weights_packed,
+                              scales, zeros);
+}
+
+static int run_matmul(const void* activations, const void* weights_packed, const void* scales,
+                      const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                      int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                      const mnq_tuning* tuning, const Epilogue& epi)
 {
     int rc = validate_matmul(activations, weights_packed, scales, out, true, M, N, K, lda, ldc, group_size,
                              quant_type, act_dtype, scale_dtype);
@@ -227,16 +295,17 @@ int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, c
     MatmulArgs a;
     fill_args(a, activations, weights_packed, scales, zeros, out, M, N, K, lda, ldc, group_size, quant_type,
               act_dtype, scale_dtype, workspace, workspace_bytes, stream);
+    a.epi = epi;
     rc = current_sm_count(&a.sm_count);
     if (rc) return rc;
 
-    if (K == 0) {  // empty reduction: the sum over no terms
+    if (K == 0) {  // empty reduction: the sum over no terms, then the epilogue
         const int64_t total = M * N;
         const int grid = static_cast<int>(total / 256 + 1 > 1024 ? 1024 : total / 256 + 1);
         if (act_dtype == MNQ_FP16)
-            zero_rows_kernel<<<grid, 256, 0, a.stream>>>(static_cast<__half*>(out), M, N, ldc);
+            zero_rows_kernel<__half><<<grid, 256, 0, a.stream>>>(out, M, N, ldc, epi);
         else
-            zero_rows_kernel<<<grid, 256, 0, a.stream>>>(static_cast<__nv_bfloat16*>(out), M, N, ldc);
+            zero_rows_kernel<__nv_bfloat16><<<grid, 256, 0, a.stream>>>(out, M, N, ldc, epi);
         return check_cuda(cudaGetLastError(), "zero-fill launch");
     }
 
@@ -247,6 +316,46 @@ int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, c
         case MNQ_PATH_GENERIC: return launch_generic(a);
         default: return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: unknown path %d", path);
     }
+}
+
+int mnq_dequant_matmul_ex(const void* activations, const void* weights_packed, const void* scales,
+                          const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                          int32_t scale_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                          const mnq_tuning* tuning)
+{
+    return run_matmul(activations, weights_packed, scales, zeros, out, M, N, K, lda, ldc, group_size, quant_type,
+                      act_dtype, scale_dtype, workspace, workspace_bytes, stream, tuning, Epilogue{});
+}
+
+int mnq_dequant_matmul_fused(const void* activations, const void* weights_packed, const void* scales,
+                             const void* zeros, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                             int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
+                             int32_t scale_dtype, int32_t out_dtype, int32_t epilogue, const void* bias,
+                             const void* residual, int64_t ldr, void* workspace, size_t workspace_bytes,
+                             void* stream)
+{
+    // include/metal_native/ops/fused_matmul.h:51-52: a required epilogue tensor that is missing is InvalidArgument
+    if (epilogue < MNQ_EPI_NONE || epilogue > MNQ_EPI_RESIDUAL)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_fused: unknown epilogue %d", epilogue);
+    const bool needs_bias = epilogue == MNQ_EPI_BIAS || epilogue == MNQ_EPI_BIAS_RELU || epilogue == MNQ_EPI_BIAS_SILU;
+    if (needs_bias && !bias && N > 0)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_fused: this epilogue requires a bias tensor [N]");
+    if (epilogue == MNQ_EPI_RESIDUAL) {
+        if (!residual && M > 0 && N > 0)
+            return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_fused: ResidualAdd requires a residual tensor [M, N]");
+        if (ldr < N) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_fused: ldr must be >= N");
+    }
+    if (out_dtype != act_dtype && out_dtype != MNQ_FP32)
+        return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_fused: out_dtype must be the activation dtype or Float32");
+    Epilogue epi{};
+    epi.kind = epilogue;
+    epi.out_f32 = out_dtype == MNQ_FP32 ? 1 : 0;
+    epi.bias = needs_bias ? bias : nullptr;
+    epi.residual = epilogue == MNQ_EPI_RESIDUAL ? residual : nullptr;
+    epi.ldr = ldr;
+    return run_matmul(activations, weights_packed, scales, zeros, out, M, N, K, lda, ldc, group_size, quant_type,
+                      act_dtype, scale_dtype, workspace, workspace_bytes, stream, nullptr, epi);
 }
 
 int mnq_dequant_matmul_gather(const void* activations, const void* weights_packed, const void* scales,

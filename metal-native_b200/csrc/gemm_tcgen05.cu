@@ -86,6 +86,7 @@ struct GemmParams {
     int kb_per_split;   // 64-k blocks per split
     float* partial;     // [splits][M][N] fp32 (splits > 1)
     int vec_store;      // bit 0: out allows 16-byte stores, bit 1: the split-K planes do
+    Epilogue epi;       // applied to the fp32 result before the store; fp32 output mode
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -388,10 +389,13 @@ template <> struct StageIO<__nv_bfloat16> {
 // each warp drops its 32 x 32 block as [token][row], then all threads copy the slab out as
 // 16-byte pieces of whole 128-row lines.  `vec`: destination base and leading dimension allow
 // 16-byte stores; otherwise the copy is element by element (still whole lines per warp).
-template <typename E>
+// T: the activation type (what bias and residual hold).  FINAL: the values stored are the
+// operator's result, so the epilogue is applied while they are staged; otherwise (a K split's
+// fp32 plane) they are stored as they are.
+template <typename E, typename T, bool FINAL>
 __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int half, int row, int e, int tok,
                                               uint32_t stage0, float scale, E* dst, size_t ld, int n0, int N, int m0,
-                                              int M, bool vec)
+                                              int M, bool vec, const Epilogue& epi)
 {
     constexpr int RB = BN * (int)sizeof(E);    // bytes per staged token row
     constexpr int PPR = RB / 16;               // 16-byte pieces per row
@@ -406,8 +410,18 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
             tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const uint32_t at = stage + (uint32_t)(half * 32 * RB) + (uint32_t)row * (uint32_t)sizeof(E);
+            if (FINAL && epi.kind != MNQ_EPI_NONE) {
+                const bool n_ok = n0 + row < N;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) StageIO<E>::put(at + i * RB, StageIO<E>::from(__uint_as_float(v[i]) * scale));
+                for (int i = 0; i < 32; ++i) {
+                    float val = __uint_as_float(v[i]) * scale;
+                    if (n_ok && m0 + c0 + i < M) val = epilogue_value<T>(epi, val, m0 + c0 + i, n0 + row);
+                    StageIO<E>::put(at + i * RB, StageIO<E>::from(val));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) StageIO<E>::put(at + i * RB, StageIO<E>::from(__uint_as_float(v[i]) * scale));
+            }
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (vec) {
@@ -771,12 +785,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             // with K split, this CTA's result goes to its [M][N] plane of the workspace instead;
             // the rings are idle now (every MMA has completed), so their memory stages the tile
             if (p.splits > 1)
-                epilogue_tile<float>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
-                                     p.partial + (size_t)blockIdx.z * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
-                                     (p.vec_store & 2) != 0);
+                epilogue_tile<float, T, false>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
+                                               p.partial + (size_t)blockIdx.z * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
+                                               (p.vec_store & 2) != 0, p.epi);
+            else if (p.epi.out_f32)
+                epilogue_tile<float, T, true>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
+                                              static_cast<float*>(p.out), (size_t)p.ldc, n0, p.N, m0, p.M,
+                                              (p.vec_store & 4) != 0, p.epi);
             else
-                epilogue_tile<T>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale, static_cast<T*>(p.out),
-                                 (size_t)p.ldc, n0, p.N, m0, p.M, (p.vec_store & 1) != 0);
+                epilogue_tile<T, T, true>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale, static_cast<T*>(p.out),
+                                          (size_t)p.ldc, n0, p.N, m0, p.M, (p.vec_store & 1) != 0, p.epi);
         }
     }
     if (failed && lane == 0) atomicOr(&g_gemm_status, 2u);
@@ -798,9 +816,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 // out[m, n] = sum over splits of partial[z][m][n], splits added in index order (deterministic).
 // VEC: eight consecutive n per thread as two 16-byte loads per split and one 16-byte store.
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, T* __restrict__ out, int M,
-                                                            int N, int64_t ldc, int splits)
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out_v, int M,
+                                                            int N, int64_t ldc, int splits, const Epilogue epi)
 {
+    T* out = static_cast<T*>(out_v);   // (VEC is never chosen with the fp32 output mode)
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the planes are the previous kernel's output
     const size_t plane = (size_t)M * N;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -827,6 +846,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
                     }
             }
             const size_t m = e / N, n = e % N;
+            if (epi.kind != MNQ_EPI_NONE) {
+                a.x = epilogue_value<T>(epi, a.x, (int)m, (int)n);     a.y = epilogue_value<T>(epi, a.y, (int)m, (int)n + 1);
+                a.z = epilogue_value<T>(epi, a.z, (int)m, (int)n + 2); a.w = epilogue_value<T>(epi, a.w, (int)m, (int)n + 3);
+                b.x = epilogue_value<T>(epi, b.x, (int)m, (int)n + 4); b.y = epilogue_value<T>(epi, b.y, (int)m, (int)n + 5);
+                b.z = epilogue_value<T>(epi, b.z, (int)m, (int)n + 6); b.w = epilogue_value<T>(epi, b.w, (int)m, (int)n + 7);
+            }
             union { T h[8]; uint4 u; } pk;
             pk.h[0] = F16Traits<T>::from_float(a.x); pk.h[1] = F16Traits<T>::from_float(a.y);
             pk.h[2] = F16Traits<T>::from_float(a.z); pk.h[3] = F16Traits<T>::from_float(a.w);
@@ -838,7 +863,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
         for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < plane; e += stride) {
             float acc = __ldcs(partial + e);
             for (int z = 1; z < splits; ++z) acc += __ldcs(partial + z * plane + e);
-            out[(e / N) * ldc + (e % N)] = F16Traits<T>::from_float(acc);
+            store_result<T>(epi, out_v, ldc, (int)(e / N), (int)(e % N), acc);
         }
     }
 }
@@ -1034,16 +1059,16 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     if (rc || p.splits <= 1) return rc;
     // second launch: add the splits' planes and write the output
     return launch_splitk_reduce(p.partial, p.out, p.M, p.N, p.ldc, p.splits,
-                                std::is_same<T, __nv_bfloat16>::value ? MNQ_BF16 : MNQ_FP16, stream);
+                                std::is_same<T, __nv_bfloat16>::value ? MNQ_BF16 : MNQ_FP16, p.epi, stream);
 }
 
 }  // namespace
 
 template <typename T>
-static int launch_reduce_t(const float* partial, void* out_v, int M, int N, int64_t ldc, int splits, cudaStream_t stream)
+static int launch_reduce_t(const float* partial, void* out, int M, int N, int64_t ldc, int splits, const Epilogue& epi,
+                           cudaStream_t stream)
 {
-    T* out = static_cast<T*>(out_v);
-    const bool vec = N % 8 == 0 && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const bool vec = N % 8 == 0 && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && !epi.out_f32;
     const size_t work = vec ? (size_t)M * N / 8 : (size_t)M * N;
     size_t blocks = (work + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
@@ -1058,14 +1083,14 @@ static int launch_reduce_t(const float* partial, void* out_v, int M, int N, int6
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     auto* red = vec ? &splitk_reduce_kernel<T, true> : &splitk_reduce_kernel<T, false>;
-    return check_cuda(cudaLaunchKernelEx(&cfg, red, partial, out, M, N, (long long)ldc, splits), "splitk_reduce launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, red, partial, out, M, N, (long long)ldc, splits, epi), "splitk_reduce launch");
 }
 
 int launch_splitk_reduce(const float* partial, void* out, int M, int N, int64_t ldc, int splits, int32_t act_dtype,
-                         cudaStream_t stream)
+                         const Epilogue& epi, cudaStream_t stream)
 {
-    if (act_dtype == MNQ_BF16) return launch_reduce_t<__nv_bfloat16>(partial, out, M, N, ldc, splits, stream);
-    return launch_reduce_t<__half>(partial, out, M, N, ldc, splits, stream);
+    if (act_dtype == MNQ_BF16) return launch_reduce_t<__nv_bfloat16>(partial, out, M, N, ldc, splits, epi, stream);
+    return launch_reduce_t<__half>(partial, out, M, N, ldc, splits, epi, stream);
 }
 
 int read_gemm_status(unsigned int* out, bool clear)
@@ -1092,7 +1117,7 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
 {
     // What plan_gemm asks for on a 148-SM part (B200).  On a device where it would split
     // further, the plan falls back to the number of splits the given workspace can hold.
-    if (M <= 32 || N < 1 || K < BK || K % BK) return 0;
+    if (M < 1 || N < 1 || K < BK || K % BK) return 0;
     GemmPlan pl{};
     if (!tile_plan(M, N, 0, &pl)) return 0;
     const int64_t tiles = static_cast<int64_t>(pl.tiles_n) * pl.tiles_m;
@@ -1124,7 +1149,9 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     const bool split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
     p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
-    p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0);
+    p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0) |
+                  ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 4 == 0) ? 4 : 0);
+    p.epi = a.epi;
     if (pl.splits > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);

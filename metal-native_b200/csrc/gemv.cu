@@ -46,6 +46,7 @@ struct GemvParams {
     int steps_per_group;  // group_size / STEP, INT_MAX for a single group
     int G;                // scale/zero columns
     int scale_dtype;
+    Epilogue epi;         // applied to the fp32 result before the store
     int steps_per_chunk;  // chunk length in steps
     int total_steps;      // ceil(K / STEP)
     int num_chunks;
@@ -304,7 +305,6 @@ gemv_mma_kernel(const GemvParams p)
 
     // ---- epilogue --------------------------------------------------------------------
     // Accumulator i of tile nt is output (m = nt*8 + 2t + (i&1), n = n0 or n1).
-    T* out = static_cast<T*>(p.out);
     if (p.num_chunks == 1) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -312,7 +312,7 @@ gemv_mma_kernel(const GemvParams p)
             for (int i = 0; i < 4; ++i) {
                 const int m = nt * 8 + 2 * t + (i & 1);
                 const int n = (i & 2) ? n1 : n0;
-                if (m < p.M && n < p.N) out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(tot[nt][i]);
+                if (m < p.M && n < p.N) store_result<T>(p.epi, p.out, p.ldc, m, n, tot[nt][i]);
             }
         return;
     }
@@ -343,7 +343,7 @@ gemv_mma_kernel(const GemvParams p)
                 float v = 0.f;
                 for (int c = 0; c < p.num_chunks; ++c)
                     v += __ldcg(&p.partial[((size_t)c * p.M + m) * p.N + n]);
-                out[(size_t)m * p.ldc + n] = F16Traits<T>::from_float(v);
+                store_result<T>(p.epi, p.out, p.ldc, m, n, v);
             }
         }
     if (tid == 0) p.counters[blockIdx.x] = 0u;  // leave the workspace ready for the next call
@@ -357,8 +357,8 @@ gemv_mma_kernel(const GemvParams p)
 template <int QUANT, typename T>
 __global__ void __launch_bounds__(256)
 generic_kernel(const T* __restrict__ x, const uint8_t* __restrict__ wq, const void* __restrict__ scales,
-               const void* __restrict__ zeros, T* __restrict__ out, int M, int N, int K, long long lda,
-               long long ldc, int group_size, int G, int scale_dtype)
+               const void* __restrict__ zeros, void* __restrict__ out, int M, int N, int K, long long lda,
+               long long ldc, int group_size, int G, int scale_dtype, const Epilogue epi)
 {
     constexpr int MB = 4;
     const int lane = threadIdx.x & 31;
@@ -393,7 +393,7 @@ generic_kernel(const T* __restrict__ x, const uint8_t* __restrict__ wq, const vo
         float v = acc[mm];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && m0 + mm < M) out[(size_t)(m0 + mm) * ldc + n] = F16Traits<T>::from_float(v);
+        if (lane == 0 && m0 + mm < M) store_result<T>(epi, out, ldc, m0 + mm, n, v);
     }
 }
 
@@ -576,6 +576,7 @@ int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning)
     p.group_size = single_group ? INT_MAX : a.group_size;
     p.steps_per_group = single_group ? INT_MAX : a.group_size / step;
     p.G = a.G; p.scale_dtype = a.scale_dtype;
+    p.epi = a.epi;
     p.steps_per_chunk = pl.steps_per_chunk; p.total_steps = pl.total_steps; p.num_chunks = pl.num_chunks;
     p.segs = pl.segs; p.xs_stride = pl.xs_stride;
     p.x_vec_ok = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && (a.lda % 8 == 0);
@@ -607,8 +608,8 @@ int launch_generic(const MatmulArgs& a)
 #define MNQ_GEN(Q, T)                                                                              \
     generic_kernel<Q, T><<<grid, warps * 32, 0, a.stream>>>(                                       \
         static_cast<const T*>(a.x), static_cast<const uint8_t*>(a.wq), a.scales, a.zeros,          \
-        static_cast<T*>(a.out), (int)a.M, (int)a.N, (int)a.K, a.lda, a.ldc, a.group_size, a.G,     \
-        a.scale_dtype)
+        a.out, (int)a.M, (int)a.N, (int)a.K, a.lda, a.ldc, a.group_size, a.G, a.scale_dtype,       \
+        a.epi)
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_GEN(MNQ_INT4, __half); else MNQ_GEN(MNQ_INT4, __nv_bfloat16);
     } else {

@@ -48,6 +48,16 @@ namespace mnq {
 
 __device__ unsigned int g_device_status = 0;  // bit 0 / bit 1: a bounded wait gave up (GEMV / GEMM)
 
+#ifdef MNQ_TS
+// development aid: per-launch, per-CTA time stamps of warps 0 and last
+__device__ unsigned long long g_ts[64][160][2][16];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TS(k) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x == blockDim.x - 32) && blockIdx.y == 0 && blockIdx.x < 160) \
+    g_ts[p.ts_slot & 63][blockIdx.x][threadIdx.x ? 1 : 0][k] = gtime(); } while (0)
+#else
+#define TS(k) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kStepBytes = 64;  // packed bytes of one row consumed per step (4 lanes x 16)
@@ -83,6 +93,11 @@ struct StreamParams {
     GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
     int gather_vec;       // the gathered buffers allow 16-byte stores at every column this call writes
     int defer_reduce;     // K chunks are added by a reduce kernel launched after this one: only store the partial sums
+    int ts_slot;
+    int scale_vec;        // scales / zeros of a piece's four groups can be fetched as one aligned 8-byte load per row
+    int weights_immutable;  // weights, scales and zeros are not written by earlier work on the stream: prefetch them at once
+    unsigned int spin_limit;   // polls a wait on another rank may take before it gives up
+    Epilogue epi;         // bias / activation / residual applied before the store; fp32 output mode
     int swiglu_h;         // > 0: fused SwiGLU -- a 16-row tile is 8 gate rows (j) and the 8 up rows (H + j); out is [M, H]
 };
 
@@ -161,8 +176,12 @@ template <> struct Enc<MNQ_INT4, __half> {
     // (n0,n4) (n1,n5) (n2,n6) (n3,n7) as L0 H0 L1 H1
     static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
     {
+#if defined(MNQ_ABL) && (MNQ_ABL & 4)
+        L0 = w; H0 = w; L1 = w; H1 = w;
+#else
         const uint32_t w8 = w >> 8;
         L0 = w & 0x000F000Fu; H0 = w & 0x00F000F0u; L1 = w8 & 0x000F000Fu; H1 = w8 & 0x00F000F0u;
+#endif
     }
 };
 template <> struct Enc<MNQ_INT4, __nv_bfloat16> {
@@ -277,6 +296,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
     extern __shared__ __align__(128) unsigned char smem[];
 
+    TS(0);
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -302,11 +322,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // ---- shared memory carve-up (offsets from the base, so every access stays a
     //      shared-space access) ---------------------------------------------------------
     const int ring_bytes = p.stages * STAGE_BYTES;
-    const int sc_floats = p.rbw * 16 * p.segs;               // per warp, per array
     const int xsum_off = p.M * p.xs_stride;
     const int xsumi_off = (xsum_off + p.segs * NT * 8 * 4 + 7) & ~7;
     const int warp0_off = (xsumi_off + p.segs * NT * 8 * 8 + 1023) & ~1023;
-    const int per_warp = ring_bytes + sc_floats * 8 + 128;
+    const int per_warp = ring_bytes + 128;
     unsigned char* xs = smem;                                                  // [M][xs_stride]
     float* xsum = reinterpret_cast<float*>(smem + xsum_off);                   // [segs][NT*8]
     // the same sums in 2^-24 fixed point: integer adds commute, so the shared-memory atomics
@@ -314,9 +333,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     unsigned long long* xsumi = reinterpret_cast<unsigned long long*>(smem + xsumi_off);
     unsigned char* my = smem + warp0_off + warp * per_warp;
     unsigned char* ring = my;                                                  // [stages][16][CH]
-    float* sS = reinterpret_cast<float*>(my + ring_bytes);                     // [rbw][16][segs]  s / alpha
-    float* sZ = sS + sc_floats;                                                // [rbw][16][segs]  (beta+c) s + z
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sZ + sc_floats);  // [stages] <= 8
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(my + ring_bytes);  // [stages] <= 8
 
     // ---- this warp's row blocks ----------------------------------------------------------
     const int rb_first = (blockIdx.x * warps + warp) * p.rbw;
@@ -331,6 +348,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
     __syncwarp();
 
+    TS(1);
     // Producer state: next piece to request (row block, piece, stage).  One lane issues a
     // single TMA tile copy per piece; rows past N and bytes past the row end are zero-filled
     // by the TMA unit, so every piece is a full box.
@@ -366,7 +384,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     if (CONVERT_X && tid == 0) x_max_bits = 0u;
     float x_down = 1.f, x_up = 1.f;       // 2^-x_shift and 2^x_shift
 
-    constexpr int SCB = 16;                        // scale entries in flight per lane (one batch = 32 groups of each of 16 rows)
     constexpr int XB = (NT == 1) ? 2 : 4;          // activation loads in flight per thread
     const int blocks_per_row = nsteps * (STEP / 8);
     const int x_count = p.M * blocks_per_row;
@@ -453,64 +470,91 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
         *reinterpret_cast<uint4*>(xs + (size_t)m * p.xs_stride + (size_t)pos * 2) = o;
     };
-    // Scales / zeros of this warp's row blocks (nrb x 16 consecutive rows x segs groups): entry
-    // e = row * segs + group goes to lane e % 32, so a warp-wide load covers 32 consecutive
-    // entries, i.e. a contiguous run of groups of one or a few rows (a cache line or two per load
-    // instead of one per lane), and the folded values land at sS[e], sZ[e].  A batch is SCB
-    // entries per lane; nothing in the load phase uses a loaded value, so a batch's loads are all
-    // in flight together, across row blocks too.
-    const int sc_entries = nrb * 16 * p.segs;
-    const int sc_q32 = 32 / p.segs, sc_r32 = 32 - sc_q32 * p.segs;   // (row, group) step of 32 entries
-    auto load_scale_batch = [&](int batch, uint32_t (&sp)[SCB], uint32_t (&zp)[SCB]) {
-        const int e0 = batch * SCB * 32 + lane;
-        int row = e0 / p.segs;
-        int g = e0 - row * p.segs;
-#pragma unroll
-        for (int u = 0; u < SCB; ++u) {
-            int n = rb_first * 16 + row;
-            bool n_ok = n < p.N;
-            if (p.swiglu_h > 0) {   // tile row -> weight row: 8 gate rows, then their 8 up rows
-                const int lr = row & 15, j = (rb_first + (row >> 4)) * 8 + (lr & 7);
-                n = (lr < 8 ? 0 : p.swiglu_h) + j;
-                n_ok = j < p.swiglu_h;
-            }
-            sp[u] = 0; zp[u] = 0;
-            if (row < nrb * 16 && n_ok && seg0 + g < p.G) {
-                const size_t at = (size_t)n * p.G + seg0 + g;
-                sp[u] = __ldg(sc16 + at);
-                if (has_zero) zp[u] = __ldg(zr16 + at);
-            }
-            row += sc_q32;
-            g += sc_r32;
-            if (g >= p.segs) { g -= p.segs; ++row; }
+    // Scales and zeros are not staged: a lane fetches, straight into registers, the raw 16-bit
+    // scale and zero of its two rows (fragment rows r and r + 8) for the PSTEPS steps of one
+    // piece, one piece ahead of the piece it is multiplying, and widens them when a group closes.
+    // When a step is a whole group and the rows are suitably aligned that is one 8-byte load per
+    // row and array; otherwise one 16-bit load per step (steps of one group repeat its address).
+    static_assert(PSTEPS == 4, "a piece's scales travel as four 16-bit values per row");
+    struct ScaleRegs { uint2 s0, s1, z0, z1; };
+    const bool scale_bf16 = (p.scale_dtype == MNQ_BF16);
+    auto load_scales = [&](int rbi, int pc, ScaleRegs& q) {
+        q.s0 = q.s1 = q.z0 = q.z1 = make_uint2(0u, 0u);
+        int na, nb;
+        bool oka, okb;
+        if (p.swiglu_h > 0) {   // tile row -> weight row: 8 gate rows, then their 8 up rows
+            const int j = (rb_first + rbi) * 8 + r;
+            na = j; nb = p.swiglu_h + j;
+            oka = okb = j < p.swiglu_h;
+        } else {
+            na = (rb_first + rbi) * 16 + r; nb = na + 8;
+            oka = na < p.N; okb = nb < p.N;
         }
-    };
-    auto fold_scale_batch = [&](int batch, const uint32_t (&sp)[SCB], const uint32_t (&zp)[SCB]) {
-#pragma unroll
-        for (int u = 0; u < SCB; ++u) {
-            const int e = (batch * SCB + u) * 32 + lane;
-            if (e < sc_entries) {
-                float s0, z0;
-                if (p.scale_dtype == MNQ_BF16) {
-                    s0 = __uint_as_float(sp[u] << 16);
-                    z0 = __uint_as_float(zp[u] << 16);
-                } else {
-                    s0 = __half2float(__ushort_as_half((unsigned short)sp[u]));
-                    z0 = __half2float(__ushort_as_half((unsigned short)zp[u]));
-                }
-                sS[e] = s0 * Enc<QUANT, MT>::inv_alpha;
-                sZ[e] = fmaf(Enc<QUANT, MT>::offset, s0, z0);
+        const int s_abs = step_begin + pc * PSTEPS;   // first step of the piece, counted from the row start
+        if (group_is_step && p.scale_vec && s_abs + PSTEPS <= p.G) {
+            if (oka) {
+                q.s0 = __ldg(reinterpret_cast<const uint2*>(sc16 + (size_t)na * p.G + s_abs));
+                if (has_zero) q.z0 = __ldg(reinterpret_cast<const uint2*>(zr16 + (size_t)na * p.G + s_abs));
             }
+            if (okb) {
+                q.s1 = __ldg(reinterpret_cast<const uint2*>(sc16 + (size_t)nb * p.G + s_abs));
+                if (has_zero) q.z1 = __ldg(reinterpret_cast<const uint2*>(zr16 + (size_t)nb * p.G + s_abs));
+            }
+            return;
         }
+        uint32_t v[4][PSTEPS];
+#pragma unroll
+        for (int ps = 0; ps < PSTEPS; ++ps) {
+            int g = (p.steps_per_group == INT_MAX) ? 0 : (group_is_step ? s_abs + ps : (s_abs + ps) / p.steps_per_group);
+            g = min(g, p.G - 1);
+            v[0][ps] = oka ? __ldg(sc16 + (size_t)na * p.G + g) : 0u;
+            v[1][ps] = okb ? __ldg(sc16 + (size_t)nb * p.G + g) : 0u;
+            v[2][ps] = (oka && has_zero) ? __ldg(zr16 + (size_t)na * p.G + g) : 0u;
+            v[3][ps] = (okb && has_zero) ? __ldg(zr16 + (size_t)nb * p.G + g) : 0u;
+        }
+        q.s0 = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
+        q.s1 = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
+        q.z0 = make_uint2(v[2][0] | (v[2][1] << 16), v[2][2] | (v[2][3] << 16));
+        q.z1 = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
     };
-    const int sc_batches = (sc_entries + 32 * SCB - 1) / (32 * SCB);
+    // folded scale and offset of step ps of a piece: S = s / alpha, Z = (beta + c) s + z
+    auto fold = [&](const uint2& sv, const uint2& zv, int ps, float& S, float& Z) {
+        const uint32_t sw = (ps & 2) ? sv.y : sv.x, zw = (ps & 2) ? zv.y : zv.x;
+        const uint32_t sb = (ps & 1) ? (sw >> 16) : (sw & 0xFFFFu), zb = (ps & 1) ? (zw >> 16) : (zw & 0xFFFFu);
+        float s0, z0;
+        if (scale_bf16) {
+            s0 = __uint_as_float(sb << 16);
+            z0 = __uint_as_float(zb << 16);
+        } else {
+            s0 = __half2float(__ushort_as_half((unsigned short)sb));
+            z0 = __half2float(__ushort_as_half((unsigned short)zb));
+        }
+        S = s0 * Enc<QUANT, MT>::inv_alpha;
+        Z = fmaf(Enc<QUANT, MT>::offset, s0, z0);
+#if defined(MNQ_ABL) && (MNQ_ABL & 1)
+        S = __uint_as_float(sv.x); Z = __uint_as_float(zv.x);
+#endif
+    };
 
-    // first batch of small loads (the only one for the benchmark shapes)
+    // The weight stream starts first: the ring is requested before anything else is read, so
+    // the copies are in flight while the activations are staged.  With `weights_immutable` that
+    // happens even before the wait below.
+    ScaleRegs sc_cur, sc_nxt;
+    sc_cur.s0 = sc_cur.s1 = sc_cur.z0 = sc_cur.z1 = make_uint2(0u, 0u);
+    sc_nxt = sc_cur;
+    if (p.weights_immutable) {
+        for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
+        if (total_pieces > 0) load_scales(0, 0, sc_cur);
+    }
     // With a programmatic dependent launch this CTA may have started while the previous kernel
-    // in the stream was still running.  Everything above touched only this CTA's shared memory;
-    // every global read below (activations, but also weights and scales, which an earlier
-    // kernel in the stream may have produced) comes after that kernel and its writes completed.
+    // in the stream was still running.  Everything above touched only this CTA's shared memory
+    // (and, if the caller declared them immutable, weights, scales and zeros); every other global
+    // read comes after that kernel and its writes completed.
+    TS(2);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    TS(3);
+    // the next kernel in the stream may be scheduled as soon as this one leaves room
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Sharded call: number of this call (the same on every rank), and the announcement that this
     // rank has begun it: whatever read its gathered output of the previous call came earlier
@@ -530,8 +574,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                              ::"l"(p.gather.flag_peer[g] + kGatherReadyBase + p.gather.rank), "r"(call_no) : "memory");
     }
 
-    uint32_t sreg[SCB], zreg[SCB];
-    load_scale_batch(0, sreg, zreg);
     uint32_t xv[XB][4];
     int xm[XB], xb[XB], xk[XB];
 #pragma unroll
@@ -541,9 +583,15 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         if (i < x_count) load_x_block(i, xv[u], xm[u], xb[u], xk[u]);
     }
 
-    // the first weight pieces
-    for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
+    // The activation loads go out ahead of the weight stream: a request issued behind a full ring
+    // of weight tiles waits in the memory system until those tiles have been fetched.
+    if (!p.weights_immutable) {
+        for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
+        if (total_pieces > 0) load_scales(0, 0, sc_cur);
+    }
+    TS(5);
     __syncthreads();   // xsum (and x_max_bits) are zeroed
+    TS(6);
 
     if (CONVERT_X) {
         // largest |x| of the chunk -> power-of-two scale that puts it just below 2^15
@@ -576,16 +624,12 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         x_up = __int_as_float((127 + sh) << 23);
     }
 
-    // consume the small loads
-    fold_scale_batch(0, sreg, zreg);
+    // consume the activation loads
 #pragma unroll
     for (int u = 0; u < XB; ++u)
         if (__any_sync(0xffffffffu, xm[u] >= 0)) store_x_block(xv[u], xm[u], xb[u], xk[u]);
-    // whatever did not fit in the first batch (several row blocks per warp, many groups, M > 8)
-    for (int batch = 1; batch < sc_batches; ++batch) {
-        load_scale_batch(batch, sreg, zreg);
-        fold_scale_batch(batch, sreg, zreg);
-    }
+    TS(7);
+    // whatever did not fit in the first batch (M > 8)
     {
         constexpr int XB2 = 8;   // deeper batches for the bulk of a many-token activation block
         for (int i0 = XB * blockDim.x; i0 < x_count; i0 += XB2 * blockDim.x) {
@@ -603,13 +647,12 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
     }
     __syncthreads();
+    TS(8);
     for (int i = tid; i < p.segs * NT * 8; i += blockDim.x)
         xsum[i] = static_cast<float>(static_cast<long long>(xsumi[i])) * (1.f / 16777216.f);
     __syncthreads();
 
-    // the next kernel in the stream may start its own prologue now
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
+    TS(9);
     // ---- main loop ----------------------------------------------------------------------------
     // this lane's position inside a staged activation row: 16 bytes per 8-block at lane t (int4),
     // 32 bytes at lane t (int8)
@@ -626,15 +669,17 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // volatile loads do) and remembered in shared memory for the rest.
     auto wait_peers_ready = [&]() -> bool {
         if (peers_ready) return true;
+        if (gather_failed) return false;
+        if (peers_ready_cta < 0) { gather_failed = true; return false; }   // another thread of the CTA already gave up
         if (!peers_ready_cta) {
             const volatile unsigned int* mine = p.gather.flag_peer[p.gather.rank] + kGatherReadyBase;
             for (int g = 0; g < p.gather.world; ++g) {
                 bool in = false;
-                for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
+                for (unsigned int spin = 0; spin < p.spin_limit && !in; ++spin) {
                     in = static_cast<int>(mine[g] - call_no) >= 0;
                     if (!in) __nanosleep(100);
                 }
-                if (!in) { gather_failed = true; return false; }
+                if (!in) { gather_failed = true; peers_ready_cta = -1; return false; }
             }
             peers_ready_cta = 1;
         }
@@ -643,16 +688,18 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     };
     // Plain call: one store.  Sharded call: the same element goes to every rank's gathered buffer
     // (peer-mapped device pointers; the local rank is one of them).
-    auto store_out = [&](int m, int n, T v) {
+    auto store_out = [&](int m, int n, float v32) {
         if (p.gather.world == 0) {
-            out[(size_t)m * p.ldc + n] = v;
+            store_result<T>(p.epi, p.out, p.ldc, m, n, v32);
         } else {
             if (!wait_peers_ready()) return;
+            const T v = F16Traits<T>::from_float(v32);
             for (int g = 0; g < p.gather.world; ++g)
                 static_cast<T*>(p.gather.out_peer[g])[(size_t)m * p.ldc + p.gather.n_offset + n] = v;
         }
     };
     bool gave_up = false;
+    int rb_arrived = 0;   // row blocks of this warp whose arrival has been counted (K split in this kernel)
 
     int stage = 0;
     uint32_t parity = 0;
@@ -671,17 +718,20 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         int steps_left = (p.steps_per_group == INT_MAX)
                              ? INT_MAX
                              : p.steps_per_group - (step_begin % p.steps_per_group);
-        const float* S0p = sS + (rbi * 16 + wr) * p.segs;   // advanced as groups close
-        const float* S1p = S0p + 8 * p.segs;
-        const float* Z0p = sZ + (rbi * 16 + wr) * p.segs;
-        const float* Z1p = Z0p + 8 * p.segs;
-        const float* Xp = xsum + 2 * t;
+        const float* Xp = xsum + 2 * t;   // advanced as groups close
         int s = 0;          // step index inside the chunk
         int xoff = 0;       // byte offset of step s in the staged activation rows
         int bytes_left = byte_end - byte_begin;
 
         for (int pc = 0; pc < ppr; ++pc) {
+            // scales and zeros of the piece after this one (the next row block's first, at the end of a row)
+#if !(defined(MNQ_ABL) && (MNQ_ABL & 8))
+            if (pc + 1 < ppr) load_scales(rbi, pc + 1, sc_nxt);
+            else if (rbi + 1 < nrb) load_scales(rbi + 1, 0, sc_nxt);
+#endif
             if (!mbar_wait(smem_u32(&bars[stage]), parity)) { gave_up = true; break; }
+            if (rbi == 0 && pc == 0) TS(10);
+            if (rbi == nrb - 1 && pc == ppr - 1) TS(11);
             const unsigned char* st0 = ring + stage * STAGE_BYTES + wr * RS + t * 16;
             const unsigned char* st1 = st0 + 8 * RS;
             if (bytes_left >= CH && group_is_step) {
@@ -694,15 +744,9 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 }
                 float Sa[PSTEPS], Sb[PSTEPS], Za[PSTEPS], Zb[PSTEPS];
 #pragma unroll
-                for (int q4 = 0; q4 < PSTEPS; q4 += 4) {
-                    const float4 a = *reinterpret_cast<const float4*>(S0p + q4);
-                    const float4 b = *reinterpret_cast<const float4*>(S1p + q4);
-                    const float4 c = *reinterpret_cast<const float4*>(Z0p + q4);
-                    const float4 d = *reinterpret_cast<const float4*>(Z1p + q4);
-                    Sa[q4] = a.x; Sa[q4 + 1] = a.y; Sa[q4 + 2] = a.z; Sa[q4 + 3] = a.w;
-                    Sb[q4] = b.x; Sb[q4 + 1] = b.y; Sb[q4 + 2] = b.z; Sb[q4 + 3] = b.w;
-                    Za[q4] = c.x; Za[q4 + 1] = c.y; Za[q4 + 2] = c.z; Za[q4 + 3] = c.w;
-                    Zb[q4] = d.x; Zb[q4 + 1] = d.y; Zb[q4 + 2] = d.z; Zb[q4 + 3] = d.w;
+                for (int ps = 0; ps < PSTEPS; ++ps) {
+                    fold(sc_cur.s0, sc_cur.z0, ps, Sa[ps], Za[ps]);
+                    fold(sc_cur.s1, sc_cur.z1, ps, Sb[ps], Zb[ps]);
                 }
                 const unsigned char* xb[NT];
 #pragma unroll
@@ -711,11 +755,17 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff + ps * STEP * 2;
                     float a4[NT][4];
                     step_mma<QUANT, MT, NT, true>(wa[ps], wb[ps], xb, a4);
+#if defined(MNQ_ABL) && (MNQ_ABL & 2)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) tot[nt][i] += a4[nt][i] * Sa[ps] + Za[ps] + Sb[ps] + Zb[ps];
+#else
                     close_group<NT>(tot, a4, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8));
+#endif
                 }
                 s += PSTEPS;
                 xoff += PSTEPS * STEP * 2;
-                S0p += PSTEPS; S1p += PSTEPS; Z0p += PSTEPS; Z1p += PSTEPS;
                 Xp += PSTEPS * (NT * 8);
             } else {
                 const int bytes = min(CH, bytes_left);
@@ -733,18 +783,21 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff;
                     step_mma<QUANT, MT, NT, false>(wa, wb, xb, acc);
                     if (--steps_left == 0 || s == nsteps - 1) {
-                        close_group<NT>(tot, acc, *S0p, *S1p, *Z0p, *Z1p, Xp);
+                        float Sa, Sb, Za, Zb;
+                        fold(sc_cur.s0, sc_cur.z0, ps, Sa, Za);
+                        fold(sc_cur.s1, sc_cur.z1, ps, Sb, Zb);
+                        close_group<NT>(tot, acc, Sa, Sb, Za, Zb, Xp);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
                         steps_left = p.steps_per_group;
-                        ++S0p; ++S1p; ++Z0p; ++Z1p;
                         Xp += NT * 8;
                     }
                 }
             }
             bytes_left -= CH;
+            sc_cur = sc_nxt;
             __syncwarp();   // every lane is done reading this stage
             if (iss_count < total_pieces) issue_piece();
             if (++stage == p.stages) { stage = 0; parity ^= 1u; }
@@ -785,7 +838,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     const int m = nt * 8 + 2 * t + (i & 1);
                     const int n = (i & 2) ? n1 : n0;
                     if (m < p.M && n < p.N)
-                        store_out(m, n, F16Traits<T>::from_float(CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]));
+                        store_out(m, n, CONVERT_X ? tot[nt][i] * x_up : tot[nt][i]);
                 }
             continue;
         }
@@ -804,6 +857,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         unsigned int arrival = 0;
         if (lane == 0) arrival = atomicAdd(&p.counters[rb], 1u);
         arrival = __shfl_sync(0xffffffffu, arrival, 0);
+        rb_arrived = rbi + 1;
         if (arrival != (unsigned int)(p.num_chunks - 1)) continue;
         __threadfence();
         // Last chunk to arrive: add the chunks in index order (deterministic).  One output per
@@ -823,12 +877,13 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 for (int c = 0; c < 8; ++c)
                     if (c0 + c < p.num_chunks) v += part[c];
             }
-            if (n < p.N) store_out(m, n, F16Traits<T>::from_float(v));
+            if (n < p.N) store_out(m, n, v);
         }
         __syncwarp();
         if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
     }
 
+    TS(12);
     if (p.gather.world > 0) {
         // Every thread's peer stores become visible system-wide, then the CTA reports in; the last
         // CTA of the grid tells every rank that this rank's slice of this call is complete and
@@ -847,7 +902,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 }
             if (tid == 0) wait_peers_ready();
             __syncthreads();
-            if (peers_ready_cta) {
+            if (peers_ready_cta > 0) {
                 const int n_cta = blockIdx.x * cols;
                 const int vpr = cols / 8;                           // 16-byte pieces per token row
                 const int per_rank = p.M * vpr;
@@ -886,7 +941,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                 bool all_in = true;
                 for (int src = 0; src < p.gather.world && all_in; ++src) {
                     bool in = false;
-                    for (unsigned int spin = 0; spin < (1u << 22) && !in; ++spin) {
+                    for (unsigned int spin = 0; spin < p.spin_limit && !in; ++spin) {
                         unsigned int v;
                         asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
                         in = static_cast<int>(v - call_no) >= 0;
@@ -901,8 +956,16 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
     }
 
+    TS(13);
     if (gave_up) {
         if (lane == 0) atomicOr(&g_device_status, 1u);
+        // The arrival counters must still return to zero (the workspace is reused by later calls):
+        // this warp reports for the row blocks it abandoned, and whoever arrives last clears the
+        // counter.  Their outputs stay unwritten; the status word says so.
+        if (p.num_chunks > 1 && !p.defer_reduce && p.swiglu_h == 0 && lane == 0)
+            for (int rbi = rb_arrived; rbi < nrb; ++rbi)
+                if (atomicAdd(&p.counters[rb_first + rbi], 1u) == (unsigned int)(p.num_chunks - 1))
+                    p.counters[rb_first + rbi] = 0u;
         // Copies already requested may still land in this CTA's shared memory: give each
         // stage one more bounded wait before the CTA exits.
         for (int k = 0; k < p.stages; ++k) {
@@ -944,11 +1007,12 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     while (warps > 1 && row_blocks < warps) warps >>= 1;
     pl.warps = warps;
     pl.piece_bytes = (tuning && tuning->piece_bytes > 0) ? tuning->piece_bytes : 256;
-    if (pl.piece_bytes != 256 && pl.piece_bytes != 512) return false;
-    if (pl.nt > 1) pl.piece_bytes = 256;
+    if (pl.piece_bytes != 256) return false;   // one piece = four steps; its scales travel as four values per row
     // more than 8 tokens: chunks are short and there are fewer warps, so each warp keeps more
     // pieces in flight (the loop below takes stages away again if shared memory runs out)
-    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : (pl.nt >= 2 ? 4 : 2);
+    // as deep a ring as shared memory allows (the loop below takes stages away until the plan fits);
+    // a warp never has use for more stages than it has pieces
+    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : 8;
     if (pl.stages > 8) pl.stages = 8;
     if (pl.stages < 2) pl.stages = 2;
     const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : 1;
@@ -1009,10 +1073,14 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         pl.segs = (segs + 3) & ~3;
         const int row_pad = (a.quant == MNQ_INT4) ? 64 : 16;
         pl.xs_stride = static_cast<int>(((chunk_k * 2 + 127) / 128) * 128 + row_pad);
+        if (!(tuning && tuning->stages > 0)) {
+            const int64_t pieces = static_cast<int64_t>(rbw) * ((static_cast<int64_t>(pl.steps_per_chunk) * kStepBytes +
+                                                                   pl.piece_bytes - 1) / pl.piece_bytes);
+            if (pl.stages > pieces) pl.stages = static_cast<int>(pieces < 2 ? 2 : pieces);
+        }
         const size_t ring = static_cast<size_t>(pl.stages) * 16 * pl.piece_bytes;
-        const size_t sc = static_cast<size_t>(rbw) * 16 * pl.segs * 8;
         pl.smem = ((static_cast<size_t>(a.M) * pl.xs_stride + static_cast<size_t>(pl.segs) * pl.nt * 8 * 12 + 8 + 1023) &
-                   ~size_t(1023)) + static_cast<size_t>(warps) * (ring + sc + 128);
+                   ~size_t(1023)) + static_cast<size_t>(warps) * (ring + 128);
         size_t need_ws = 0;
         if (pl.num_chunks > 1) need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
         const bool smem_ok = pl.smem <= kMaxSmem;
@@ -1075,8 +1143,6 @@ template <int QUANT, typename T>
 int launch_stream_nt(const StreamParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap8, int nt, int ch, dim3 grid,
                      int threads, size_t smem, cudaStream_t stream)
 {
-    // 512-byte pieces only for NT == 1: wider activation tiles run out of registers
-    if (nt == 1 && ch == 512) return launch_stream_one<QUANT, T, 1, 512>(p, wmap, wmap8, grid, threads, smem, stream);
     if (nt == 1) return launch_stream_one<QUANT, T, 1, 256>(p, wmap, wmap8, grid, threads, smem, stream);
     if (nt == 2) return launch_stream_one<QUANT, T, 2, 256>(p, wmap, wmap8, grid, threads, smem, stream);
     return launch_stream_one<QUANT, T, 4, 256>(p, wmap, wmap8, grid, threads, smem, stream);
@@ -1133,7 +1199,18 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.rbw = pl.rbw; p.stages = pl.stages;
     p.row_blocks = static_cast<int>(a.swiglu_h > 0 ? (a.swiglu_h + 7) / 8 : (a.N + 15) / 16);
     p.swiglu_h = static_cast<int>(a.swiglu_h);
+    p.epi = a.epi;
     p.gather = a.gather;
+#ifdef MNQ_TS
+    { static int slot = 0; p.ts_slot = slot++; }
+#endif
+    p.weights_immutable = option_value(MNQ_OPT_WEIGHTS_IMMUTABLE) != 0 ? 1 : 0;
+    p.spin_limit = static_cast<unsigned int>(option_value(MNQ_OPT_PEER_WAIT_POLLS));
+    // one aligned 8-byte load fetches a row's four scales of a piece: rows and chunk starts must
+    // fall on 8-byte boundaries
+    p.scale_vec = (a.G % 4 == 0) && (pl.num_chunks == 1 || pl.steps_per_chunk % 4 == 0) &&
+                  reinterpret_cast<uintptr_t>(a.scales) % 8 == 0 &&
+                  (a.zeros == nullptr || reinterpret_cast<uintptr_t>(a.zeros) % 8 == 0);
     // many tokens: the chunk planes are big and every unit would pay a fence and an atomic round
     // trip; a separate coalesced kernel adds them instead (not with the fused gather, whose peer
     // stores live in this kernel)
@@ -1179,7 +1256,7 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     }
 #undef MNQ_GS
     if (rcl || !p.defer_reduce) return rcl;
-    return launch_splitk_reduce(p.partial, a.out, p.M, p.N, a.ldc, pl.num_chunks, a.act_dtype, a.stream);
+    return launch_splitk_reduce(p.partial, a.out, p.M, p.N, a.ldc, pl.num_chunks, a.act_dtype, a.epi, a.stream);
 }
 
 int read_gemm_status(unsigned int* out, bool clear);
@@ -1200,5 +1277,9 @@ int read_device_status(unsigned int* out, bool clear)
     *out = v | g;
     return MNQ_SUCCESS;
 }
+
+#ifdef MNQ_TS
+extern "C" MNQ_API int mnq_dbg_ts(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_ts, sizeof(g_ts)); }
+#endif
 
 }  // namespace mnq

@@ -191,6 +191,42 @@ __device__ __forceinline__ void mma_16x8x16<__nv_bfloat16>(float (&d)[4], uint32
 }
 
 // ---------------------------------------------------------------------------
+// What happens to an fp32 result between the accumulator and memory: the reference's
+// MatmulEpilogue (include/metal_native/ops/fused_matmul.h:18-24) as applied by its
+// apply_epilogue (shaders/matmul_fused_epilogue.metal:97-124: fp32 arithmetic on the accumulated
+// value, bias [N] broadcast over rows, residual [M, N], one rounding at the store), plus an fp32
+// output mode that stores the value unrounded.
+// ---------------------------------------------------------------------------
+struct Epilogue {
+    int32_t kind;          // mnq_epilogue
+    int32_t out_f32;       // 1: out is float [M, ldc]
+    const void* bias;      // [N] in the activation dtype (kinds BIAS, BIAS_RELU, BIAS_SILU)
+    const void* residual;  // [M, ldr] in the activation dtype (kind RESIDUAL)
+    long long ldr;
+};
+
+template <typename T>
+__device__ __forceinline__ float epilogue_value(const Epilogue& e, float v, int m, int n)
+{
+    if (e.kind == MNQ_EPI_NONE) return v;
+    if (e.kind == MNQ_EPI_RESIDUAL)
+        return v + F16Traits<T>::to_float(static_cast<const T*>(e.residual)[(size_t)m * e.ldr + n]);
+    v += F16Traits<T>::to_float(static_cast<const T*>(e.bias)[n]);
+    if (e.kind == MNQ_EPI_BIAS_RELU) return fmaxf(0.f, v);
+    if (e.kind == MNQ_EPI_BIAS_SILU) return v / (1.f + expf(-v));
+    return v;
+}
+
+// out[m, n] = epilogue(v), rounded to T unless the fp32 output mode is on
+template <typename T>
+__device__ __forceinline__ void store_result(const Epilogue& e, void* out, long long ldc, int m, int n, float v)
+{
+    v = epilogue_value<T>(e, v, m, n);
+    if (e.out_f32) static_cast<float*>(out)[(size_t)m * ldc + n] = v;
+    else static_cast<T*>(out)[(size_t)m * ldc + n] = F16Traits<T>::from_float(v);
+}
+
+// ---------------------------------------------------------------------------
 // Launch-argument bundles
 // ---------------------------------------------------------------------------
 // Column-sharded call: this rank's [M, N] result is stored into the gathered [M, ldc] buffer of
@@ -232,7 +268,11 @@ struct MatmulArgs {
     int32_t sm_count;
     GatherArgs gather;    // world == 0 unless called through mnq_dequant_matmul_gather
     int64_t swiglu_h;     // > 0: weights are [2H, K] (gate rows, then up rows) and out is [M, H] = silu(gate) * up
+    Epilogue epi;         // kind NONE and out_f32 0 unless called through mnq_dequant_matmul_fused
 };
+
+// Process-wide options (mnq_set_option); defined in api.cu.
+int64_t option_value(int option);
 
 // Split-K workspace layout, the same for every kernel and every problem shape: arrival
 // counters (always left at zero by the kernel that used them) in the first kCounterBytes,
@@ -258,7 +298,7 @@ bool gemv_stream_supported(const MatmulArgs& a, const mnq_tuning* tuning);
 int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning);
 // out[m, n] = sum over splits of partial[split][m][n] (fp32 planes, index order), as fp16 / bf16
 int launch_splitk_reduce(const float* partial, void* out, int M, int N, int64_t ldc, int splits, int32_t act_dtype,
-                         cudaStream_t stream);
+                         const Epilogue& epi, cudaStream_t stream);
 int read_device_status(unsigned int* out, bool clear);
 size_t gemv_stream_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant, bool* supported);
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);

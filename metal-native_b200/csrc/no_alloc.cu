@@ -13,17 +13,21 @@
 // GPU that loads the library, held until the process exits.  On the host the array's name
 // is only a handle, not a device address; the address is obtained once per device with
 // cudaGetSymbolAddress (in this file, with that device current) and handed to the kernels.
+#include <atomic>
+
 #include "mnq_common.cuh"
 
 namespace mnq {
 namespace {
 
-constexpr size_t kStaticScratchBytes = MNQ_STATIC_SCRATCH_BYTES;   // 64 KiB of counters + partial sums
+constexpr size_t kStaticScratchBytes = MNQ_STATIC_SCRATCH_BYTES;   // 4 MiB: 64 KiB of arrival counters, then partial sums
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices];   // device address of g_static_scratch, per device ordinal
+// device address of g_static_scratch per device ordinal; several host threads may make a device's
+// first call together (each resolves the same address; the atomic makes that well defined)
+std::atomic<void*> g_scratch_addr[kMaxDevices];
 
 // Device address of the scratch array on the current device.  The first call on a device
 // resolves it (a synchronous runtime call, not capturable); later calls read the cache.
@@ -33,14 +37,14 @@ int static_scratch(void** out)
     int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (rc) return rc;
     if (dev < 0 || dev >= kMaxDevices) return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul_static: device ordinal %d", dev);
-    if (!g_scratch_addr[dev]) {
-        void* ptr = nullptr;
+    void* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         rc = check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
         if (rc) return rc;
         if (!ptr) return fail(MNQ_INTERNAL_ERROR, "dequant_matmul_static: null scratch address");
-        g_scratch_addr[dev] = ptr;
+        g_scratch_addr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = ptr;
     return MNQ_SUCCESS;
 }
 

@@ -77,6 +77,17 @@ def _load() -> ctypes.CDLL:
     L.mnq_host_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.mnq_dequant_matmul_host.restype = ctypes.c_int
     L.mnq_dequant_matmul_host.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
+    L.mnq_select_path_ex.restype = ctypes.c_int
+    L.mnq_select_path_ex.argtypes = [i64, i64, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.mnq_set_option.restype = ctypes.c_int
+    L.mnq_set_option.argtypes = [i32, i64]
+    L.mnq_get_option.restype = i64
+    L.mnq_get_option.argtypes = [i32]
+    L.mnq_dequant_matmul_fused.restype = ctypes.c_int
+    L.mnq_dequant_matmul_fused.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32, i32, i32, i32,
+                                           vp, vp, i64, vp, sz, vp]
+    L.mnq_dequant_matmul_static.restype = ctypes.c_int
+    L.mnq_dequant_matmul_static.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32, i32, vp]
     L.mnq_dequant_matmul_gather.restype = ctypes.c_int
     L.mnq_dequant_matmul_gather.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64,
                                             i64, i64, i64, i64, i64, i32, i32, i32, i32, vp, sz, vp]
@@ -140,9 +151,13 @@ def _weights_as_bytes(weights_packed: torch.Tensor, quant: int) -> torch.Tensor:
     raise _invalid("dequant_matmul: INT8 weights must be int8 [N, K]")
 
 
-# one zero-filled workspace per (device, stream); the kernels leave it zero-filled
+# One zero-filled workspace per (device, stream); the kernels leave its counters at zero.  A
+# workspace grows when a call needs more and is dropped by release_workspaces() (or when the
+# table holds more than _MAX_WORKSPACES streams: the least recently used one goes).
 _ws_lock = threading.Lock()
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_MAX_WORKSPACES = 64
+COUNTER_BYTES = 64 * 1024   # arrival counters at the front of every workspace (include/mnq.h)
 
 
 def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor | None:
@@ -153,8 +168,42 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor |
     if ws is None or ws.numel() < nbytes:
         with _ws_lock:
             ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _workspaces.pop(key, None)
             _workspaces[key] = ws
+            while len(_workspaces) > _MAX_WORKSPACES:
+                _workspaces.pop(next(iter(_workspaces)))
     return ws
+
+
+def release_workspaces(device=None) -> None:
+    """Drops the cached split-K workspaces (of one device, or of all).  Work already enqueued
+    keeps its memory alive through torch's stream-ordered allocator."""
+    with _ws_lock:
+        for key in [k for k in _workspaces if device is None or k[0] == torch.device(device).index]:
+            del _workspaces[key]
+
+
+OPTIONS = {"weights_immutable": 0, "peer_wait_polls": 1, "gemv_max_m": 2}   # mnq_option of include/mnq.h
+
+
+def set_option(name: str, value) -> None:
+    """Process-wide option of the library (``mnq_set_option``):
+
+    ``weights_immutable``  weights, scales and zeros are never written while an operator call
+                           may be in flight (model state, loaded once): the decode kernels then
+                           start fetching weights before the previous kernel in the stream ends;
+    ``peer_wait_polls``    how long a sharded call waits for another rank before it gives up;
+    ``gemv_max_m``         largest M that takes the decode kernels (1..32, default 32, or the
+                           environment variable METAL_NATIVE_GEMV_MAX_M)."""
+    if name not in OPTIONS:
+        raise _invalid(f"set_option: unknown option {name!r}")
+    _check(_lib.mnq_set_option(OPTIONS[name], int(value)))
+
+
+def get_option(name: str) -> int:
+    if name not in OPTIONS:
+        raise _invalid(f"get_option: unknown option {name!r}")
+    return int(_lib.mnq_get_option(OPTIONS[name]))
 
 
 def _prepare(activations, weights_packed, scales, zeros, group_size, quant_type, host_x=False):
@@ -275,6 +324,72 @@ def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size,
     return out
 
 
+EPILOGUES = {"none": 0, "bias": 1, "bias_relu": 2, "bias_silu": 3, "residual": 4}   # mnq_epilogue
+
+
+def dequant_matmul_fused(activations, weights_packed, scales, zeros, group_size, quant_type, epilogue="none",
+                         bias=None, residual=None, *, out_dtype=None, out=None):
+    """``dequant_matmul`` followed, inside the kernel, by one of the reference's matmul epilogues
+    (``MatmulEpilogue``, ``include/metal_native/ops/fused_matmul.h:18-24``): ``"bias"`` (+ bias[N]),
+    ``"bias_relu"``, ``"bias_silu"``, ``"residual"`` (+ residual[M, N]); fp32 arithmetic on the
+    accumulated value, one rounding at the store (``shaders/matmul_fused_epilogue.metal:97-124``).
+    As in the reference, a required tensor that is missing raises InvalidArgument.
+
+    ``out_dtype=torch.float32`` returns the fp32 value before the final rounding (the kernel's
+    accumulators plus epilogue): a checking aid, not a faster path."""
+    if epilogue not in EPILOGUES:
+        raise _invalid(f"dequant_matmul_fused: unknown epilogue {epilogue!r}")
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
+    dev = x.device
+    odt = x.dtype if out_dtype is None else out_dtype
+    if odt not in (x.dtype, torch.float32):
+        raise _invalid("dequant_matmul_fused: out_dtype must be the activation dtype or float32")
+    for name, t, shape in (("bias", bias, (N,)), ("residual", residual, (M, N))):
+        if t is None:
+            continue
+        _require_cuda(name, t, dev)
+        if t.dtype != x.dtype or tuple(t.shape) != shape or t.stride(-1) != 1:
+            raise _invalid(f"dequant_matmul_fused: {name} must be {list(shape)} in the dtype of activations")
+    if out is None:
+        out = torch.empty((M, N), dtype=odt, device=dev)
+    else:
+        _require_cuda("out", out, dev)
+        if out.shape != (M, N) or out.dtype != odt or out.stride(1) != 1:
+            raise _invalid("dequant_matmul_fused: out must be [M, N] in out_dtype")
+    ldc = out.stride(0) if M > 1 else max(N, 1)
+    ldr = (residual.stride(0) if M > 1 else max(N, 1)) if residual is not None else max(N, 1)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ws = _workspace(dev, stream, _lib.mnq_workspace_bytes(M, N, K, g, q))
+        _check(_lib.mnq_dequant_matmul_fused(
+            x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
+            M, N, K, lda, ldc, g, q, _DT[x.dtype], _DT[s.dtype], _DT[odt], EPILOGUES[epilogue],
+            bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+            ldr, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream))
+    return out
+
+
+STATIC_SCRATCH_BYTES = 4 << 20   # MNQ_STATIC_SCRATCH_BYTES of include/mnq.h
+
+
+def dequant_matmul_static(activations, weights_packed, scales, zeros, group_size, quant_type, out):
+    """``dequant_matmul`` through ``mnq_dequant_matmul_static``: no workspace is passed and the
+    library allocates nothing; split-K scratch is a fixed area inside the library image.  ``out``
+    must be given (allocating it would defeat the purpose).  Problems that want more than
+    STATIC_SCRATCH_BYTES of scratch are refused; calls that overlap on one GPU race."""
+    x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
+    _require_cuda("out", out, x.device)
+    if out.shape != (M, N) or out.dtype != x.dtype or out.stride(1) != 1:
+        raise _invalid("dequant_matmul_static: out must be [M, N] in the dtype of activations")
+    ldc = out.stride(0) if M > 1 else max(N, 1)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _check(_lib.mnq_dequant_matmul_static(x.data_ptr(), w.data_ptr(), s.data_ptr(),
+                                              z.data_ptr() if z is not None else None, out.data_ptr(), M, N, K, lda,
+                                              ldc, g, q, _DT[x.dtype], _DT[s.dtype], stream))
+    return out
+
+
 def dequant_matmul_swiglu(activations, weights_packed, scales, zeros, group_size, quant_type, out=None):
     """``silu(x @ Wg.T) * (x @ Wu.T)`` for the fused weight matrix ``[Wg; Wu]`` of shape [2H, K]
     (``mnq_dequant_matmul_swiglu``): the gate+up projection of an MLP with the reference's
@@ -328,14 +443,16 @@ def dequant_matmul_gather(activations, weights_shard, scales_shard, zeros_shard,
 
 
 def select_path(M, N, K, group_size, quant_type, dtype=torch.float16, lda=None, alignment=256,
-                zeros=True) -> str:
+                zeros=True, scale_dtype=None) -> str:
     """Kernel family the library picks for a problem: 'gemv', 'gemm' or 'generic'.
     Host logic only (works without a GPU); ``alignment`` is the assumed alignment of the
-    buffers' base addresses, ``zeros`` whether a zeros tensor is passed."""
+    buffers' base addresses, ``zeros`` whether a zeros tensor is passed, ``scale_dtype`` the
+    dtype of scales and zeros (default: fp16 for fp16 activations, bf16 for bf16)."""
     q = _quant_code(quant_type)
     fake = ctypes.c_void_p(alignment * 4096)
-    rc = _lib.mnq_select_path(M, N, K, lda if lda is not None else K, int(group_size), q, _DT[dtype],
-                              fake, fake, fake, fake if zeros else None)
+    sdt = _DT[dtype if scale_dtype is None else scale_dtype]
+    rc = _lib.mnq_select_path_ex(M, N, K, lda if lda is not None else K, int(group_size), q, _DT[dtype], sdt,
+                                 fake, fake, fake, fake if zeros else None)
     if rc < 0:
         raise MetalNativeError(-rc, _lib.mnq_last_error().decode())
     return _PATH_NAMES[rc]
@@ -415,10 +532,14 @@ def device_status(clear: bool = True) -> int:
 
 
 def check_device_status() -> None:
-    """Raise ``MetalNativeError`` (TimeoutError) if a kernel gave up a bounded wait."""
+    """Raise ``MetalNativeError`` (TimeoutError) if a kernel gave up a bounded wait: bits 0 / 1, a
+    decode / tensor-core kernel waiting for an asynchronous copy; bit 2, a sharded call waiting for
+    another rank.  The output of that call is incomplete.  Synchronises the device; the operator
+    calls themselves never do, so a caller that wants the check makes it at its own sync points."""
     v = device_status(clear=True)
     if v:
-        raise MetalNativeError(6, f"a kernel gave up waiting for an asynchronous copy (status {v:#x})")
+        what = "for another rank" if v & 4 else "for an asynchronous copy"
+        raise MetalNativeError(6, f"a kernel gave up waiting {what} (status {v:#x})")
 
 
 def version() -> str:
@@ -434,4 +555,5 @@ def exported_symbols() -> list[str]:
     return ["mnq_status_name", "mnq_last_error", "mnq_version", "mnq_workspace_bytes",
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
             "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather", "mnq_host_workspace_bytes",
-            "mnq_dequant_matmul_host", "mnq_dequant_matmul_swiglu"]
+            "mnq_dequant_matmul_host", "mnq_dequant_matmul_swiglu", "mnq_select_path_ex", "mnq_set_option",
+            "mnq_get_option", "mnq_dequant_matmul_fused", "mnq_dequant_matmul_static"]

@@ -6,11 +6,13 @@ here.  As in the reference, the operator lives in ``metal_native._C``; it is re-
 at package level for convenience.
 """
 from . import _C
-from ._C import (MetalNativeError, dequant_matmul, dequant_matmul_swiglu, dequantize, dequantize_flat,
-                 synchronize)
+from ._C import (MetalNativeError, dequant_matmul, dequant_matmul_fused, dequant_matmul_swiglu, dequantize,
+                 dequantize_flat, synchronize)
 from .quant_weight_cache import QuantFormat, QuantWeightCache
-from .workloads import pack_int4
+from .packing import pack_int4
+from .phase_pipeline import InferencePhase, PhaseConfig, PhasePipeline
 
-__all__ = ["_C", "MetalNativeError", "dequant_matmul", "dequant_matmul_swiglu", "dequantize", "dequantize_flat", "synchronize",
-           "QuantWeightCache", "QuantFormat", "pack_int4"]
+__all__ = ["_C", "MetalNativeError", "dequant_matmul", "dequant_matmul_fused", "dequant_matmul_swiglu", "dequantize",
+           "dequantize_flat", "synchronize", "QuantWeightCache", "QuantFormat", "pack_int4", "InferencePhase",
+           "PhaseConfig", "PhasePipeline"]
 __version__ = _C.version()

@@ -5,6 +5,9 @@ small positive range, activations standard normal.
 
 Everything is generated on the CPU with a seeded ``torch.Generator`` so that a CPU
 checker and the GPU see identical bits; tensors are moved by the caller.
+
+Benchmark and test input only: this module sits beside the ``metal_native`` package, not in
+it, and imports nothing from it, so generating inputs never loads the CUDA library.
 """
 from __future__ import annotations
 
@@ -138,18 +141,30 @@ def config3(seed: int = 3, M: int = 512) -> list[Layer]:
 
 def config4(M: int, seed: int = 4, world_size: int = 1, rank: int = 0, scale_down: int = 1) -> list[Layer]:
     """Llama-3-70B layers, int8 per-channel symmetric (fp16 scales U(0.001, 0.01)), bf16
-    activations: fused gate+up (K=8192, N=57344) and down (K=28672, N=8192).  With
-    ``world_size`` > 1 only this rank's block of output rows is generated (column
-    sharding over N); every rank draws the same activations.  ``scale_down`` divides N
-    (tests use it to keep the CPU checker fast)."""
+    activations: fused gate+up (K=8192, N=57344) and down (K=28672, N=8192).  The whole matrix is
+    drawn from one seed whatever the world size; with ``world_size`` > 1 this rank keeps its block
+    of output rows (column sharding over N), so the ranks' slices together are exactly the
+    matrix a single GPU gets.  ``scale_down`` divides N (tests use it to keep the CPU checker
+    fast)."""
     layers = []
     for i, (name, K, N) in enumerate((("llama3-70b.gate_up", 8192, 57344), ("llama3-70b.down", 28672, 8192))):
         N //= scale_down
+        if N % world_size:
+            raise ValueError(f"N={N} is not divisible by world_size={world_size}")
         gx = torch.Generator(device="cpu").manual_seed(seed * 1000 + i)
         x = torch.randn((M, K), generator=gx, dtype=torch.float32).to(torch.bfloat16)
+        gw = torch.Generator(device="cpu").manual_seed(seed * 1000 + 100 + i)
         n_local = N // world_size
-        gw = torch.Generator(device="cpu").manual_seed(seed * 1000 + 100 + i * 16 + rank)
-        wq = torch.randint(-127, 128, (n_local, K), generator=gw, dtype=torch.int8)
-        scales = (torch.rand((n_local, 1), generator=gw, dtype=torch.float32) * 0.009 + 0.001).to(torch.float16)
+        # rows are drawn in blocks of 1024 from the one generator, every rank walking the same
+        # sequence and keeping only its own rows (a whole [N, K] draw would need 470 MB per rank)
+        lo, hi = rank * n_local, (rank + 1) * n_local
+        wq = torch.empty((n_local, K), dtype=torch.int8)
+        for r0 in range(0, N, 1024):
+            r1 = min(N, r0 + 1024)
+            blk = torch.randint(-127, 128, (r1 - r0, K), generator=gw, dtype=torch.int8)
+            a, b = max(r0, lo), min(r1, hi)
+            if a < b:
+                wq[a - lo:b - lo] = blk[a - r0:b - r0]
+        scales = (torch.rand((N, 1), generator=gw, dtype=torch.float32) * 0.009 + 0.001).to(torch.float16)[lo:hi].contiguous()
         layers.append(Layer(name, "int8", M, K, n_local, K, x, wq, scales, None))
     return layers

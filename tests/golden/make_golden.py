@@ -13,8 +13,15 @@ outputs are
     evaluation of w = (q-8)*s - z (int4) / q*s - z (int8) and C = A . W^T,
     done here with numpy and no oracle code.
 
+A second file, tests/golden/reference_cpu_outputs.json, holds outputs of the reference's own
+CPU helpers (tests/cpp/test_dequant_matmul.mm:103-259, compiled from the reference checkout
+into oracle/_ref/libmnref.so by oracle/build_ref.py) on small seeded cases the fixture never
+checks: non-zero zeros, several groups per row, a ragged last group, odd K, int8.  It is
+written only where that library exists; inputs and outputs are stored as fp32 bit patterns.
+
 Run:  python tests/golden/make_golden.py
 """
+import sys
 import json
 from pathlib import Path
 
@@ -73,11 +80,46 @@ def square(quant):
     }
 
 
+def reference_outputs():
+    """Small seeded cases through the reference's own helpers."""
+    sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+    from oracle import ref
+    if not ref.available():
+        print("oracle/_ref/libmnref.so is not built: reference_cpu_outputs.json left as it is")
+        return
+    rng = np.random.default_rng(20240607)
+    cases = []
+    for name, quant, M, N, K, g in [("int4_zeros_groups", "int4", 2, 5, 64, 32), ("int4_ragged_group", "int4", 1, 3, 80, 32),
+                                    ("int4_odd_K", "int4", 1, 2, 7, 32), ("int8_zeros_groups", "int8", 3, 4, 96, 32),
+                                    ("int8_per_channel", "int8", 1, 6, 40, 40), ("int4_g64", "int4", 1, 4, 256, 64)]:
+        G = (K + g - 1) // g
+        x = rng.standard_normal((M, K)).astype(np.float16).astype(np.float32)
+        s = rng.uniform(0.005, 0.02, (N, G)).astype(np.float16).astype(np.float32)
+        z = ((rng.integers(0, 16, (N, G)) - 8) * s).astype(np.float16).astype(np.float32)
+        if quant == "int4":
+            q = rng.integers(0, 16, (N, K)).astype(np.int8)
+            wq = np.stack([ref.pack_int4(q[n]) for n in range(N)])
+        else:
+            wq = rng.integers(-127, 128, (N, K)).astype(np.int8)
+        w = ref.dequant(wq, s, z, K, N, g, quant)
+        out = ref.matmul(x, w)
+        cases.append({"name": name, "quant": quant, "M": M, "N": N, "K": K, "group_size": g,
+                      "x_bits": x.view(np.uint32).ravel().tolist(), "scales_bits": s.view(np.uint32).ravel().tolist(),
+                      "zeros_bits": z.view(np.uint32).ravel().tolist(), "wq": wq.astype(np.int16).ravel().tolist()
+                      if quant == "int8" else wq.ravel().tolist(),
+                      "w_bits": w.view(np.uint32).ravel().tolist(), "out_bits": out.view(np.uint32).ravel().tolist(),
+                      "source": "reference helpers dequant_reference_int4/int8 + matmul_reference via oracle/_ref"})
+    out_path = Path(__file__).with_name("reference_cpu_outputs.json")
+    out_path.write_text(json.dumps({"cases": cases}) + "\n")
+    print("wrote", out_path, "with", len(cases), "cases")
+
+
 def main():
     cases = [small_int4(), small_int8(), square("int4"), square("int8")]
     out = Path(__file__).with_name("reference_kats.json")
     out.write_text(json.dumps({"cases": cases}, indent=1) + "\n")
     print("wrote", out, "with", len(cases), "cases")
+    reference_outputs()
 
 
 if __name__ == "__main__":

@@ -21,7 +21,8 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     import datetime
     dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=120))
-    from metal_native import _C, sharded, workloads
+    from metal_native import _C, sharded
+    import mnq_workloads as workloads
     dev = torch.device("cuda", torch.cuda.current_device())
     cases = [(1, 1024, 4096, "int4", 128, torch.float16),
              (1, 4096, 512, "int4", 128, torch.float16),      # few rows per rank: K split

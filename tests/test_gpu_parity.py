@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import oracle
-from tests import helpers as H
+from oracle import check as H
 
 pytestmark = pytest.mark.gpu
 
@@ -42,7 +42,7 @@ def _tuning(mn, **kw):
     ("int8", 64, 256, 32, True, torch.bfloat16),
 ])
 def test_dequantize_bit_exact(mn, quant, N, K, g, zeros, sdt):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", 1, K, N, quant_type=quant, group_size=g, scale_dtype=sdt,
                              asymmetric=zeros, seed=11)
     ref = H.oracle_dequant(L)
@@ -148,7 +148,7 @@ SWEEP = [
 
 @pytest.mark.parametrize("quant,M,N,K,g,asym,adt,sdt", SWEEP)
 def test_shape_sweep(mn, quant, M, N, K, g, asym, adt, sdt):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
                              scale_dtype=sdt, asymmetric=asym, seed=M * 1000 + N + K)
     ref = H.oracle_matmul(L, threads=1)
@@ -168,7 +168,7 @@ def test_shape_sweep(mn, quant, M, N, K, g, asym, adt, sdt):
 @pytest.mark.parametrize("quant,M,g,adt", [("int4", 1, 128, torch.float16), ("int4", 6, 128, torch.bfloat16),
                                            ("int8", 20, 4096, torch.bfloat16), ("int4", 3, 64, torch.float16)])
 def test_split_k_reduction_and_workspace_reuse(mn, split, quant, M, g, adt):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     K = 4096
     L = workloads.make_layer("t", M, K, 272, quant_type=quant, group_size=g, act_dtype=adt,
                              scale_dtype=torch.float16, asymmetric=(quant == "int4"), seed=split)
@@ -182,7 +182,7 @@ def test_split_k_reduction_and_workspace_reuse(mn, split, quant, M, g, adt):
 
 
 def test_activation_row_stride_and_unaligned_views(mn):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", 4, 256, 64, seed=3)
     ref = H.oracle_matmul(L, threads=1)
     d = L.to("cuda")
@@ -200,7 +200,7 @@ def test_activation_row_stride_and_unaligned_views(mn):
 def test_bf16_activation_range(mn, scale, quant, g):
     """bf16 activations run on fp16 tensor-core instructions after an exact power-of-two
     rescale per CTA: magnitudes far outside the fp16 range must still come out right."""
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", 3, 1024, 160, quant_type=quant, group_size=g, act_dtype=torch.bfloat16,
                              scale_dtype=torch.bfloat16, asymmetric=(quant == "int4"), seed=17)
     L.x = (L.x.float() * scale).to(torch.bfloat16)
@@ -212,7 +212,7 @@ def test_bf16_activation_range(mn, scale, quant, g):
 
 def test_paths_agree(mn):
     """The three kernel families compute the same function."""
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", 8, 1024, 256, seed=9).to("cuda")
     a = mn._C.dequant_matmul(*L.args(), tuning=_tuning(mn, path=mn._C.PATH_GEMV))
     b = mn._C.dequant_matmul(*L.args(), tuning=_tuning(mn, path=mn._C.PATH_GENERIC))
@@ -222,7 +222,7 @@ def test_paths_agree(mn):
 # --------------------------------------------------------------------------- benchmark configurations
 
 def test_config0_qwen05b_down(mn):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     (L,) = workloads.config0()
     ref = H.oracle_matmul(L)
     out = mn._C.dequant_matmul(*L.to("cuda").args())
@@ -231,7 +231,7 @@ def test_config0_qwen05b_down(mn):
 
 
 def test_config1_qwen7b_decode_full_size(mn):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     for L in workloads.config1():
         ref = H.oracle_matmul(L)
         d = L.to("cuda")
@@ -245,7 +245,7 @@ def test_config1_qwen7b_decode_full_size(mn):
 
 @pytest.mark.parametrize("M", [4, 16, 32])
 def test_config2_llama8b_batched_decode(mn, M):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     rng = np.random.default_rng(M)
     for L in workloads.config2(M):
         d = L.to("cuda")
@@ -253,6 +253,10 @@ def test_config2_llama8b_batched_decode(mn, M):
         cols = np.sort(rng.choice(L.N, 1024, replace=False))
         ref = H.oracle_matmul(L, cols=cols)
         H.assert_close_to_oracle(out[:, torch.as_tensor(cols, device="cuda")], ref, f"{L.name} M={M}")
+        # bf16 outputs cannot meet rel-L2 1e-3; the same kernel's fp32 output must
+        out32 = mn._C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
+        H.assert_fp32_gate(out32[:, torch.as_tensor(cols, device="cuda")], ref, f"{L.name} M={M}")
+        assert torch.equal(out32.to(torch.bfloat16), out)
         # whole output against fp32 math on the (bit-exactly verified) dequantised weights
         W = mn.dequantize(d.wq, d.scales, None, d.group_size, "int4", torch.float32)
         full = d.x.float() @ W.t()
@@ -262,7 +266,7 @@ def test_config2_llama8b_batched_decode(mn, M):
 
 @pytest.mark.parametrize("M", [1])
 def test_config4_llama70b_decode_int8_full_size(mn, M):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     rng = np.random.default_rng(4)
     for L in workloads.config4(M):
         d = L.to("cuda")
@@ -270,6 +274,9 @@ def test_config4_llama70b_decode_int8_full_size(mn, M):
         cols = np.sort(rng.choice(L.N, 512, replace=False))
         ref = H.oracle_matmul(L, cols=cols)
         H.assert_close_to_oracle(out[:, torch.as_tensor(cols, device="cuda")], ref, L.name)
+        out32 = mn._C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
+        H.assert_fp32_gate(out32[:, torch.as_tensor(cols, device="cuda")], ref, L.name)
+        assert torch.equal(out32.to(torch.bfloat16), out)
         W = mn.dequantize(d.wq, d.scales, None, d.group_size, "int8", torch.float32)
         full = d.x.float() @ W.t()
         rel = float((out.float() - full).norm() / full.norm())
@@ -281,7 +288,7 @@ def test_config4_llama70b_decode_int8_full_size(mn, M):
 # --------------------------------------------------------------------------- errors
 
 def test_errors_are_raised_before_any_launch(mn):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", 2, 128, 32, seed=1).to("cuda")
     E = mn.MetalNativeError
     with pytest.raises(E, match="InvalidArgument: dequant_matmul: activations must be 2D"):
@@ -325,7 +332,7 @@ def test_host_activations_and_output(mn, M, K, N, quant, g, adt):
     """Activations filled on the CPU, result read on the CPU after synchronize(), as the reference's
     callers do with its shared-memory tensors; the two copies are enqueued with the kernel
     (mnq_dequant_matmul_host).  Same bits as the device-tensor call."""
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
                              asymmetric=adt == torch.float16, seed=M + K)
     d = L.to("cuda")
@@ -358,7 +365,7 @@ def test_fused_swiglu_epilogue(mn, M, K, Hd, quant, g, adt):
     SwiGLU formula (shaders/fused_swiglu.metal:48-84).  Two roundings of 16-bit inputs would give
     the unfused pipeline about 2x the relative error of one projection; the fused kernel rounds
     once, and is held to 2e-3 relative L2 (fp16) or the bf16 rounding floor."""
-    from metal_native import workloads
+    import mnq_workloads as workloads
     L = workloads.make_layer("t", M, K, 2 * Hd, quant_type=quant, group_size=g, act_dtype=adt,
                              asymmetric=adt == torch.float16, seed=Hd + K)
     ref = H.oracle_matmul(L).astype(np.float64)

@@ -15,7 +15,7 @@ from pathlib import Path
 import pytest
 import torch
 
-from tests import helpers as H
+from oracle import check as H
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
@@ -35,7 +35,7 @@ def mn():
     (16, 1024, 208, "int4", 128, torch.bfloat16),   # two token tiles, N not a multiple of the CTA's rows
 ])
 def test_world_of_one_matches_the_plain_operator(mn, M, K, N, quant, g, adt):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     C = mn._C
     L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
                              asymmetric=adt == torch.float16, seed=K + N).to("cuda")
@@ -57,7 +57,7 @@ def test_world_of_one_matches_the_plain_operator(mn, M, K, N, quant, g, adt):
 
 
 def test_shapes_outside_the_decode_kernel_are_refused(mn):
-    from metal_native import workloads
+    import mnq_workloads as workloads
     C = mn._C
     L = workloads.make_layer("t", 64, 256, 128, seed=3).to("cuda")    # M > 32: tensor-core path, no fused gather
     out = torch.empty((64, 128), dtype=torch.float16, device="cuda")

@@ -29,7 +29,8 @@ def _worker(rank, world, port, M, out_dir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    from metal_native import sharded, workloads
+    from metal_native import sharded
+    import mnq_workloads as workloads
     from oracle import oracle
     from tests import helpers as H
 
