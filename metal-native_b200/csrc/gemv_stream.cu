@@ -1,14 +1,16 @@
-// Decode-shaped fused dequantise + matmul, streaming variant: the kernel the benchmark
-// shapes run (M <= 32).  Replaces the reference's dequant_matmul_int{4,8}_vecmat_fp16
-// (shaders/matmul_dequant_kernel.metal:229-345, 485-576), computing every row m < M.
+// Decode-shaped fused dequantise + matmul, the general streaming kernel (M <= 32).  Replaces the
+// reference's dequant_matmul_int{4,8}_vecmat_fp16 (shaders/matmul_dequant_kernel.metal:229-345,
+// 485-576), computing every row m < M.  The common case of at most 8 tokens runs the compact
+// kernel of gemv_lean.cu, which shares this file's plan; this kernel takes 9-32 tokens, groups
+// that span several steps, ragged rows, the fused SwiGLU epilogue and the fused all-gather.
 //
 // Data movement.  Every warp owns 16 consecutive weight rows at a time and a small
-// ring of stages in shared memory; one stage holds a piece of CH consecutive packed
+// ring of stages in shared memory; one stage holds a piece of 256 consecutive packed
 // bytes of each of those rows.  One lane fills a stage with a single TMA tile copy
-// (cp.async.bulk.tensor.2d over a [N, row_bytes] tensor map, box 16 rows x CH bytes,
+// (cp.async.bulk.tensor.2d over a [N, row_bytes] tensor map, box 16 rows x 256 bytes,
 // out-of-range rows and bytes zero-filled) that signals an mbarrier, so the bytes in
 // flight are bounded by shared memory rather than by registers or occupancy, the copy
-// costs one instruction per 4-8 KB, and DRAM sees contiguous bursts.  Lanes pick their
+// costs one instruction per 4 KB, and DRAM sees contiguous bursts.  Lanes pick their
 // MMA fragments out of the stage with 128-bit shared loads.
 //
 // Arithmetic.  m16n8k16 warp MMAs with fp32 accumulators; A = 16 weight rows,
@@ -23,8 +25,14 @@
 // quantisation group gives
 //     sum_k (q - c) * s * x - z * x  =  (s / alpha) * P  -  ((beta + c) * s + z) * X
 // where c = 8 for int4 and 0 for int8, and X is the sum of the group's activations.
-// s / alpha and (beta + c) * s + z are computed once per (row, group) when the warp
-// stages its scales; X once per CTA when the activations are staged.
+// A lane fetches the raw 16-bit scale and zero of its two rows for one piece (four steps)
+// straight into registers, one piece ahead, and widens them when a group closes; X is computed
+// once per CTA when the activations are staged.
+//
+// Start-up.  The first global accesses after the dependency wait are the activation loads; the
+// ring is requested right behind them (or, when the caller has declared the weights immutable,
+// before the wait).  Loads that are issued behind a ring of weight tiles come back only after
+// the tiles: the L2 serves requests in arrival order and every SM asks for its ring at once.
 //
 // When there are too few 16-row blocks to fill the GPU the K range is cut into chunks
 // (grid.y); each warp writes its fp32 partial block to the workspace and the last warp
@@ -42,28 +50,17 @@
 
 #include <type_traits>
 
+#include "gemv_mma_common.cuh"
 #include "mnq_common.cuh"
 
 namespace mnq {
 
-__device__ unsigned int g_device_status = 0;  // bit 0 / bit 1: a bounded wait gave up (GEMV / GEMM)
-
-#ifdef MNQ_TS
-// development aid: per-launch, per-CTA time stamps of warps 0 and last
-__device__ unsigned long long g_ts[64][160][2][16];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TS(k) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x == blockDim.x - 32) && blockIdx.y == 0 && blockIdx.x < 160) \
-    g_ts[p.ts_slot & 63][blockIdx.x][threadIdx.x ? 1 : 0][k] = gtime(); } while (0)
-#else
-#define TS(k) do {} while (0)
-#endif
+__device__ unsigned int g_device_status = 0;  // bit 0: a wait for a weight tile gave up; bit 2: a wait for another rank
 
 namespace {
 
-constexpr int kStepBytes = 64;  // packed bytes of one row consumed per step (4 lanes x 16)
 constexpr int kMaxSplitK = 32;
 constexpr int kMaxSmem = 224 * 1024;
-constexpr unsigned kSpinLimit = 1u << 24;
 
 struct StreamParams {
     const void* x;
@@ -93,189 +90,12 @@ struct StreamParams {
     GatherArgs gather;    // world > 0: store to every rank's gathered buffer, then wait for all slices
     int gather_vec;       // the gathered buffers allow 16-byte stores at every column this call writes
     int defer_reduce;     // K chunks are added by a reduce kernel launched after this one: only store the partial sums
-    int ts_slot;
     int scale_vec;        // scales / zeros of a piece's four groups can be fetched as one aligned 8-byte load per row
     int weights_immutable;  // weights, scales and zeros are not written by earlier work on the stream: prefetch them at once
     unsigned int spin_limit;   // polls a wait on another rank may take before it gives up
     Epilogue epi;         // bias / activation / residual applied before the store; fp32 output mode
     int swiglu_h;         // > 0: fused SwiGLU -- a 16-row tile is 8 gate rows (j) and the 8 up rows (H + j); out is [M, H]
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)  // bounded; false = gave up
-{
-    for (unsigned i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// One TMA tile copy: box of the tensor map at element coordinates (x, y) -> shared memory.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// D = A * B + C with C passed by value, so that a chain can start from literal zeros.
-template <typename T>
-__device__ __forceinline__ void mma_c(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                      uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3);
-template <>
-__device__ __forceinline__ void mma_c<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                              uint32_t a3, uint32_t b0, uint32_t b1, float c0, float c1,
-                                              float c2, float c3)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%11,%12,%13};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
-}
-template <>
-__device__ __forceinline__ void mma_c<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                                     uint32_t a3, uint32_t b0, uint32_t b1, float c0,
-                                                     float c1, float c2, float c3)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%11,%12,%13};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
-}
-
-// Encodings (see the header comment).  inv_alpha multiplies the scale; offset = beta + c.
-// hi_x_scale: the high-nibble encoding of int4/fp16 is 16 times larger than the low-nibble
-// one, so the activations those MMAs consume are staged pre-multiplied by 1/16 (exact in
-// fp16 down to |x| = 2^-10; below that the lost bits are worth less than 2^-25 each) and
-// both encodings accumulate into one fp32 chain.
-template <int QUANT, typename T> struct Enc;
-template <> struct Enc<MNQ_INT4, __half> {
-    static constexpr float inv_alpha = 16777216.f, offset = 8.f;
-    static constexpr bool hi_x_scale = true;
-    // (n0,n4) (n1,n5) (n2,n6) (n3,n7) as L0 H0 L1 H1
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
-    {
-#if defined(MNQ_ABL) && (MNQ_ABL & 4)
-        L0 = w; H0 = w; L1 = w; H1 = w;
-#else
-        const uint32_t w8 = w >> 8;
-        L0 = w & 0x000F000Fu; H0 = w & 0x00F000F0u; L1 = w8 & 0x000F000Fu; H1 = w8 & 0x00F000F0u;
-#endif
-    }
-};
-template <> struct Enc<MNQ_INT4, __nv_bfloat16> {
-    static constexpr float inv_alpha = 1.f, offset = 136.f;
-    static constexpr bool hi_x_scale = false;
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t& L0, uint32_t& H0, uint32_t& L1, uint32_t& H1)
-    {
-        constexpr uint32_t M = 0x000F000Fu, MAGIC = 0x43004300u;
-        L0 = lop3<0xEA>(w, M, MAGIC); H0 = lop3<0xEA>(w >> 4, M, MAGIC);
-        L1 = lop3<0xEA>(w >> 8, M, MAGIC); H1 = lop3<0xEA>(w >> 12, M, MAGIC);
-    }
-};
-template <> struct Enc<MNQ_INT8, __half> {
-    static constexpr float inv_alpha = 16777216.f, offset = 128.f;
-    static constexpr bool hi_x_scale = false;
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
-    {
-        const uint32_t u = w ^ 0x80808080u;
-        A0 = prmt(u, 0u, 0x4140u); A1 = prmt(u, 0u, 0x4342u);
-    }
-};
-template <> struct Enc<MNQ_INT8, __nv_bfloat16> {
-    static constexpr float inv_alpha = 1.f, offset = 0.f;
-    static constexpr bool hi_x_scale = false;
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t& A0, uint32_t& A1)
-    {
-        uint32_t o[2];
-        UnpackInt8<__nv_bfloat16>::run(w, o);
-        A0 = o[0]; A1 = o[1];
-    }
-};
-
-// One step: 64 packed bytes of 16 rows against NT x 8 activation rows, accumulated into
-// acc (one chain of 8 MMAs; with ZERO_START it starts from zero in this step).  xb[nt] points
-// at this lane's 16 bytes of the step's first 8-block (int4) / 32 bytes (int8) in the staged
-// activation row; all further offsets are compile-time constants.
-template <int QUANT, typename T, int NT, bool ZERO_START>
-__device__ __forceinline__ void step_mma(const uint4& wa, const uint4& wb, const unsigned char* const (&xb)[NT],
-                                         float (&acc)[NT][4])
-{
-    const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w};
-    const uint32_t bw[4] = {wb.x, wb.y, wb.z, wb.w};
-    if (QUANT == MNQ_INT4) {
-#pragma unroll
-        for (int jw = 0; jw < 4; ++jw) {
-            uint32_t aL0, aH0, aL1, aH1, bL0, bH0, bL1, bH1;
-            Enc<MNQ_INT4, T>::run(aw[jw], aL0, aH0, aL1, aH1);
-            Enc<MNQ_INT4, T>::run(bw[jw], bL0, bH0, bL1, bH1);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + jw * 64);
-                if (ZERO_START && jw == 0)
-                    mma_c<T>(acc[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
-                else
-                    mma_c<T>(acc[nt], aL0, bL0, aL1, bL1, xv.x, xv.y, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-                mma_c<T>(acc[nt], aH0, bH0, aH1, bH1, xv.z, xv.w, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int jw = 0; jw < 4; jw += 2) {
-            uint32_t a0, a1, b0, b1, c0, c1, d0, d1;
-            Enc<MNQ_INT8, T>::run(aw[jw], a0, a1);
-            Enc<MNQ_INT8, T>::run(bw[jw], b0, b1);
-            Enc<MNQ_INT8, T>::run(aw[jw + 1], c0, c1);
-            Enc<MNQ_INT8, T>::run(bw[jw + 1], d0, d1);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + jw * 8);
-                if (ZERO_START && jw == 0)
-                    mma_c<T>(acc[nt], a0, b0, a1, b1, xv.x, xv.y, 0.f, 0.f, 0.f, 0.f);
-                else
-                    mma_c<T>(acc[nt], a0, b0, a1, b1, xv.x, xv.y, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-                mma_c<T>(acc[nt], c0, d0, c1, d1, xv.z, xv.w, acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-            }
-        }
-    }
-}
-
-// tot += S * acc - Z * X for the lane's two rows (S0/Z0: row r, S1/Z1: row r+8).  xsum_lane
-// points at this lane's pair of activation sums of the group (columns 2t, 2t+1 of tile 0).
-template <int NT>
-__device__ __forceinline__ void close_group(float (&tot)[NT][4], const float (&acc)[NT][4], float S0, float S1,
-                                            float Z0, float Z1, const float* xsum_lane)
-{
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const float2 X = *reinterpret_cast<const float2*>(xsum_lane + nt * 8);
-        tot[nt][0] = fmaf(-Z0, X.x, fmaf(S0, acc[nt][0], tot[nt][0]));
-        tot[nt][1] = fmaf(-Z0, X.y, fmaf(S0, acc[nt][1], tot[nt][1]));
-        tot[nt][2] = fmaf(-Z1, X.x, fmaf(S1, acc[nt][2], tot[nt][2]));
-        tot[nt][3] = fmaf(-Z1, X.y, fmaf(S1, acc[nt][3], tot[nt][3]));
-    }
-}
 
 // T is the activation / output type.  The MMAs always run in fp16: bf16 activations are
 // converted while they are staged, multiplied by a power of two chosen per CTA so that the
@@ -296,7 +116,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
     extern __shared__ __align__(128) unsigned char smem[];
 
-    TS(0);
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -348,7 +167,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
     __syncwarp();
 
-    TS(1);
     // Producer state: next piece to request (row block, piece, stage).  One lane issues a
     // single TMA tile copy per piece; rows past N and bytes past the row end are zero-filled
     // by the TMA unit, so every piece is a full box.
@@ -531,14 +349,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
         S = s0 * Enc<QUANT, MT>::inv_alpha;
         Z = fmaf(Enc<QUANT, MT>::offset, s0, z0);
-#if defined(MNQ_ABL) && (MNQ_ABL & 1)
-        S = __uint_as_float(sv.x); Z = __uint_as_float(zv.x);
-#endif
     };
 
-    // The weight stream starts first: the ring is requested before anything else is read, so
-    // the copies are in flight while the activations are staged.  With `weights_immutable` that
-    // happens even before the wait below.
+    // Immutable weights: the ring and the first scales are requested before the wait below, while
+    // the previous kernel in the stream may still be running.
     ScaleRegs sc_cur, sc_nxt;
     sc_cur.s0 = sc_cur.s1 = sc_cur.z0 = sc_cur.z1 = make_uint2(0u, 0u);
     sc_nxt = sc_cur;
@@ -550,9 +364,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     // in the stream was still running.  Everything above touched only this CTA's shared memory
     // (and, if the caller declared them immutable, weights, scales and zeros); every other global
     // read comes after that kernel and its writes completed.
-    TS(2);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TS(3);
     // the next kernel in the stream may be scheduled as soon as this one leaves room
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -589,9 +401,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
         if (total_pieces > 0) load_scales(0, 0, sc_cur);
     }
-    TS(5);
     __syncthreads();   // xsum (and x_max_bits) are zeroed
-    TS(6);
 
     if (CONVERT_X) {
         // largest |x| of the chunk -> power-of-two scale that puts it just below 2^15
@@ -628,7 +438,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 #pragma unroll
     for (int u = 0; u < XB; ++u)
         if (__any_sync(0xffffffffu, xm[u] >= 0)) store_x_block(xv[u], xm[u], xb[u], xk[u]);
-    TS(7);
     // whatever did not fit in the first batch (M > 8)
     {
         constexpr int XB2 = 8;   // deeper batches for the bulk of a many-token activation block
@@ -647,12 +456,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
     }
     __syncthreads();
-    TS(8);
     for (int i = tid; i < p.segs * NT * 8; i += blockDim.x)
         xsum[i] = static_cast<float>(static_cast<long long>(xsumi[i])) * (1.f / 16777216.f);
     __syncthreads();
 
-    TS(9);
     // ---- main loop ----------------------------------------------------------------------------
     // this lane's position inside a staged activation row: 16 bytes per 8-block at lane t (int4),
     // 32 bytes at lane t (int8)
@@ -725,13 +532,9 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
         for (int pc = 0; pc < ppr; ++pc) {
             // scales and zeros of the piece after this one (the next row block's first, at the end of a row)
-#if !(defined(MNQ_ABL) && (MNQ_ABL & 8))
             if (pc + 1 < ppr) load_scales(rbi, pc + 1, sc_nxt);
             else if (rbi + 1 < nrb) load_scales(rbi + 1, 0, sc_nxt);
-#endif
             if (!mbar_wait(smem_u32(&bars[stage]), parity)) { gave_up = true; break; }
-            if (rbi == 0 && pc == 0) TS(10);
-            if (rbi == nrb - 1 && pc == ppr - 1) TS(11);
             const unsigned char* st0 = ring + stage * STAGE_BYTES + wr * RS + t * 16;
             const unsigned char* st1 = st0 + 8 * RS;
             if (bytes_left >= CH && group_is_step) {
@@ -755,14 +558,7 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     for (int nt = 0; nt < NT; ++nt) xb[nt] = xrow[nt] + xoff + ps * STEP * 2;
                     float a4[NT][4];
                     step_mma<QUANT, MT, NT, true>(wa[ps], wb[ps], xb, a4);
-#if defined(MNQ_ABL) && (MNQ_ABL & 2)
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) tot[nt][i] += a4[nt][i] * Sa[ps] + Za[ps] + Sb[ps] + Zb[ps];
-#else
                     close_group<NT>(tot, a4, Sa[ps], Sb[ps], Za[ps], Zb[ps], Xp + ps * (NT * 8));
-#endif
                 }
                 s += PSTEPS;
                 xoff += PSTEPS * STEP * 2;
@@ -883,7 +679,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
     }
 
-    TS(12);
     if (p.gather.world > 0) {
         // Every thread's peer stores become visible system-wide, then the CTA reports in; the last
         // CTA of the grid tells every rank that this rank's slice of this call is complete and
@@ -956,7 +751,6 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
         }
     }
 
-    TS(13);
     if (gave_up) {
         if (lane == 0) atomicOr(&g_device_status, 1u);
         // The arrival counters must still return to zero (the workspace is reused by later calls):
@@ -979,6 +773,7 @@ struct StreamPlan {
     int nt, warps, rbw, num_chunks, steps_per_chunk, total_steps, segs, xs_stride, piece_bytes, stages;
     size_t smem;
     unsigned grid_x;
+    int resident_ctas;   // SMs x CTAs per SM the plan assumed
 };
 
 bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, StreamPlan* out)
@@ -1001,7 +796,9 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
 
     // 16 warps per CTA (measured: always better than 8 at equal work); the widest activation
     // tile is compiled for 256 threads
-    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : (pl.nt >= 4 ? 8 : 16);
+    // Up to 8 tokens: CTAs of 8 warps, two per SM (measured 1 us per launch better than one CTA of 16 on
+    // the Qwen2.5-7B shapes: a CTA of the next kernel starts its set-up while its neighbour still streams)
+    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : (pl.nt == 2 ? 16 : 8);
     if (warps > 16) warps = 16;
     if (pl.nt >= 4 && warps > 8) warps = 8;
     while (warps > 1 && row_blocks < warps) warps >>= 1;
@@ -1010,12 +807,14 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     if (pl.piece_bytes != 256) return false;   // one piece = four steps; its scales travel as four values per row
     // more than 8 tokens: chunks are short and there are fewer warps, so each warp keeps more
     // pieces in flight (the loop below takes stages away again if shared memory runs out)
-    // as deep a ring as shared memory allows (the loop below takes stages away until the plan fits);
-    // a warp never has use for more stages than it has pieces
-    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : 8;
+    // Two pieces in flight per warp already keep HBM busy; a deeper ring only delays the activation
+    // loads, which queue in L2 behind every SM's outstanding weight requests (measured: three stages
+    // cost 1.5 us per launch on the Qwen2.5-7B gate+up shape).  With more than 8 tokens the chunks
+    // are short and there are fewer warps, so each warp keeps more pieces in flight.
+    pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : (pl.nt >= 2 ? 4 : 2);
     if (pl.stages > 8) pl.stages = 8;
     if (pl.stages < 2) pl.stages = 2;
-    const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : 1;
+    const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : (pl.nt == 1 ? 2 : 1);
     const int64_t slots = static_cast<int64_t>(a.sm_count) * ctas_per_sm * warps;
 
     // K chunks.  A warp processes `rbw` units (row block x chunk) one after the other, so the
@@ -1038,7 +837,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         for (int c = 1; c <= kMaxSplitK && c <= pl.total_steps; ++c) {
             int spc = (pl.total_steps + c - 1) / c;
             if (c > 1 && spc < 4) break;
-            if (many_tokens && c > 1) spc = (spc + 3) & ~3;   // whole 256-byte pieces: the unrolled path
+            if (c > 1) spc = (spc + 3) & ~3;   // whole 256-byte pieces: no partial piece at a chunk's end
             double cost;
             if (many_tokens) {
                 const int64_t per_warp = (row_blocks * c + slots - 1) / slots;           // units per warp
@@ -1058,7 +857,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
 
     for (;;) {
         pl.steps_per_chunk = (pl.total_steps + chunks - 1) / chunks;
-        if (many_tokens && chunks > 1) pl.steps_per_chunk = (pl.steps_per_chunk + 3) & ~3;
+        if (chunks > 1) pl.steps_per_chunk = (pl.steps_per_chunk + 3) & ~3;
         pl.num_chunks = (pl.total_steps + pl.steps_per_chunk - 1) / pl.steps_per_chunk;
         const int64_t units = row_blocks * pl.num_chunks;
         // a warp takes at most rbw_cap consecutive row blocks (their scales are all staged up
@@ -1106,6 +905,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
         if (chunks == 1) return false;
         --chunks;
     }
+    pl.resident_ctas = a.sm_count * ctas_per_sm;
     pl.grid_x = static_cast<unsigned>((row_blocks + static_cast<int64_t>(pl.warps) * rbw - 1) /
                                       (static_cast<int64_t>(pl.warps) * rbw));
     *out = pl;
@@ -1201,9 +1001,6 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
     p.swiglu_h = static_cast<int>(a.swiglu_h);
     p.epi = a.epi;
     p.gather = a.gather;
-#ifdef MNQ_TS
-    { static int slot = 0; p.ts_slot = slot++; }
-#endif
     p.weights_immutable = option_value(MNQ_OPT_WEIGHTS_IMMUTABLE) != 0 ? 1 : 0;
     p.spin_limit = static_cast<unsigned int>(option_value(MNQ_OPT_PEER_WAIT_POLLS));
     // one aligned 8-byte load fetches a row's four scales of a piece: rows and chunk starts must
@@ -1243,6 +1040,11 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
                                              CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc8) return rc8;
     }
+    // the compact kernel takes the common decode case (see gemv_lean.cu); variant 3 forces this one
+    if (pl.nt == 1 && !(tuning && tuning->gemv_variant == 3)) {
+        LeanShape ls{pl.warps, pl.num_chunks, pl.steps_per_chunk, pl.total_steps, pl.stages, pl.resident_ctas};
+        if (gemv_lean_supported(a, ls)) return launch_gemv_lean(a, ls, wmap);
+    }
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
 #define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, wmap8, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
@@ -1271,15 +1073,14 @@ int read_device_status(unsigned int* out, bool clear)
         rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &zero, sizeof zero), "cudaMemcpyToSymbol(status)");
         if (rc) return rc;
     }
-    unsigned int g = 0;
+    unsigned int g = 0, l = 0;
     rc = read_gemm_status(&g, clear);
     if (rc) return rc;
-    *out = v | g;
+    rc = read_lean_status(&l, clear);
+    if (rc) return rc;
+    *out = v | g | l;
     return MNQ_SUCCESS;
 }
 
-#ifdef MNQ_TS
-extern "C" MNQ_API int mnq_dbg_ts(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_ts, sizeof(g_ts)); }
-#endif
 
 }  // namespace mnq

@@ -291,6 +291,16 @@ int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType
                          uint64_t dim0, uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1,
                          CUtensorMapSwizzle swizzle);
 #endif
+// The streaming plan's figures the compact decode kernel (gemv_lean.cu) needs.
+struct LeanShape {
+    int warps, num_chunks, steps_per_chunk, total_steps, stages;
+    int resident_ctas;   // CTAs the plan expects to be resident on the GPU at once
+};
+bool gemv_lean_supported(const MatmulArgs& a, const LeanShape& s);
+#ifdef CUDA_VERSION
+int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap& wmap);
+#endif
+int read_lean_status(unsigned int* out, bool clear);
 int launch_generic(const MatmulArgs& a);
 bool gemv_supported(const MatmulArgs& a);
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);

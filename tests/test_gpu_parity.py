@@ -181,6 +181,36 @@ def test_split_k_reduction_and_workspace_reuse(mn, split, quant, M, g, adt):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "split-K result is not deterministic"
 
 
+@pytest.mark.parametrize("quant,M,N,K,g,asym,adt", [
+    ("int4", 1, 4096, 3584, 128, True, torch.float16),      # a step is a group: scales as 8-byte loads
+    ("int4", 1, 528, 18944, 128, True, torch.float16),      # few rows: K split, last-arriver reduction
+    ("int4", 4, 1000, 4096, 128, False, torch.bfloat16),    # bf16 activations and scales, ragged last row block
+    ("int4", 8, 2048, 2048, 128, True, torch.bfloat16),
+    ("int8", 1, 2048, 8192, 8192, False, torch.bfloat16),   # one group per row
+    ("int8", 6, 272, 28672, 28672, False, torch.bfloat16),  # one group per row, K split
+    ("int8", 3, 1024, 1024, 64, True, torch.float16),       # int8 with a group per step
+])
+def test_compact_and_general_decode_kernels(mn, quant, M, N, K, g, asym, adt):
+    """Shapes the compact decode kernel takes, through it (the default) and through the general
+    streaming kernel (kernel variant 3): both against the oracle, twice in a row on one workspace."""
+    import mnq_workloads as workloads
+    C = mn._C
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             scale_dtype=adt if quant == "int4" else torch.float16, asymmetric=asym, seed=N + K)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    general = _tuning(mn, gemv_variant=3)
+    for call in range(2):
+        a = C.dequant_matmul(*d.args())
+        b = C.dequant_matmul(*d.args(), tuning=general)
+        C.synchronize()
+        assert C.device_status() == 0
+        H.assert_close_to_oracle(a, ref, f"compact {quant} {M}x{N}x{K} call {call}")
+        H.assert_close_to_oracle(b, ref, f"general {quant} {M}x{N}x{K} call {call}")
+    a32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
+    H.assert_fp32_gate(a32, ref, f"compact fp32 {quant} {M}x{N}x{K}")
+
+
 def test_activation_row_stride_and_unaligned_views(mn):
     import mnq_workloads as workloads
     L = workloads.make_layer("t", 4, 256, 64, seed=3)

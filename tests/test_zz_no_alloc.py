@@ -51,8 +51,12 @@ def test_static_entry_point_matches_the_ordinary_one_twice(C, M, K, N, quant, g)
                              seed=K + N).to("cuda")
     expected = C.dequant_matmul(*L.args())
     out = torch.empty((M, N), dtype=L.x.dtype, device="cuda")
-    assert _static_call(C, L, out) == 0, C._lib.mnq_last_error().decode()   # first call on the device: address look-up
+    # a dry run of everything the loop below does: the first call on a device looks the array's address
+    # up, and a kernel's first launch (ours, or torch's fill and compare) loads its code into device memory
+    out.fill_(float("nan"))
+    assert _static_call(C, L, out) == 0, C._lib.mnq_last_error().decode()
     torch.cuda.synchronize()
+    assert torch.equal(out, expected)
     free_before, torch_before = _free_bytes(), torch.cuda.memory_allocated()
     for call in range(2):                       # the second call finds the scratch as the first left it
         out.fill_(float("nan"))
