@@ -25,8 +25,16 @@
 
 namespace mnq {
 
-__device__ unsigned int g_lean_status = 0;   // bit 0: a bounded wait for a weight tile gave up
+__device__ unsigned int g_lean_status = 0;   // bit 0: a bounded wait for a weight tile gave up; bit 2: a wait for another rank
 
+
+#ifdef MNQ_TS
+__device__ unsigned long long g_gts[64][16];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define GTS(k) (g_gts[p.ts_slot & 63][k] = gtime())
+#else
+#define GTS(k) ((void)0)
+#endif
 
 namespace {
 
@@ -51,11 +59,21 @@ struct LeanParams {
     int xsum_bytes;                // bytes of the activation-sum area that follows the staged rows
     int weights_immutable;
     Epilogue epi;
+    GatherArgs gather;             // world > 0: the result goes to every rank's gathered buffer (GATHER kernels)
+    int gather_vec;                // the gathered buffers allow 16-byte stores at every row block this call writes
+    int stage_rbs;                 // row blocks of output a CTA may stage before it stores them to the peers
+    unsigned int spin_limit;       // polls a wait on another rank may take
+    int ts_slot;
 };
 
 // GROUPED: every step is one quantisation group (scale and offset applied per step); otherwise
 // one group per row (applied once per row block).
-template <int QUANT, typename T, bool GROUPED>
+// GATHER: column-sharded call (mnq_dequant_matmul_gather).  Finished row blocks are staged in shared
+// memory as [token][column]; when the CTA's warps are done it stores them into every rank's gathered
+// buffer through peer-mapped pointers (16-byte pieces) and reports in; the last CTA of the grid
+// publishes this rank's call number in every rank's flag block and waits, bounded, for every rank's
+// number to arrive here.  The protocol and the flag words are those of gemv_stream_kernel.
+template <int QUANT, typename T, bool GROUPED, bool GATHER>
 __global__ void __launch_bounds__(512)
 gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ CUtensorMap wmap)
 {
@@ -83,11 +101,19 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
     const long long gw = (long long)blockIdx.x * warps + warp, W = (long long)gridDim.x * warps;
     const int rb_first = static_cast<int>(gw * p.row_blocks / W);
     const int nrb = static_cast<int>((gw + 1) * p.row_blocks / W) - rb_first;
+    const int rb_cta = static_cast<int>((long long)blockIdx.x * warps * p.row_blocks / W);          // the CTA's first row block
+    const int nrb_cta = static_cast<int>(((long long)blockIdx.x + 1) * warps * p.row_blocks / W) - rb_cta;
+    __shared__ int peers_ready_cta;   // GATHER: 1 every rank has begun this call, -1 the wait for that gave up
     const int total_pieces = nrb * ppr;
 
     unsigned char* xs = smem;                                                       // [M][xs_stride]
     float* xsum = reinterpret_cast<float*>(smem + p.M * p.xs_stride);               // GROUPED: [nsteps][8]; else [8] then [M][nsteps]
-    unsigned char* ring = smem + ((p.M * p.xs_stride + p.xsum_bytes + 1023) & ~1023) + warp * (p.stages * STAGE_BYTES + 128);
+    // GATHER: [token][stage_rbs * 16] outputs, then one "staged" byte per row block
+    T* ostage = reinterpret_cast<T*>(smem + p.M * p.xs_stride + p.xsum_bytes);
+    unsigned char* staged = reinterpret_cast<unsigned char*>(ostage + (GATHER ? p.M * p.stage_rbs * 16 : 0));
+    const int ostage_bytes = GATHER ? ((p.M * p.stage_rbs * 32 + p.stage_rbs + 15) & ~15) : 0;
+    unsigned char* ring = smem + ((p.M * p.xs_stride + p.xsum_bytes + ostage_bytes + 1023) & ~1023) +
+                          warp * (p.stages * STAGE_BYTES + 128);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(ring + p.stages * STAGE_BYTES);
 
     // ---- the weight stream starts at once ------------------------------------------------------
@@ -147,6 +173,9 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
     // access comes after the previous kernel in the stream has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef MNQ_TS
+    if (GATHER && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) GTS(0);
+#endif
 
     // ---- activations: this CTA's K chunk of every token, as 8-blocks ----------------------------
     const int bpr = nsteps * SEG;                 // 8-blocks per token row
@@ -165,6 +194,21 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
     if (!p.weights_immutable) {
         for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
         if (nrb > 0) load_scales(sc_cur);
+    }
+    // Sharded call: number of this call (the same on every rank), and the announcement that this
+    // rank has begun it: whatever read its gathered output of the previous call came earlier in
+    // the stream, so peers may overwrite that buffer from now on.
+    unsigned int call_no = 0;
+    if (GATHER) {
+        unsigned int* mine = p.gather.flag_peer[p.gather.rank];
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(call_no) : "l"(mine + kGatherEpochWord) : "memory");
+        call_no += 1u;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
+            for (int g = 0; g < p.gather.world; ++g)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;"
+                             ::"l"(p.gather.flag_peer[g] + kGatherReadyBase + p.gather.rank), "r"(call_no) : "memory");
+        if (tid == 0) peers_ready_cta = 0;
+        for (int i = tid; i < p.stage_rbs; i += blockDim.x) staged[i] = 0;
     }
     float x_down = 1.f, x_up = 1.f;               // 2^-shift and 2^shift of the bf16 -> fp16 rescale
     if (CONVERT_X) {
@@ -260,6 +304,11 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
         if (scale_bf16) { a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xFFFF0000u); }
         else { const float2 f = __half22float2(u32_as_h2(w)); a = f.x; b = f.y; }
     };
+    // one finished output: stored (with the epilogue), or staged for the peers
+    auto emit = [&](int m, int n, float v) {
+        if (!GATHER) store_result<T>(p.epi, p.out, p.ldc, m, n, v);
+        else ostage[(m * p.stage_rbs + (n >> 4) - rb_cta) * 16 + (n & 15)] = F16Traits<T>::from_float(v);
+    };
     bool gave_up = false;
     int rb_arrived = 0;
     int stage = 0;
@@ -334,8 +383,9 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
             for (int i = 0; i < 4; ++i) {
                 const int m = 2 * t + (i & 1);
                 const int n = (i & 2) ? n0 + 8 : n0;
-                if (m < p.M && n < p.N) store_result<T>(p.epi, p.out, p.ldc, m, n, CONVERT_X ? tot[0][i] * x_up : tot[0][i]);
+                if (m < p.M && n < p.N) emit(m, n, CONVERT_X ? tot[0][i] * x_up : tot[0][i]);
             }
+            if (GATHER && lane == 0) staged[rb - rb_cta] = 1;
             continue;
         }
         float* mine = p.partial + (size_t)blockIdx.y * p.M * p.N;
@@ -369,10 +419,100 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
                 for (int c = 0; c < 8; ++c)
                     if (c0 + c < p.num_chunks) v += part[c];
             }
-            if (n < p.N) store_result<T>(p.epi, p.out, p.ldc, m, n, v);
+            if (n < p.N) emit(m, n, v);
         }
         __syncwarp();
         if (lane == 0) p.counters[rb] = 0u;   // leave the counters ready for the next call
+        if (GATHER && lane == 0) staged[rb - rb_cta] = 1;
+    }
+
+    if (GATHER) {
+        __syncthreads();   // every warp's outputs are staged
+        bool any = false;
+        for (int i = 0; i < nrb_cta; ++i) any |= staged[i] != 0;
+        if (tid == 0 && any) {
+            // every rank has begun this call, i.e. none still reads the previous call's gathered output
+            // (the words are written by the peers; nothing is read through them, so plain loads do)
+            const volatile unsigned int* ready = p.gather.flag_peer[p.gather.rank] + kGatherReadyBase;
+            int ok = 1;
+            for (int g = 0; g < p.gather.world && ok > 0; ++g) {
+                bool in = false;
+                for (unsigned int spin = 0; spin < p.spin_limit && !in; ++spin) {
+                    in = static_cast<int>(ready[g] - call_no) >= 0;
+                    if (!in) __nanosleep(100);
+                }
+                if (!in) ok = -1;
+            }
+            peers_ready_cta = ok;
+        }
+        __syncthreads();
+        if (any && peers_ready_cta > 0) {
+            // (rank, row block, token, half of the block's 16 columns): one 16-byte store each
+            const int per_rank = nrb_cta * p.M * 2;
+            for (int idx = tid; idx < per_rank * p.gather.world; idx += blockDim.x) {
+                const int g = idx / per_rank;
+                int e = idx - g * per_rank;
+                const int rbl = e / (p.M * 2);
+                e -= rbl * p.M * 2;
+                const int m = e >> 1, h = e & 1;
+                if (!staged[rbl]) continue;
+                const int n = (rb_cta + rbl) * 16 + h * 8;
+                const T* src = ostage + (m * p.stage_rbs + rbl) * 16 + h * 8;
+                T* dst = static_cast<T*>(p.gather.out_peer[g]) + (size_t)m * p.ldc + p.gather.n_offset + n;
+                if (p.gather_vec && n + 8 <= p.N) {
+                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    for (int k = 0; k < 8; ++k)
+                        if (n + k < p.N) dst[k] = src[k];
+                }
+            }
+        }
+        // The thread that reports for the CTA orders every thread's peer stores (the barrier puts
+        // them before it) ahead of its arrival with a device-scope fence; the last CTA to arrive has
+        // thereby observed every CTA's stores, and its one system-scope fence (fences are cumulative)
+        // orders them all ahead of the arrival words it sends out.  (A system-scope fence per CTA
+        // cost 6-8 us per launch: three hundred of them queue behind each other.)  The last CTA then
+        // waits, bounded, until every rank's word says the same here: the kernel's completion means
+        // "the gathered output is complete here".
+        __syncthreads();
+        if (tid == 0) {
+            if (any && peers_ready_cta < 0) atomicOr(&g_lean_status, 4u);
+#ifdef MNQ_TS
+            const unsigned long long t_before_fence = gtime();
+#endif
+            __threadfence();
+#ifdef MNQ_TS
+            const unsigned long long t_after_fence = gtime();
+#endif
+            unsigned int* mine = p.gather.flag_peer[p.gather.rank];
+            const unsigned int total = gridDim.x * gridDim.y;
+            if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
+#ifdef MNQ_TS
+                g_gts[p.ts_slot & 63][1] = t_before_fence; g_gts[p.ts_slot & 63][2] = t_after_fence;
+#endif
+                GTS(3);
+                mine[kGatherCounterWord] = 0u;   // ready for the next call
+                __threadfence_system();
+                GTS(4);
+                for (int g = 0; g < p.gather.world; ++g)
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
+                                 "r"(call_no) : "memory");
+                bool all_in = true;
+                for (int src = 0; src < p.gather.world && all_in; ++src) {
+                    bool in = false;
+                    for (unsigned int spin = 0; spin < p.spin_limit && !in; ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
+                        in = static_cast<int>(v - call_no) >= 0;
+                        if (!in) __nanosleep(100);
+                    }
+                    all_in = in;
+                }
+                GTS(5);
+                if (!all_in) atomicOr(&g_lean_status, 4u);   // a rank never reported: give up, do not hang
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine + kGatherEpochWord), "r"(call_no) : "memory");
+            }
+        }
     }
 
     if (gave_up) {
@@ -390,10 +530,10 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
     }
 }
 
-template <int QUANT, typename T, bool GROUPED>
+template <int QUANT, typename T, bool GROUPED, bool GATHER>
 int launch_lean_one(const LeanParams& p, const CUtensorMap& wmap, dim3 grid, int threads, size_t smem, cudaStream_t stream)
 {
-    auto* kern = &gemv_lean_kernel<QUANT, T, GROUPED>;
+    auto* kern = &gemv_lean_kernel<QUANT, T, GROUPED, GATHER>;
     if (smem > 48 * 1024) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanMaxSmem),
                                   "cudaFuncSetAttribute(gemv_lean)");
@@ -412,14 +552,30 @@ int launch_lean_one(const LeanParams& p, const CUtensorMap& wmap, dim3 grid, int
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, wmap), "gemv_lean launch");
 }
 
-size_t lean_smem(const MatmulArgs& a, const LeanShape& s, int* xs_stride, int* xsum_bytes)
+// row blocks one CTA handles at most (they are dealt out evenly over one wave of CTAs)
+int lean_grid_x(const MatmulArgs& a, const LeanShape& s)
+{
+    const int64_t row_blocks = (a.N + 15) / 16;
+    const int64_t want = (row_blocks + s.warps - 1) / s.warps;
+    const int64_t cap = s.resident_ctas / s.num_chunks > 0 ? s.resident_ctas / s.num_chunks : 1;
+    return static_cast<int>(want < cap ? want : cap);
+}
+
+size_t lean_smem(const MatmulArgs& a, const LeanShape& s, int* xs_stride, int* xsum_bytes, int* stage_rbs_out = nullptr)
 {
     const int step = a.quant == MNQ_INT4 ? 128 : 64;
     const bool grouped = a.group_size < a.K;
     const int64_t chunk_k = static_cast<int64_t>(s.steps_per_chunk) * step;
     *xs_stride = static_cast<int>(chunk_k * 2 + (a.quant == MNQ_INT4 ? 64 : 16));   // the pad staggers rows over banks
     *xsum_bytes = grouped ? s.steps_per_chunk * 8 * 4 : (8 + static_cast<int>(a.M) * s.steps_per_chunk) * 4;
-    return ((static_cast<size_t>(a.M) * *xs_stride + *xsum_bytes + 1023) & ~size_t(1023)) +
+    int stage_rbs = 0, ostage_bytes = 0;
+    if (a.gather.world > 0) {
+        const int64_t row_blocks = (a.N + 15) / 16;
+        stage_rbs = static_cast<int>((row_blocks + lean_grid_x(a, s) - 1) / lean_grid_x(a, s)) + 1;
+        ostage_bytes = (static_cast<int>(a.M) * stage_rbs * 32 + stage_rbs + 15) & ~15;
+    }
+    if (stage_rbs_out) *stage_rbs_out = stage_rbs;
+    return ((static_cast<size_t>(a.M) * *xs_stride + *xsum_bytes + ostage_bytes + 1023) & ~size_t(1023)) +
            static_cast<size_t>(s.warps) * (static_cast<size_t>(s.stages) * 16 * kPieceBytes + 128);
 }
 
@@ -428,7 +584,8 @@ size_t lean_smem(const MatmulArgs& a, const LeanShape& s, int* xs_stride, int* x
 bool gemv_lean_supported(const MatmulArgs& a, const LeanShape& s)
 {
     const int step = a.quant == MNQ_INT4 ? 128 : 64;
-    if (a.M < 1 || a.M > 8 || a.gather.world > 0 || a.swiglu_h > 0) return false;
+    if (a.M < 1 || a.M > 8 || a.swiglu_h > 0) return false;
+    if (a.gather.world > 0 && (a.epi.kind != MNQ_EPI_NONE || a.epi.out_f32)) return false;
     if (a.K % step || s.total_steps % kPieceSteps) return false;                       // whole pieces only
     if (s.num_chunks > 1 && s.steps_per_chunk % kPieceSteps) return false;
     const bool grouped = a.group_size < a.K;
@@ -456,23 +613,34 @@ int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap&
     p.stages = s.stages;
     p.row_blocks = static_cast<int>((a.N + 15) / 16);
     p.scale_bf16 = a.scale_dtype == MNQ_BF16 ? 1 : 0;
-    const size_t smem = lean_smem(a, s, &p.xs_stride, &p.xsum_bytes);
+    const size_t smem = lean_smem(a, s, &p.xs_stride, &p.xsum_bytes, &p.stage_rbs);
+    p.gather = a.gather;
+    p.spin_limit = static_cast<unsigned int>(option_value(MNQ_OPT_PEER_WAIT_POLLS));
+    if (a.gather.world > 0) {   // 16-byte peer stores: every row block starts on a 16-byte boundary of every buffer
+        bool ok = (a.ldc * 2) % 16 == 0 && (a.gather.n_offset * 2) % 16 == 0;
+        for (int g = 0; g < a.gather.world; ++g) ok = ok && reinterpret_cast<uintptr_t>(a.gather.out_peer[g]) % 16 == 0;
+        p.gather_vec = ok ? 1 : 0;
+    }
     p.weights_immutable = option_value(MNQ_OPT_WEIGHTS_IMMUTABLE) != 0 ? 1 : 0;
     p.epi = a.epi;
+#ifdef MNQ_TS
+    { static int slot = 0; p.ts_slot = slot++; }
+#endif
     if (s.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
     // one wave of CTAs at most: the rest is dealt out inside the kernel
-    const int64_t want = (static_cast<int64_t>(p.row_blocks) + s.warps - 1) / s.warps;
-    const int64_t cap = s.resident_ctas / s.num_chunks > 0 ? s.resident_ctas / s.num_chunks : 1;
-    const dim3 grid(static_cast<unsigned>(want < cap ? want : cap), static_cast<unsigned>(s.num_chunks), 1);
+    const dim3 grid(static_cast<unsigned>(lean_grid_x(a, s)), static_cast<unsigned>(s.num_chunks), 1);
     const int threads = s.warps * 32;
     const bool grouped = a.group_size < a.K;
+    const bool gather = a.gather.world > 0;
 #define MNQ_LEAN(Q, T)                                                                                  \
-    return grouped ? launch_lean_one<Q, T, true>(p, wmap, grid, threads, smem, a.stream)                \
-                   : launch_lean_one<Q, T, false>(p, wmap, grid, threads, smem, a.stream)
+    return grouped ? (gather ? launch_lean_one<Q, T, true, true>(p, wmap, grid, threads, smem, a.stream)   \
+                             : launch_lean_one<Q, T, true, false>(p, wmap, grid, threads, smem, a.stream)) \
+                   : (gather ? launch_lean_one<Q, T, false, true>(p, wmap, grid, threads, smem, a.stream)  \
+                             : launch_lean_one<Q, T, false, false>(p, wmap, grid, threads, smem, a.stream))
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_LEAN(MNQ_INT4, __half);
         MNQ_LEAN(MNQ_INT4, __nv_bfloat16);
@@ -482,6 +650,10 @@ int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap&
 #undef MNQ_LEAN
 }
 
+
+#ifdef MNQ_TS
+extern "C" MNQ_API int mnq_dbg_gts(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gts, sizeof(g_gts)); }
+#endif
 
 int read_lean_status(unsigned int* out, bool clear)
 {

@@ -680,9 +680,9 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     }
 
     if (p.gather.world > 0) {
-        // Every thread's peer stores become visible system-wide, then the CTA reports in; the last
-        // CTA of the grid tells every rank that this rank's slice of this call is complete and
-        // waits (bounded) until every rank has said the same here, so that the kernel's completion
+        // Every CTA orders its peer stores before its arrival (device scope); the last CTA of the
+        // grid tells every rank that this rank's slice of this call is complete and waits
+        // (bounded) until every rank has said the same here, so that the kernel's completion
         // means "the gathered output is complete on this rank".
         if (stage_out) {
             __syncthreads();   // every warp is done reading the staged activations
@@ -718,17 +718,18 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
             }
         }
         if (gather_failed) atomicOr(&g_device_status, 4u);
-        // One system-scope fence by the thread that reports for the CTA covers every thread's
-        // peer stores: they are ordered before it by the barrier.
+        // The thread that reports for the CTA orders every thread's peer stores (the barrier puts
+        // them before it) ahead of its arrival.
         __syncthreads();
         if (tid == 0) {
-            __threadfence_system();
+            __threadfence();   // device scope: the last CTA's system-scope fence below is cumulative
             unsigned int* mine = p.gather.flag_peer[p.gather.rank];
             const unsigned int total = gridDim.x * gridDim.y;
             if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
                 mine[kGatherCounterWord] = 0u;   // ready for the next call
-                // one fence orders every CTA's peer stores before the arrival words, which then go
-                // out together; the polls are plain loads, with one fence after the last of them
+                // one system-scope fence orders every CTA's peer stores (observed through the
+                // device-scope arrivals above: fences are cumulative) before the arrival words, which
+                // then go out together; the polls are acquire loads
                 __threadfence_system();
                 for (int g = 0; g < p.gather.world; ++g)
                     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
@@ -738,13 +739,12 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
                     bool in = false;
                     for (unsigned int spin = 0; spin < p.spin_limit && !in; ++spin) {
                         unsigned int v;
-                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + src) : "memory");
                         in = static_cast<int>(v - call_no) >= 0;
                         if (!in) __nanosleep(100);
                     }
                     all_in = in;
                 }
-                __threadfence_system();
                 if (!all_in) atomicOr(&g_device_status, 4u);   // a rank never reported: give up, do not hang
                 asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine + kGatherEpochWord), "r"(call_no) : "memory");
             }
