@@ -455,10 +455,22 @@ def measure_single_gpu(h, name, steps, want_e2e=True):
         xs_host = [L.x.pin_memory() for L in layers_cpu]
         outs_host = [torch.empty((L.M, L.N), dtype=L.x.dtype).pin_memory() for L in layers_cpu]
 
+        def host_step(c):
+            def body():
+                for j, L in enumerate(dev_layers[c]):
+                    # host activations in, host result out: the operator enqueues the copies itself
+                    _C.dequant_matmul(xs_host[j], L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs_host[j])
+            return body
+
+        # the public phase pipeline decides how a step is issued: a decode step is recorded once
+        # and replayed with one launch (one recording per weight copy), a prefill step runs eagerly
+        import metal_native
+        pipe = metal_native.PhasePipeline()
+        phase = pipe.auto_detect_phase(batch_size=layers_cpu[0].M, seq_len=1 if layers_cpu[0].M <= 32 else layers_cpu[0].M)
+        issue = [pipe.capture_step(host_step(c)) for c in range(copies)]
+
         def e2e_step(i):
-            for j, L in enumerate(dev_layers[i % copies]):
-                # host activations in, host result out: the operator enqueues both copies itself
-                _C.dequant_matmul(xs_host[j], L.wq, L.scales, L.zeros, L.group_size, L.quant_type, out=outs_host[j])
+            issue[i % copies]()
             torch.cuda.current_stream().synchronize()
 
         e2e_steps = min(max(steps, 50), 400)
@@ -477,8 +489,11 @@ def measure_single_gpu(h, name, steps, want_e2e=True):
                       "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in xs_host),
                       "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs_host),
                       "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-                      "call": "metal_native._C.dequant_matmul(host activations, out=host tensor) per projection, eager: "
-                              "the operator enqueues the host->device and device->host copies; weights resident"}
+                      "call": "metal_native._C.dequant_matmul(host activations, out=host tensor) per projection (the operator "
+                              "copies the activations in and writes the result to the pinned host tensor), issued through "
+                              f"metal_native.PhasePipeline.capture_step ({phase.name}: "
+                              + ("recorded once, replayed with one launch per step" if pipe.active_config().capture_graph
+                                 else "eager") + "), stream synchronised every step; weights resident"}
     return res
 
 
@@ -705,10 +720,22 @@ def run_sharded(h, args):
     outs_host = [torch.empty((L.M, L.N * world), dtype=L.x.dtype).pin_memory() for L in layers_cpu]
     xs_dev = [torch.empty_like(L.x, device=dev) for L in layers_cpu]
 
+    def host_step(c):
+        def body():
+            for j, L in enumerate(dev_layers[c]):
+                xs_dev[j].copy_(xs_host[j], non_blocking=True)
+                outs_host[j].copy_(run_layer(j, L, xs_dev[j]), non_blocking=True)
+        return body
+
+    # a decode step is recorded once per weight copy and replayed with one launch (every rank
+    # records and replays the same sequence)
+    import metal_native
+    pipe = metal_native.PhasePipeline()
+    phase = pipe.auto_detect_phase(batch_size=layers_cpu[0].M, seq_len=1 if layers_cpu[0].M <= 32 else layers_cpu[0].M)
+    issue = [pipe.capture_step(host_step(c)) for c in range(copies)]
+
     def e2e_step(i):
-        for j, L in enumerate(dev_layers[i % copies]):
-            xs_dev[j].copy_(xs_host[j], non_blocking=True)
-            outs_host[j].copy_(run_layer(j, L, xs_dev[j]), non_blocking=True)
+        issue[i % copies]()
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(max(args.steps, 50), 400)
@@ -729,7 +756,8 @@ def run_sharded(h, args):
            "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
            "call": ("metal_native.sharded.PeerGather.matmul" if fused else
                     "metal_native._C.dequant_matmul + sharded.GatherBuffer.all_gather")
-           + " per projection between pinned-memory copies, eager, on every rank; weights resident"}
+           + " per projection between copies from and to pinned host memory, on every rank, issued through "
+             f"metal_native.PhasePipeline.capture_step ({phase.name}), stream synchronised every step; weights resident"}
 
     # ---- keep the load on for the clock sampler: every rank replays the same number of times
     for _ in range(max(1, min(2000, int(1000.0 / max(ms * args.steps, 1e-3))))):

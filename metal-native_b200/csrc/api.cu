@@ -71,6 +71,21 @@ int64_t option_value(int option)
     return g_options[option].load(std::memory_order_relaxed);
 }
 
+// A kernel's shared-memory attribute has to be set once per device, not once per launch: one bit
+// per device ordinal says whether it has been.  (Two threads racing through the first launch both
+// set the attribute, which is harmless; the bit is set only after the attribute is.)
+bool attribute_done_on_device(const std::atomic<uint64_t>& flags)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    return (flags.load(std::memory_order_acquire) >> dev) & 1u;
+}
+void mark_attribute_done_on_device(std::atomic<uint64_t>& flags)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) flags.fetch_or(uint64_t(1) << dev, std::memory_order_acq_rel);
+}
+
 int check_cuda(cudaError_t e, const char* what)
 {
     if (e == cudaSuccess) return MNQ_SUCCESS;
@@ -98,6 +113,24 @@ int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType
     }
     if (reinterpret_cast<uintptr_t>(base) % 16 || pitch_bytes % 16 || (static_cast<uint64_t>(box0) * elem_bytes) % 16)
         return fail(MNQ_INVALID_ARGUMENT, "tensor map: base, pitch and box width must be multiples of 16 bytes");
+    // A descriptor is a pure function of these arguments, and a decode step asks for the same few over
+    // and over: a small direct-mapped table saves the driver call (about a microsecond) on a hit.
+    struct Entry {
+        const void* base; uint64_t dim0, dim1, pitch; uint32_t box0, box1; int dtype, elem_bytes, swizzle; bool valid;
+        CUtensorMap map;
+    };
+    static Entry table[64];
+    static std::mutex table_lock;
+    const uint64_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + dim1 * 31 + box1 * 7 + box0 + swizzle;
+    Entry& e = table[(h >> 32) & 63];
+    {
+        std::lock_guard<std::mutex> g(table_lock);
+        if (e.valid && e.base == base && e.dim0 == dim0 && e.dim1 == dim1 && e.pitch == pitch_bytes && e.box0 == box0 &&
+            e.box1 == box1 && e.dtype == static_cast<int>(dtype) && e.elem_bytes == elem_bytes && e.swizzle == static_cast<int>(swizzle)) {
+            *out = e.map;
+            return MNQ_SUCCESS;
+        }
+    }
     const cuuint64_t dims[2] = {dim0, dim1};
     const cuuint64_t strides[1] = {pitch_bytes};
     const cuuint32_t box[2] = {box0, box1};
@@ -106,6 +139,12 @@ int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType
                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MNQ_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    {
+        std::lock_guard<std::mutex> g(table_lock);
+        e.base = base; e.dim0 = dim0; e.dim1 = dim1; e.pitch = pitch_bytes; e.box0 = box0; e.box1 = box1;
+        e.dtype = static_cast<int>(dtype); e.elem_bytes = elem_bytes; e.swizzle = static_cast<int>(swizzle);
+        e.map = *out; e.valid = true;
+    }
     return MNQ_SUCCESS;
 }
 
@@ -428,6 +467,38 @@ int mnq_dequant_matmul_swiglu(const void* activations, const void* weights_packe
 
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+// Device address of a host buffer if it is pinned and mapped into this device's address space
+// (cudaHostAlloc / cudaHostRegister memory, torch's pinned tensors), else null.  The answer for a pointer
+// is remembered per thread: the query costs about a microsecond.
+static void* device_pointer_of_pinned(const void* host)
+{
+    struct Seen { const void* host; void* dev; int device; };
+    static thread_local Seen seen[8];
+    static thread_local int next = 0;
+    int device = 0;
+    if (!host || cudaGetDevice(&device) != cudaSuccess) return nullptr;
+    for (const Seen& s : seen)
+        if (s.host == host && s.device == device) return s.dev;
+    cudaPointerAttributes attr{};
+    void* dev = nullptr;
+    if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+        dev = attr.devicePointer;
+    else
+        cudaGetLastError();   // an unregistered pointer is not an error here
+    seen[next] = Seen{host, dev, device};
+    next = (next + 1) & 7;
+    return dev;
+}
+
+// Copies a small activation block out of pinned, device-mapped host memory.  A kernel instead of a
+// copy operation: the operator's kernel, launched programmatically dependent behind it, starts its
+// set-up (and, with immutable weights, its weight stream) while this one is still fetching over the bus.
+__global__ void __launch_bounds__(256) stage_activations_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = src[i];
+}
+
 // Operator scratch at the front of a host-call workspace.  Never shorter than the counter region:
 // a workspace is shared by successive calls of any kind, and the device copies of activations and
 // output that follow the scratch must not land where a later split-K call expects zeroed counters.
@@ -464,14 +535,28 @@ int mnq_dequant_matmul_host(const void* activations_host, const void* weights_pa
     unsigned char* x_dev = ws + scratch;
     unsigned char* out_dev = x_dev + align256(static_cast<size_t>(M) * K * 2);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // (The activations are staged in device memory even when they sit in pinned, device-mapped memory:
+    // every CTA reads its K range of them, and three hundred reads over the bus cost far more than one.)
     if (K > 0) {
-        rc = check_cuda(cudaMemcpyAsync(x_dev, activations_host, static_cast<size_t>(M) * K * 2, cudaMemcpyHostToDevice, st),
-                        "cudaMemcpyAsync(activations to device)");
+        const size_t x_bytes = static_cast<size_t>(M) * K * 2;
+        const void* x_mapped = (M <= 32 && x_bytes % 16 == 0) ? device_pointer_of_pinned(activations_host) : nullptr;
+        if (x_mapped && reinterpret_cast<uintptr_t>(x_mapped) % 16 == 0) {
+            const size_t n16 = x_bytes / 16;
+            const unsigned blocks = static_cast<unsigned>(n16 / 256 + 1 > 16 ? 16 : n16 / 256 + 1);
+            stage_activations_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x_mapped), reinterpret_cast<uint4*>(x_dev), n16);
+            rc = check_cuda(cudaGetLastError(), "activation staging launch");
+        } else {
+            rc = check_cuda(cudaMemcpyAsync(x_dev, activations_host, x_bytes, cudaMemcpyHostToDevice, st),
+                            "cudaMemcpyAsync(activations to device)");
+        }
         if (rc) return rc;
     }
-    rc = mnq_dequant_matmul(x_dev, weights_packed, scales, zeros, out_dev, M, N, K, K, N, group_size, quant_type, act_dtype,
-                            scale_dtype, op_scratch ? ws : nullptr, op_scratch ? scratch : 0, stream);
-    if (rc) return rc;
+    // A decode-sized result goes straight from the kernel's epilogue into pinned, device-mapped host
+    // memory (every output is written once, as posted writes): the copy back and its launch are saved.
+    void* out_mapped = (M <= 32) ? device_pointer_of_pinned(out_host) : nullptr;
+    rc = mnq_dequant_matmul(x_dev, weights_packed, scales, zeros, out_mapped ? out_mapped : out_dev, M, N, K, K, N, group_size,
+                            quant_type, act_dtype, scale_dtype, op_scratch ? ws : nullptr, op_scratch ? scratch : 0, stream);
+    if (rc || out_mapped) return rc;
     return check_cuda(cudaMemcpyAsync(out_host, out_dev, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, st),
                       "cudaMemcpyAsync(output to host)");
 }

@@ -1031,10 +1031,13 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     if constexpr (!std::is_same<TT, BSplit>::value) {
         if (occ2 && !pair) kern = &gemm_tcgen05_kernel<QUANT, T, TT, false, true>;
     }
-    if (smem > 48 * 1024) {
+    static std::atomic<uint64_t> attr_set[3];   // per kernel of this instantiation: CTA pairs, single CTAs, two CTAs per SM
+    std::atomic<uint64_t>& attr_flags = attr_set[pair ? 0 : (occ2 ? 2 : 1)];
+    if (smem > 48 * 1024 && !attribute_done_on_device(attr_flags)) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
         if (rc) return rc;
+        mark_attribute_done_on_device(attr_flags);
     }
     {
         // programmatic dependent launch (see the kernel); CTA pairs are clusters of two along x

@@ -534,10 +534,12 @@ template <int QUANT, typename T, bool GROUPED, bool GATHER>
 int launch_lean_one(const LeanParams& p, const CUtensorMap& wmap, dim3 grid, int threads, size_t smem, cudaStream_t stream)
 {
     auto* kern = &gemv_lean_kernel<QUANT, T, GROUPED, GATHER>;
-    if (smem > 48 * 1024) {
+    static std::atomic<uint64_t> attr_set{0};   // (one flag word per template instantiation)
+    if (smem > 48 * 1024 && !attribute_done_on_device(attr_set)) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanMaxSmem),
                                   "cudaFuncSetAttribute(gemv_lean)");
         if (rc) return rc;
+        mark_attribute_done_on_device(attr_set);
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;

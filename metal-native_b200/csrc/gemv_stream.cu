@@ -917,11 +917,13 @@ int launch_stream_one(const StreamParams& p, const CUtensorMap& wmap, const CUte
                       size_t smem, cudaStream_t stream)
 {
     auto* kern = &gemv_stream_kernel<QUANT, T, NT, CH>;
-    if (smem > 48 * 1024) {
+    static std::atomic<uint64_t> attr_set{0};   // (one flag word per template instantiation)
+    if (smem > 48 * 1024 && !attribute_done_on_device(attr_set)) {
         const int rc = check_cuda(
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem),
             "cudaFuncSetAttribute(gemv_stream)");
         if (rc) return rc;
+        mark_attribute_done_on_device(attr_set);
     }
     // Programmatic dependent launch: the CTAs of this kernel may be scheduled while the previous
     // kernel in the stream is still draining (that hides the launch gap and the cold start);

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/mnq.h"
 
 namespace mnq {
@@ -16,6 +18,8 @@ namespace mnq {
 // ---------------------------------------------------------------------------
 int fail(int status, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
+bool attribute_done_on_device(const std::atomic<uint64_t>& flags);
+void mark_attribute_done_on_device(std::atomic<uint64_t>& flags);
 
 // ---------------------------------------------------------------------------
 // 16-bit float traits

@@ -256,6 +256,43 @@ def _prepare(activations, weights_packed, scales, zeros, group_size, quant_type,
     return activations, w, scales, zeros, M, N, K, lda, group_size, q
 
 
+# Repeated calls with the very same tensor objects (a decode loop: same weights, same activation
+# and output buffers, step after step) skip validation and argument marshalling: the checked,
+# converted argument list of the previous call is replayed after confirming that every tensor is
+# still the same object at the same address.  Keyed by object identity; bounded.
+import weakref
+
+_MAX_REPLAY = 256
+_replay: dict[tuple, "_Replay"] = {}
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+class _Replay:
+    __slots__ = ("refs", "ptrs", "numels", "fn", "args", "device", "stream", "keep", "result")
+
+    def __init__(self, tensors, fn, args, device, stream, keep, result):
+        self.refs = [None if t is None else weakref.ref(t) for t in tensors]
+        self.ptrs = [None if t is None else t.data_ptr() for t in tensors]
+        self.numels = [None if t is None else t.numel() for t in tensors]
+        self.fn, self.args, self.device, self.stream, self.keep, self.result = fn, args, device, stream, keep, result
+
+    def valid(self, tensors) -> bool:
+        for t, r, p, n in zip(tensors, self.refs, self.ptrs, self.numels):
+            if t is None:
+                if r is not None:
+                    return False
+            elif r is None or r() is not t or t.data_ptr() != p or t.numel() != n:
+                return False
+        return _raw_device() == self.device and _raw_stream(self.device) == self.stream
+
+
+def _remember(key, entry) -> None:
+    if len(_replay) >= _MAX_REPLAY:
+        _replay.pop(next(iter(_replay)))
+    _replay[key] = entry
+
+
 def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant_type,
                    *, out=None, tuning: Tuning | None = None):
     """Fused dequantization + matrix multiplication.
@@ -268,8 +305,19 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
     enqueued on the current CUDA stream; like the reference op it returns before the
     GPU has finished (``synchronize()`` or any torch sync waits for it).
     """
+    key = None
+    if out is not None and tuning is None and _raw_stream is not None:
+        key = (id(activations), id(weights_packed), id(scales), id(zeros), id(out), group_size, quant_type)
+        ent = _replay.get(key)
+        if ent is not None:
+            if ent.valid((activations, weights_packed, scales, zeros, out)):
+                rc = ent.fn(*ent.args)
+                if rc != 0:
+                    _check(rc)
+                return ent.result
+            del _replay[key]
     if isinstance(activations, torch.Tensor) and not activations.is_cuda:
-        return _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out)
+        return _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out, key)
     x, w, s, z, M, N, K, lda, g, q = _prepare(activations, weights_packed, scales, zeros, group_size, quant_type)
     dev = x.device
     if out is None:
@@ -290,12 +338,20 @@ def dequant_matmul(activations, weights_packed, scales, zeros, group_size, quant
             ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
     if tuning is None:
         _check(_lib.mnq_dequant_matmul(*args))
+        if key is not None and x is activations:
+            _remember(key, _Replay((activations, weights_packed, scales, zeros, out), _lib.mnq_dequant_matmul,
+                                   _marshal(_lib.mnq_dequant_matmul, args), dev.index, stream, ws, out))
     else:
         _check(_lib.mnq_dequant_matmul_ex(*args, ctypes.byref(tuning)))
     return out
 
 
-def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out):
+def _marshal(fn, args):
+    """The arguments as ctypes objects of the function's declared types (converted once)."""
+    return [None if (a is None and t is ctypes.c_void_p) else t(a) for t, a in zip(fn.argtypes, args)]
+
+
+def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size, quant_type, out, key=None):
     """Host-memory activations and output (``mnq_dequant_matmul_host``): the reference's callers
     fill tensors on the CPU and read results on the CPU after ``synchronize()`` because its
     memory is shared between CPU and GPU; here the two copies are enqueued with the kernel.
@@ -317,10 +373,13 @@ def _dequant_matmul_host(activations, weights_packed, scales, zeros, group_size,
     stream = torch.cuda.current_stream(dev).cuda_stream
     nbytes = _lib.mnq_host_workspace_bytes(M, N, K, g, q)
     ws = _workspace(dev, stream, nbytes)
-    _check(_lib.mnq_dequant_matmul_host(
-        x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
-        M, N, K, g, q, _DT[x.dtype], _DT[s.dtype], ws.data_ptr() if ws is not None else None,
-        ws.numel() if ws is not None else 0, stream))
+    args = (x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr() if z is not None else None, out.data_ptr(),
+            M, N, K, g, q, _DT[x.dtype], _DT[s.dtype], ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, stream)
+    _check(_lib.mnq_dequant_matmul_host(*args))
+    if key is not None and x is activations:
+        _remember(key, _Replay((activations, weights_packed, scales, zeros, out), _lib.mnq_dequant_matmul_host,
+                               _marshal(_lib.mnq_dequant_matmul_host, args), dev.index, stream, ws, out))
     return out
 
 

@@ -216,3 +216,46 @@ def test_phase_pipeline_applies_threshold_and_replays_a_captured_decode_step(mn)
         assert pipe.strategy_for(24) == "gemm" and C.select_path(24, 512, 2048, 128, "int4") == "gemm"
     finally:
         C.set_option("gemv_max_m", 32)
+
+
+def test_repeated_calls_replay_the_checked_arguments(mn):
+    """A decode loop calls the operator with the same tensor objects step after step; from the second
+    call on the shim replays the checked argument list.  The replay must see new contents of the same
+    buffers, must not outlive its tensors, and must not be used on another stream."""
+    import mnq_workloads as workloads
+    C = mn._C
+    L = workloads.make_layer("t", 1, 2048, 512, seed=11)
+    d = L.to("cuda")
+    out = torch.zeros((1, 512), dtype=torch.float16, device="cuda")
+    ref = H.oracle_matmul(L)
+    for _ in range(3):
+        out.zero_()
+        assert C.dequant_matmul(*d.args(), out=out) is out
+        H.assert_close_to_oracle(out, ref, "replay")
+    d.x.mul_(2.0)                                             # same buffer, new contents
+    C.dequant_matmul(*d.args(), out=out)
+    H.assert_close_to_oracle(out, 2.0 * ref, "replay after an in-place update")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                             # another stream: another workspace, no replay
+        C.dequant_matmul(*d.args(), out=out)
+    side.synchronize()
+    H.assert_close_to_oracle(out, 2.0 * ref, "other stream")
+    # host activations and output
+    xh = L.x.pin_memory()
+    oh = torch.zeros((1, 512), dtype=torch.float16).pin_memory()
+    for scale in (1.0, 3.0, 1.0):
+        xh.copy_(L.x * scale)
+        C.dequant_matmul(xh, d.wq, d.scales, d.zeros, d.group_size, d.quant_type, out=oh)
+        C.synchronize()
+        H.assert_close_to_oracle(oh, scale * ref, f"host replay x{scale}")
+    # pageable host memory takes the copying path
+    xp = (L.x * 1.0).clone()
+    op = torch.zeros((1, 512), dtype=torch.float16)
+    C.dequant_matmul(xp, d.wq, d.scales, d.zeros, d.group_size, d.quant_type, out=op)
+    C.synchronize()
+    H.assert_close_to_oracle(op, ref, "pageable host tensors")
+    del out
+    out2 = torch.zeros((1, 512), dtype=torch.float16, device="cuda")   # may reuse the freed tensor's id and address
+    C.dequant_matmul(*d.args(), out=out2)
+    H.assert_close_to_oracle(out2, 2.0 * ref, "fresh output tensor")
