@@ -61,7 +61,7 @@ SCALING_WORKLOAD = "llama70b-int8-m1"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of a workload's dominant kernel, each
 # from one ncu capture of this program on that workload (--workload NAME --steps 2 --warmup 3)
 TRAFFIC = {
-    "qwen7b-decode": 72_224_256 + 705_792,
+    "qwen7b-decode": 72_212_736 + 1_035_008,
     "qwen7b-prefill": 39_830_016 + 378_368,
 }
 
