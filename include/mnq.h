@@ -87,9 +87,10 @@ typedef enum mnq_option {
      * sets bit 2 of the device status word.  Default 1 << 22 (about 0.4 s). */
     MNQ_OPT_PEER_WAIT_POLLS = 1,
     /* Largest token count M that takes the decode (GEMV) kernels; above it the tensor-core
-     * kernel runs.  1..32, default 32, initialised from the environment variable
-     * METAL_NATIVE_GEMV_MAX_M when set.  The reference's counterpart is the fixed
-     * `use_vecmat = (M <= 8)` (src/ops/matmul.mm:946). */
+     * kernel runs.  0..32, initialised from the environment variable METAL_NATIVE_GEMV_MAX_M
+     * when set.  Default 0: chosen per problem from B200 measurements (8 for int8 weights with
+     * one scale per row, 24 for other fp16 activations, 32 for other bf16 activations).  The
+     * reference's counterpart is the fixed `use_vecmat = (M <= 8)` (src/ops/matmul.mm:946). */
     MNQ_OPT_GEMV_MAX_M = 2
 } mnq_option;
 
@@ -101,7 +102,8 @@ typedef struct mnq_tuning {
     int32_t warps_per_cta;       /* GEMV: 16 output rows per warp at a time */
     int32_t gemv_variant;        /* kernel variant, 0 auto.  GEMV path: 1 register-prefetch kernel, 2 shared-memory
                                     streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2),
-                                    3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it */
+                                    3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it, 5 no raw-integer
+                                    tiles.  Streaming GEMV: 3 the general kernel even where the compact one would run */
     int32_t piece_bytes;         /* streaming GEMV: packed bytes per row per stage (multiple of 64) */
     int32_t stages;              /* streaming GEMV: stages per warp (2..8) */
     int32_t ctas_per_sm;         /* streaming GEMV: resident CTAs per SM the plan assumes */

@@ -40,7 +40,7 @@ int fail(int status, const char* fmt, ...)
 // ---------------------------------------------------------------------------
 namespace {
 constexpr int kNumOptions = 3;
-std::atomic<int64_t> g_options[kNumOptions] = {{0}, {int64_t(1) << 22}, {32}};
+std::atomic<int64_t> g_options[kNumOptions] = {{0}, {int64_t(1) << 22}, {0}};
 std::once_flag g_options_env;
 
 bool option_in_range(int option, int64_t v)
@@ -48,7 +48,7 @@ bool option_in_range(int option, int64_t v)
     switch (option) {
         case MNQ_OPT_WEIGHTS_IMMUTABLE: return v == 0 || v == 1;
         case MNQ_OPT_PEER_WAIT_POLLS: return v >= 1 && v <= (int64_t(1) << 31) - 1;
-        case MNQ_OPT_GEMV_MAX_M: return v >= 1 && v <= 32;
+        case MNQ_OPT_GEMV_MAX_M: return v >= 0 && v <= 32;   // 0: chosen per problem
         default: return false;
     }
 }
@@ -218,11 +218,26 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
     a.epi = Epilogue{};
 }
 
-// Decode kernels up to the threshold (MNQ_OPT_GEMV_MAX_M, at most the 32 tokens they are built
-// for), the tensor-core kernel above it, the any-shape kernel for whatever neither takes.
+// Largest token count the decode kernels take.  MNQ_OPT_GEMV_MAX_M when set (1..32); otherwise by
+// what was measured on B200: the decode kernels' cost grows with every 8 tokens while the
+// tensor-core kernel's is flat up to 128, and where they cross depends on the tile mode.  int8
+// weights with one scale per row run raw-integer tiles, which win from 9 tokens; fp16 activations
+// use one fp16 tile per k-block and win from about 25; bf16 activations with group-wise scales
+// need two tiles per k-block and lose up to the decode kernels' limit of 32.
+int64_t gemv_max_m_for(int64_t K, int32_t group_size, int32_t quant, int32_t act_dtype)
+{
+    const int64_t set = option_value(MNQ_OPT_GEMV_MAX_M);
+    if (set > 0) return set;
+    if (quant == MNQ_INT8 && group_size >= K) return 8;
+    if (act_dtype == MNQ_FP16) return 24;
+    return 32;
+}
+
+// Decode kernels up to the threshold, the tensor-core kernel above it, the any-shape kernel for
+// whatever neither takes.
 int choose_path(const MatmulArgs& a)
 {
-    const int64_t gemv_max_m = option_value(MNQ_OPT_GEMV_MAX_M);
+    const int64_t gemv_max_m = gemv_max_m_for(a.K, a.group_size, a.quant, a.act_dtype);
     if (a.M <= gemv_max_m && gemv_supported(a)) return MNQ_PATH_GEMV;
     if (a.M > gemv_max_m && gemm_supported(a)) return MNQ_PATH_GEMM;
     if (a.M <= 32 && gemv_supported(a)) return MNQ_PATH_GEMV;   // e.g. K not a multiple of 64
@@ -277,10 +292,10 @@ int mnq_device_status(uint32_t* status, int32_t clear)
 
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
-    if (M > 32) return gemm_workspace_bytes(M, N, K, group_size);
-    // M <= 32 takes either family, depending on MNQ_OPT_GEMV_MAX_M: enough for both
+    if (M > 32) return gemm_workspace_bytes(M, N, K, group_size, quant_type);
+    // 9..32 tokens take either family, depending on MNQ_OPT_GEMV_MAX_M and the dtypes: enough for both
     const size_t a = gemv_workspace_bytes(M, N, K, group_size, quant_type);
-    const size_t b = M > option_value(MNQ_OPT_GEMV_MAX_M) ? gemm_workspace_bytes(M, N, K, group_size) : 0;
+    const size_t b = M > 8 ? gemm_workspace_bytes(M, N, K, group_size, quant_type) : 0;
     return a > b ? a : b;
 }
 

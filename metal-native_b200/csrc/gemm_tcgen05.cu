@@ -87,6 +87,10 @@ struct GemmParams {
     float* partial;     // [splits][M][N] fp32 (splits > 1)
     int vec_store;      // bit 0: out allows 16-byte stores, bit 1: the split-K planes do
     Epilogue epi;       // applied to the fp32 result before the store; fp32 output mode
+    // raw-integer tiles (RawInt): per-token factor and activation sum, written by prep_activations_kernel
+    const float* tok_scale;   // [M]: out column m is multiplied by it (undoes the activations' power-of-two rescale)
+    const float* tok_sum;     // [M]: sum over k of the original activations of token m
+    int offset_term;          // 1: this launch subtracts (128 s + z) * tok_sum (always; with K split, split 0 does)
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -309,6 +313,22 @@ template <> struct TileChunk<MNQ_INT8, __nv_bfloat16> {
     }
 };
 
+// Raw-integer tiles: int8 weights with one scale per row enter the tensor core as the exact fp16
+// values (q + 128) * 2^-24 (byte ^ 0x80 in the low mantissa bits of an fp16 subnormal): one XOR per
+// word and one byte permute per pair of weights instead of a convert, a multiply and an add.  The
+// activations are fp16 (bf16 ones are converted once per call, prep_activations_kernel), and the
+// epilogue turns the accumulator P of row n and token m into
+//     s_n * 2^24 * c_m * P  -  (128 s_n + z_n) * X_m
+// with c_m the token's power-of-two rescale and X_m the sum of its activations.
+struct RawInt {};
+template <> struct TileChunk<MNQ_INT8, RawInt> {
+    static constexpr int WORDS = 2;
+    static __device__ __forceinline__ uint4 run(const uint32_t* w, __half2, __half2)
+    {
+        const uint32_t u0 = w[0] ^ 0x80808080u, u1 = w[1] ^ 0x80808080u;
+        return make_uint4(prmt(u0, 0u, 0x4140u), prmt(u0, 0u, 0x4342u), prmt(u1, 0u, 0x4140u), prmt(u1, 0u, 0x4342u));
+    }
+};
 // bf16 activations with group-wise scales (or zeros): a dequantised weight does not fit bf16's
 // 8 significant bits (rounding it would cost 1.6e-3 relative error by itself), and the MMA wants
 // both operands in one format.  So the weight w = fma(q, s, -z), computed in fp32, is split into
@@ -392,10 +412,13 @@ template <> struct StageIO<__nv_bfloat16> {
 // T: the activation type (what bias and residual hold).  FINAL: the values stored are the
 // operator's result, so the epilogue is applied while they are staged; otherwise (a K split's
 // fp32 plane) they are stored as they are.
+// tok_scale / tok_sum / zterm: raw-integer tiles only (tok_scale == nullptr otherwise): the value of token m is
+// acc * scale * tok_scale[m] - zterm * tok_sum[m].
 template <typename E, typename T, bool FINAL>
 __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int half, int row, int e, int tok,
                                               uint32_t stage0, float scale, E* dst, size_t ld, int n0, int N, int m0,
-                                              int M, bool vec, const Epilogue& epi)
+                                              int M, bool vec, const Epilogue& epi, const float* tok_scale = nullptr,
+                                              const float* tok_sum = nullptr, float zterm = 0.f)
 {
     constexpr int RB = BN * (int)sizeof(E);    // bytes per staged token row
     constexpr int PPR = RB / 16;               // 16-byte pieces per row
@@ -410,7 +433,16 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
             tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const uint32_t at = stage + (uint32_t)(half * 32 * RB) + (uint32_t)row * (uint32_t)sizeof(E);
-            if (FINAL && epi.kind != MNQ_EPI_NONE) {
+            if (tok_scale) {
+                const bool n_ok = n0 + row < N;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int m = min(m0 + c0 + i, M - 1);
+                    float val = fmaf(-zterm, __ldg(tok_sum + m), __uint_as_float(v[i]) * scale * __ldg(tok_scale + m));
+                    if (FINAL && n_ok && m0 + c0 + i < M) val = epilogue_value<T>(epi, val, m0 + c0 + i, n0 + row);
+                    StageIO<E>::put(at + i * RB, StageIO<E>::from(val));
+                }
+            } else if (FINAL && epi.kind != MNQ_EPI_NONE) {
                 const bool n_ok = n0 + row < N;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -478,6 +510,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr int RAW_BYTES = BN * 128;
     constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
     constexpr bool SPLIT = std::is_same<TT, BSplit>::value;
+    constexpr bool RAW = std::is_same<TT, RawInt>::value;      // fp16 tiles of raw integers, fp16 activations whatever T is
+    constexpr bool MMA_BF16 = IS_BF16 && !RAW;
     constexpr int A_STAGE = SPLIT ? 2 * A_BYTES : A_BYTES;   // bytes of one weight-ring slot
 
     extern __shared__ unsigned char smem_raw[];
@@ -600,7 +634,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = instr_desc(p.tokh, IS_BF16, PAIR ? 2 * BN : BN);
+            const uint32_t idesc = instr_desc(p.tokh, MMA_BF16, PAIR ? 2 * BN : BN);
             int s = 0, sb = 0, d = 0; uint32_t dph = 0;
             int hp = 0;                             // pair barrier of this k-block
             for (int kb = 0; kb < num_kb; ++kb) {   // kb: position in this CTA's k order
@@ -650,7 +684,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         const int kbg_shift = (kbg & (kbg - 1)) == 0 ? 31 - __clz(kbg) : -1;
         const bool one_group = p.group_size >= p.K;
         const int g_first = one_group ? 0 : (kb_begin * BK) / p.group_size;
-        {   // scale | zero << 16 of every (row, group) this CTA touches, [group][row]
+        if (!RAW) {   // scale | zero << 16 of every (row, group) this CTA touches, [group][row]
             const unsigned short* sc16 = static_cast<const unsigned short*>(p.scales);
             const unsigned short* zr16 = static_cast<const unsigned short*>(p.zeros);
             const int g_last = one_group ? 0 : ((kb_begin + num_kb) * BK - 1) / p.group_size;
@@ -714,7 +748,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 }
                 const int gi = one_group ? 0
                                : (kbg_shift >= 0 ? (kb_begin + kb) >> kbg_shift : (kb_begin + kb) / kbg) - g_first;
-                const uint32_t sz = lds32(tbl0 + (uint32_t)(gi * BN + row) * 4u);
+                const uint32_t sz = RAW ? 0u : lds32(tbl0 + (uint32_t)(gi * BN + row) * 4u);
                 __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
                 // -z with the sign flipped in place (exact)
                 __half2 nz2 = __half2half2(__ushort_as_half((unsigned short)((sz >> 16) ^ 0x8000u)));
@@ -744,7 +778,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 } else {
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
-                        const uint4 o = TileChunk<QUANT, T>::run(&w[c * TileChunk<QUANT, T>::WORDS], s2, nz2);
+                        using Chunk = TileChunk<QUANT, typename std::conditional<RAW, RawInt, T>::type>;
+                        const uint4 o = Chunk::run(&w[c * Chunk::WORDS], s2, nz2);
                         sts128(a_row + xoff[c], o);
                     }
                 }
@@ -780,21 +815,29 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         }
         if (!failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float scale = 1.f;
+            float scale = 1.f, zterm = 0.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
+            const float* tscale = nullptr;
+            if (RAW) {
+                const float s_n = scale;
+                scale = s_n * 16777216.f;
+                if (p.offset_term && (p.splits == 1 || blockIdx.z == 0))
+                    zterm = fmaf(128.f, s_n, p.zeros ? widen16(p.zeros, sc_row, p.scale_dtype) : 0.f);
+                tscale = p.tok_scale;
+            }
             // with K split, this CTA's result goes to its [M][N] plane of the workspace instead;
             // the rings are idle now (every MMA has completed), so their memory stages the tile
             if (p.splits > 1)
                 epilogue_tile<float, T, false>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
                                                p.partial + (size_t)blockIdx.z * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
-                                               (p.vec_store & 2) != 0, p.epi);
+                                               (p.vec_store & 2) != 0, p.epi, tscale, p.tok_sum, zterm);
             else if (p.epi.out_f32)
                 epilogue_tile<float, T, true>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
                                               static_cast<float*>(p.out), (size_t)p.ldc, n0, p.N, m0, p.M,
-                                              (p.vec_store & 4) != 0, p.epi);
+                                              (p.vec_store & 4) != 0, p.epi, tscale, p.tok_sum, zterm);
             else
                 epilogue_tile<T, T, true>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale, static_cast<T*>(p.out),
-                                          (size_t)p.ldc, n0, p.N, m0, p.M, (p.vec_store & 1) != 0, p.epi);
+                                          (size_t)p.ldc, n0, p.N, m0, p.M, (p.vec_store & 1) != 0, p.epi, tscale, p.tok_sum, zterm);
         }
     }
     if (failed && lane == 0) atomicOr(&g_gemm_status, 2u);
@@ -868,11 +911,86 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
+// Prepares the activations for raw-integer tiles, one CTA per token row: the row's sum X_m (fp32,
+// threads stride over the row, then a fixed tree: the same bits every time), and for bf16 rows an
+// fp16 copy multiplied by the power of two c_m^-1 that puts the row's largest magnitude just below
+// 2^15 (exact: a bf16 significand fits fp16's; only values 2^29 below the row's maximum are flushed).
+// fp16 rows are used as they are (c_m = 1).
+template <typename T>
+__global__ void __launch_bounds__(256) prep_activations_kernel(const T* __restrict__ x, long long lda, int K,
+                                                               __half* __restrict__ x16, float* __restrict__ tok_scale,
+                                                               float* __restrict__ tok_sum)
+{
+    constexpr bool CONVERT = std::is_same<T, __nv_bfloat16>::value;
+    __shared__ float warp_sum[8];
+    __shared__ unsigned int warp_max[8];
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may be the previous kernel's output
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int m = blockIdx.x;
+    const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)m * lda);
+    const int n8 = K / 8;   // K is a multiple of 64
+    float down = 1.f, up = 1.f;
+    if (CONVERT) {
+        unsigned int mx = 0;
+        for (int i = threadIdx.x; i < n8; i += 256) {
+            const uint4 q = __ldg(row + i);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mx = max(mx, max(w[e] & 0x7FFFu, (w[e] >> 16) & 0x7FFFu));
+        }
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        mx = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mx = max(mx, warp_max[w]);
+        const int E = static_cast<int>(mx >> 7);           // biased bf16 exponent of the maximum
+        int sh = (E == 0) ? 0 : (E - 127) - 14;
+        sh = max(-100, min(100, sh));
+        down = __int_as_float((127 - sh) << 23);
+        up = __int_as_float((127 + sh) << 23);
+    }
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < n8; i += 256) {
+        const uint4 q = __ldg(row + i);
+        uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        if (CONVERT) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+                sum += lo;
+                sum += hi;
+                w[e] = h2_as_u32(__floats2half2_rn(lo * down, hi * down));
+            }
+            reinterpret_cast<uint4*>(x16 + (size_t)m * K)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(u32_as_h2(w[e]));
+                sum += f.x;
+                sum += f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += warp_sum[w];
+        tok_sum[m] = t;
+        tok_scale[m] = up;
+    }
+}
+
 struct GemmPlan {
     int tok, tokh, nh, tiles_m, stages, b_stages, raw_stages, raw_segs, commit_every, table_groups, tmem_cols, splits, kb_per_split;
     int pair;       // 1: clusters of two CTAs sharing each activation tile
     int occ2;       // 1: planned for two CTAs per SM (at most half the shared memory, <= 256 tensor-memory columns)
     int tiles_n;    // CTAs along N (even when pair)
+    int raw;        // 1: raw-integer tiles (int8, one scale per row): activations prepared in the workspace first
     size_t smem;
 };
 
@@ -917,6 +1035,26 @@ inline size_t split_workspace_bytes(int splits, int64_t M, int64_t N)
     return kCounterBytes + static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * 4;
 }
 
+// Raw-integer tiles: int8 weights with one scale per row, up to kRawMaxTokens tokens (beyond that the
+// kernel is bound by the tensor pipe and the dequantise work hides behind it, while preparing the
+// activations would cost a pass over them).  The workspace then also holds, after the K-split planes,
+// the per-token factors and sums and (bf16 activations) their fp16 copy.
+constexpr int64_t kRawMaxTokens = 256;
+inline bool raw_applicable(int64_t M, int64_t K, int32_t group_size, int32_t quant)
+{
+    return quant == MNQ_INT8 && group_size >= K && M <= kRawMaxTokens;
+}
+inline size_t raw_region_offset(int splits, int64_t M, int64_t N)
+{
+    const size_t planes = splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * 4 : 0;
+    return (kCounterBytes + planes + 255) & ~size_t(255);
+}
+inline size_t raw_region_bytes(int64_t M, int64_t K, bool convert)
+{
+    const size_t tok = ((static_cast<size_t>(M) * 8 + 255) & ~size_t(255));   // scale and sum per token
+    return tok + (convert ? static_cast<size_t>(M) * static_cast<size_t>(K) * 2 : 0);
+}
+
 // Token tiling and CTA pairing: up to 512 tokens per CTA as two accumulators of up to 256;
 // CTA pairs (variant 0: for tiles of more than 256 tokens, where activation tiles dominate the
 // L2 -> SM traffic and no longer fit three stages deep otherwise; 1: never; 2: always).
@@ -951,10 +1089,15 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (a.K > (1 << 28) || a.N > (1 << 30) || a.M > (1 << 24)) return false;
     if (reinterpret_cast<uintptr_t>(a.wq) % 16 || reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8) return false;
     if (a.group_size < a.K && a.group_size % BK) return false;
-    if (a.act_dtype == MNQ_FP16 && a.scale_dtype != MNQ_FP16) return false;   // the fp16 tile math is fp16 x fp16
-    // bf16 activations: integer tile when one scale per row and no zeros, else two bf16 tiles per k-block
-    const bool split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
-    const size_t a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
+    if (a.act_dtype == MNQ_FP16 && a.scale_dtype != MNQ_FP16 && !raw_applicable(a.M, a.K, a.group_size, a.quant))
+        return false;   // the fp16 tile math is fp16 x fp16
+    // int8 with one scale per row, few tokens: raw-integer tiles (variant 5 forbids them); their workspace
+    // need is checked once the K split is known
+    bool raw = raw_applicable(a.M, a.K, a.group_size, a.quant) && !(tuning && tuning->gemv_variant == 5) &&
+               (a.act_dtype == MNQ_BF16 || a.scale_dtype == MNQ_FP16 || a.scale_dtype == MNQ_BF16);
+    // bf16 activations otherwise: integer tile when one scale per row and no zeros, else two bf16 tiles per k-block
+    bool split_tiles = !raw && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    size_t a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
     GemmPlan pl{};
     if (!tile_plan(a.M, a.N, tuning ? tuning->gemv_variant : 0, &pl)) return false;
 
@@ -978,6 +1121,15 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     if (best > 1 && split_workspace_bytes(best, a.M, a.N) > (a.workspace ? a.workspace_bytes : 0)) return false;
     pl.kb_per_split = (num_kb + best - 1) / best;
     pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
+    if (raw && raw_region_offset(pl.splits, a.M, a.N) + raw_region_bytes(a.M, a.K, a.act_dtype == MNQ_BF16) >
+                   (a.workspace ? a.workspace_bytes : 0)) {
+        // not enough workspace for the prepared activations: the dequantising tile path
+        raw = false;
+        if (a.act_dtype == MNQ_FP16 && a.scale_dtype != MNQ_FP16) return false;
+        split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+        a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
+    }
+    pl.raw = raw ? 1 : 0;
     pl.table_groups = a.group_size >= a.K
                           ? 1
                           : static_cast<int>((static_cast<int64_t>(pl.kb_per_split) * BK + a.group_size - 1) / a.group_size + 1);
@@ -1003,6 +1155,18 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
         if (pl.raw_stages < 1) return false;
         int ast = static_cast<int>((budget - b_stage * bst) / a_stage);
         if (ast > 8) ast = 8;
+        if (raw) {
+            // Few tokens: the kernel streams weights and a k-block in flight needs a weight tile and an
+            // activation tile alike, so both rings get the same depth (the 60 % rule above leaves two
+            // weight tiles at 64 tokens, and a CTA then waits on its own MMAs every other k-block).
+            int n = static_cast<int>(budget / (a_stage + b_stage));
+            if (n > 8) n = 8;
+            if (n >= 2) {
+                ast = n;
+                bst = static_cast<int>((budget - a_stage * n) / b_stage);
+                if (bst > 8) bst = 8;
+            }
+        }
         // deep rings: release operands a pair of k-blocks at a time (needs even stage counts)
         pl.commit_every = 1;
         if (bst >= 4 && ast >= 4) {
@@ -1116,7 +1280,16 @@ bool gemm_supported(const MatmulArgs& a)
     return plan_gemm(a, nullptr, &pl);
 }
 
-size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant)
+{
+    const size_t base = gemm_split_workspace_bytes(M, N, K, group_size);
+    if (M < 1 || N < 1 || K < BK || K % BK || !raw_applicable(M, K, group_size, quant)) return base;
+    // room for the prepared activations (sized for bf16 ones, which need the fp16 copy)
+    const int splits = base > kCounterBytes ? static_cast<int>((base - kCounterBytes) / (static_cast<size_t>(M) * N * 4)) : 1;
+    return raw_region_offset(splits, M, N) + raw_region_bytes(M, K, true);
+}
+
+size_t gemm_split_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
 {
     // What plan_gemm asks for on a 148-SM part (B200).  On a device where it would split
     // further, the plan falls back to the number of splits the given workspace can hold.
@@ -1149,7 +1322,7 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
     p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.commit_every = pl.commit_every; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
-    const bool split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    const bool split_tiles = !pl.raw && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
     p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0) |
@@ -1160,12 +1333,44 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
 
+    // raw-integer tiles: per-token factors and sums (and the fp16 copy of bf16 activations) first
+    const void* x_for_tiles = a.x;
+    int64_t lda_tiles = a.lda;
+    bool x_is_bf16 = a.act_dtype == MNQ_BF16;
+    if (pl.raw) {
+        unsigned char* region = static_cast<unsigned char*>(a.workspace) + raw_region_offset(pl.splits, a.M, a.N);
+        float* tok_scale = reinterpret_cast<float*>(region);
+        float* tok_sum = tok_scale + a.M;
+        __half* x16 = reinterpret_cast<__half*>(region + ((static_cast<size_t>(a.M) * 8 + 255) & ~size_t(255)));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(a.M));
+        cfg.blockDim = dim3(256);
+        cfg.stream = a.stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int rcp;
+        if (x_is_bf16)
+            rcp = check_cuda(cudaLaunchKernelEx(&cfg, &prep_activations_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(a.x),
+                                                (long long)a.lda, (int)a.K, x16, tok_scale, tok_sum), "prep_activations launch");
+        else
+            rcp = check_cuda(cudaLaunchKernelEx(&cfg, &prep_activations_kernel<__half>, static_cast<const __half*>(a.x),
+                                                (long long)a.lda, (int)a.K, x16, tok_scale, tok_sum), "prep_activations launch");
+        if (rcp) return rcp;
+        p.tok_scale = tok_scale;
+        p.tok_sum = tok_sum;
+        p.offset_term = 1;
+        p.epilogue_scale = 1;
+        if (x_is_bf16) { x_for_tiles = x16; lda_tiles = a.K; x_is_bf16 = false; }
+    }
     // activations as a [M, K] tensor of 16-bit elements; box = 64 k x the tokens one CTA loads, 128-byte swizzle
     CUtensorMap xmap;
-    const int rc = encode_tensor_map_2d(&xmap, a.x, a.act_dtype == MNQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+    const int rc = encode_tensor_map_2d(&xmap, x_for_tiles, x_is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                         2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
-                                        static_cast<uint64_t>(a.lda) * 2, BK,
+                                        static_cast<uint64_t>(lda_tiles) * 2, BK,
                                         static_cast<uint32_t>(pl.pair ? pl.tokh / 2 : pl.tokh),
                                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
@@ -1179,6 +1384,10 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m),
               static_cast<unsigned>(pl.splits));
     const bool pair = pl.pair != 0;
+    if (pl.raw) {   // int8 only (plan_gemm)
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+        return launch_gemm_one<MNQ_INT8, __nv_bfloat16, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+    }
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
         if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);

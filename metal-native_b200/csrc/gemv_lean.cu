@@ -28,14 +28,6 @@ namespace mnq {
 __device__ unsigned int g_lean_status = 0;   // bit 0: a bounded wait for a weight tile gave up; bit 2: a wait for another rank
 
 
-#ifdef MNQ_TS
-__device__ unsigned long long g_gts[64][16];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define GTS(k) (g_gts[p.ts_slot & 63][k] = gtime())
-#else
-#define GTS(k) ((void)0)
-#endif
-
 namespace {
 
 constexpr int kPieceBytes = 256;
@@ -63,7 +55,6 @@ struct LeanParams {
     int gather_vec;                // the gathered buffers allow 16-byte stores at every row block this call writes
     int stage_rbs;                 // row blocks of output a CTA may stage before it stores them to the peers
     unsigned int spin_limit;       // polls a wait on another rank may take
-    int ts_slot;
 };
 
 // GROUPED: every step is one quantisation group (scale and offset applied per step); otherwise
@@ -173,9 +164,6 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
     // access comes after the previous kernel in the stream has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#ifdef MNQ_TS
-    if (GATHER && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) GTS(0);
-#endif
 
     // ---- activations: this CTA's K chunk of every token, as 8-blocks ----------------------------
     const int bpr = nsteps * SEG;                 // 8-blocks per token row
@@ -477,23 +465,12 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
         __syncthreads();
         if (tid == 0) {
             if (any && peers_ready_cta < 0) atomicOr(&g_lean_status, 4u);
-#ifdef MNQ_TS
-            const unsigned long long t_before_fence = gtime();
-#endif
             __threadfence();
-#ifdef MNQ_TS
-            const unsigned long long t_after_fence = gtime();
-#endif
             unsigned int* mine = p.gather.flag_peer[p.gather.rank];
             const unsigned int total = gridDim.x * gridDim.y;
             if (atomicAdd(mine + kGatherCounterWord, 1u) == total - 1) {
-#ifdef MNQ_TS
-                g_gts[p.ts_slot & 63][1] = t_before_fence; g_gts[p.ts_slot & 63][2] = t_after_fence;
-#endif
-                GTS(3);
                 mine[kGatherCounterWord] = 0u;   // ready for the next call
                 __threadfence_system();
-                GTS(4);
                 for (int g = 0; g < p.gather.world; ++g)
                     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.gather.flag_peer[g] + p.gather.rank),
                                  "r"(call_no) : "memory");
@@ -508,7 +485,6 @@ gemv_lean_kernel(const __grid_constant__ LeanParams p, const __grid_constant__ C
                     }
                     all_in = in;
                 }
-                GTS(5);
                 if (!all_in) atomicOr(&g_lean_status, 4u);   // a rank never reported: give up, do not hang
                 asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine + kGatherEpochWord), "r"(call_no) : "memory");
             }
@@ -625,9 +601,6 @@ int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap&
     }
     p.weights_immutable = option_value(MNQ_OPT_WEIGHTS_IMMUTABLE) != 0 ? 1 : 0;
     p.epi = a.epi;
-#ifdef MNQ_TS
-    { static int slot = 0; p.ts_slot = slot++; }
-#endif
     if (s.num_chunks > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.counters = reinterpret_cast<unsigned int*>(ws);
@@ -653,9 +626,6 @@ int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap&
 }
 
 
-#ifdef MNQ_TS
-extern "C" MNQ_API int mnq_dbg_gts(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gts, sizeof(g_gts)); }
-#endif
 
 int read_lean_status(unsigned int* out, bool clear)
 {

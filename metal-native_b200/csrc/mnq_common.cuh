@@ -317,7 +317,8 @@ int read_device_status(unsigned int* out, bool clear);
 size_t gemv_stream_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant, bool* supported);
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
 bool gemm_supported(const MatmulArgs& a);
-size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size);
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
+size_t gemm_split_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size);
 int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning);
 
 }  // namespace mnq

@@ -193,8 +193,9 @@ def set_option(name: str, value) -> None:
                            may be in flight (model state, loaded once): the decode kernels then
                            start fetching weights before the previous kernel in the stream ends;
     ``peer_wait_polls``    how long a sharded call waits for another rank before it gives up;
-    ``gemv_max_m``         largest M that takes the decode kernels (1..32, default 32, or the
-                           environment variable METAL_NATIVE_GEMV_MAX_M)."""
+    ``gemv_max_m``         largest M that takes the decode kernels (1..32), or 0, the default, to
+                           have it chosen per problem; the environment variable
+                           METAL_NATIVE_GEMV_MAX_M sets the initial value."""
     if name not in OPTIONS:
         raise _invalid(f"set_option: unknown option {name!r}")
     _check(_lib.mnq_set_option(OPTIONS[name], int(value)))

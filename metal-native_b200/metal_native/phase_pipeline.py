@@ -34,18 +34,20 @@ class PhaseConfig:
 
     ``matmul_strategy``  ``"gemv"`` (the reference's "vecmat"), ``"gemm"`` (its "tiled64") or
                          ``"auto"``: advisory, as in the reference;
-    ``gemv_max_m``       largest M that takes the decode kernels while this phase is active;
+    ``gemv_max_m``       largest M that takes the decode kernels while this phase is active
+                         (1..32), or 0 to let the library choose per problem (8, 24 or 32 by
+                         weight format and activation type);
     ``capture_graph``    replay the step from a CUDA graph (the counterpart of the reference's
                          ``encoder_max_ops`` / ``auto_flush_threshold`` command batching)."""
     matmul_strategy: str = "auto"
-    gemv_max_m: int = 32
+    gemv_max_m: int = 0
     capture_graph: bool = False
 
     def validate(self) -> None:
         if self.matmul_strategy not in MATMUL_STRATEGIES:
             raise ValueError(f"matmul_strategy must be one of {MATMUL_STRATEGIES}")
-        if not 1 <= int(self.gemv_max_m) <= 32:
-            raise ValueError("gemv_max_m must be in 1..32")
+        if not 0 <= int(self.gemv_max_m) <= 32:
+            raise ValueError("gemv_max_m must be in 0..32")
 
 
 def detect_phase(batch_size: int, seq_len: int) -> InferencePhase:
@@ -68,8 +70,8 @@ class PhasePipeline:
         self._lock = threading.Lock()
         self._phase = InferencePhase.Unknown
         # phase_pipeline.mm:27-40: tiled kernel for prefill, vecmat for decode
-        self._prefill = PhaseConfig(matmul_strategy="gemm", gemv_max_m=32, capture_graph=False)
-        self._decode = PhaseConfig(matmul_strategy="gemv", gemv_max_m=32, capture_graph=True)
+        self._prefill = PhaseConfig(matmul_strategy="gemm", gemv_max_m=0, capture_graph=False)
+        self._decode = PhaseConfig(matmul_strategy="gemv", gemv_max_m=0, capture_graph=True)
 
     # -- phase management (phase_pipeline.mm:76-89)
     def set_phase(self, phase: InferencePhase) -> None:
@@ -125,8 +127,13 @@ class PhasePipeline:
 
     def strategy_for(self, M: int) -> str:
         """Kernel family the applied threshold sends M tokens to: "gemv" or "gemm" (problems
-        neither family takes fall to the any-shape kernel whatever the phase)."""
-        return "gemv" if M <= self.active_config().gemv_max_m else "gemm"
+        neither family takes fall to the any-shape kernel whatever the phase); "auto" where the
+        threshold is left to the library and M lies between its smallest and largest choice
+        (``select_path`` answers for a concrete problem)."""
+        limit = self.active_config().gemv_max_m
+        if limit == 0:
+            return "gemv" if M <= 8 else "gemm" if M > 32 else "auto"
+        return "gemv" if M <= limit else "gemm"
 
     def capture_step(self, step, warmup: int = 2):
         """Records ``step()`` (operator calls on the current device, with fixed tensors) into a

@@ -143,7 +143,7 @@ def test_gemv_max_m_moves_the_threshold(mn):
     L = workloads.make_layer("t", 16, 1024, 256, seed=4)
     d = L.to("cuda")
     ref = H.oracle_matmul(L)
-    assert C.get_option("gemv_max_m") == 32 and C.select_path(16, 256, 1024, 128, "int4") == "gemv"
+    assert C.get_option("gemv_max_m") == 0 and C.select_path(16, 256, 1024, 128, "int4") == "gemv"
     a = C.dequant_matmul(*d.args())
     try:
         C.set_option("gemv_max_m", 8)
@@ -153,7 +153,7 @@ def test_gemv_max_m_moves_the_threshold(mn):
         with pytest.raises(C.MetalNativeError, match="InvalidArgument"):
             C.set_option("gemv_max_m", 33)
     finally:
-        C.set_option("gemv_max_m", 32)
+        C.set_option("gemv_max_m", 0)
     H.assert_close_to_oracle(a, ref, "gemv at M=16")
     H.assert_close_to_oracle(b, ref, "gemm at M=16")
 
@@ -215,7 +215,7 @@ def test_phase_pipeline_applies_threshold_and_replays_a_captured_decode_step(mn)
         assert pipe.apply().gemv_max_m == 4 and C.get_option("gemv_max_m") == 4
         assert pipe.strategy_for(24) == "gemm" and C.select_path(24, 512, 2048, 128, "int4") == "gemm"
     finally:
-        C.set_option("gemv_max_m", 32)
+        C.set_option("gemv_max_m", 0)
 
 
 def test_repeated_calls_replay_the_checked_arguments(mn):

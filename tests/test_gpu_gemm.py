@@ -76,6 +76,54 @@ PAIR_CASES = [
 ]
 
 
+RAW_CASES = [
+    # int8 with one scale per row, at most 256 tokens: raw-integer tiles (activations prepared once per call)
+    # M, N, K, asym, act dtype, scale dtype, K splits (0 = the plan's)
+    (64, 256, 512, False, torch.bfloat16, torch.float16, 0),     # config 4 style
+    (64, 200, 1024, True, torch.bfloat16, torch.float16, 0),     # with zeros: offset term through the token sums
+    (33, 128, 64, True, torch.float16, torch.float16, 0),        # fp16 activations are used as they are
+    (256, 384, 2048, True, torch.bfloat16, torch.bfloat16, 3),   # K split: the offset goes into the first plane only
+    (100, 130, 4096, False, torch.float16, torch.bfloat16, 2),   # fp16 activations with bf16 scales
+    (16, 256, 1024, True, torch.bfloat16, torch.float16, 0),     # few tokens (forced onto the tensor-core path)
+]
+
+
+@pytest.mark.parametrize("M,N,K,asym,adt,sdt,split", RAW_CASES)
+def test_gemm_raw_integer_tiles(mn, M, N, K, asym, adt, sdt, split):
+    """Raw-integer tiles against the oracle, against the dequantising tile path (kernel variant 5) where that
+    path takes the problem, in the fp32 output mode, and with wide-ranged bf16 activations (the per-token
+    rescale)."""
+    import mnq_workloads as workloads
+    C = mn._C
+    L = workloads.make_layer("t", M, K, N, quant_type="int8", group_size=K, act_dtype=adt, scale_dtype=sdt,
+                             asymmetric=asym, seed=M + N + K)
+    if adt == torch.bfloat16:   # rows of very different magnitude: every token gets its own power of two
+        L.x.mul_(torch.logspace(-6, 4, M).to(torch.bfloat16)[:, None])
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    t = _gemm_tuning(mn)
+    t.split_k = split
+    out = C.dequant_matmul(*d.args(), tuning=t)
+    C.synchronize()
+    assert C.device_status() == 0
+    # rows differ by ten orders of magnitude: compare row by row
+    for m in range(0, M, max(1, M // 8)):
+        H.assert_close_to_oracle(out[m:m + 1], ref[m:m + 1], f"raw int8 {M}x{N}x{K} row {m}")
+    if M > 32:
+        out32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
+        assert torch.equal(out32.to(adt), C.dequant_matmul(*d.args()))
+        for m in range(0, M, max(1, M // 4)):
+            scale = float(np.abs(ref[m]).max()) or 1.0
+            H.assert_fp32_gate(out32[m:m + 1] / scale * 8.0, ref[m:m + 1] / scale * 8.0, f"raw int8 fp32 row {m}")
+    if not (adt == torch.float16 and sdt == torch.bfloat16):
+        t5 = _gemm_tuning(mn)
+        t5.gemv_variant = 5                      # the dequantising tile path
+        t5.split_k = split
+        other = C.dequant_matmul(*d.args(), tuning=t5)
+        for m in range(0, M, max(1, M // 8)):
+            H.assert_close_to_oracle(other[m:m + 1], ref[m:m + 1], f"dequantised tiles row {m}")
+
+
 @pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("quant,M,N,K,g,adt,split", PAIR_CASES)
 def test_gemm_single_cta_and_cta_pairs(mn, quant, M, N, K, g, adt, split, variant):

@@ -25,7 +25,7 @@ def test_configurations_and_fallback():
 
     class Fake:
         def __init__(self):
-            self.opts = {"gemv_max_m": 32}
+            self.opts = {"gemv_max_m": 0}
 
         def set_option(self, k, v):
             self.opts[k] = v
@@ -35,6 +35,8 @@ def test_configurations_and_fallback():
     assert p.current_phase() is InferencePhase.Unknown
     assert p.active_config() == p.prefill_config()            # Unknown falls back to prefill
     assert p.decode_config().matmul_strategy == "gemv" and p.prefill_config().matmul_strategy == "gemm"
+    assert p.prefill_config().gemv_max_m == 0                 # threshold left to the library
+    assert [p.strategy_for(m) for m in (8, 9, 32, 33)] == ["gemv", "auto", "auto", "gemm"]
     p.set_decode_config(PhaseConfig("gemv", 16, True))
     p.set_prefill_config(PhaseConfig("gemm", 8, False))
     p.set_phase(InferencePhase.Decode)
@@ -56,9 +58,10 @@ def test_configurations_and_fallback():
 def test_threshold_option_and_environment_override():
     code = ("import sys; sys.path.insert(0, r'%s'); from metal_native import _C; "
             "print(_C.get_option('gemv_max_m'), _C.select_path(12, 4096, 4096, 128, 'int4'), "
-            "_C.select_path(4, 4096, 4096, 128, 'int4'))" % (ROOT / "metal-native_b200"))
-    for env_val, want in ((None, "32 gemv gemv"), ("8", "8 gemm gemv"), ("4", "4 gemm gemv"), ("99", "32 gemv gemv"),
-                          ("x", "32 gemv gemv")):
+            "_C.select_path(4, 4096, 4096, 128, 'int4'), _C.select_path(28, 4096, 4096, 128, 'int4'), "
+            "_C.select_path(12, 4096, 4096, 4096, 'int8'))" % (ROOT / "metal-native_b200"))
+    for env_val, want in ((None, "0 gemv gemv gemm gemm"), ("0", "0 gemv gemv gemm gemm"), ("8", "8 gemm gemv gemm gemm"),
+                          ("32", "32 gemv gemv gemv gemv"), ("99", "0 gemv gemv gemm gemm"), ("x", "0 gemv gemv gemm gemm")):
         env = dict(os.environ)
         env.pop("METAL_NATIVE_GEMV_MAX_M", None)
         if env_val is not None:
@@ -74,14 +77,21 @@ def test_options_validate_and_round_trip():
     _C.set_option("weights_immutable", 1)
     assert _C.get_option("weights_immutable") == 1
     _C.set_option("weights_immutable", 0)
-    for name, bad in (("weights_immutable", 2), ("peer_wait_polls", 0), ("gemv_max_m", 0), ("gemv_max_m", 33)):
+    for name, bad in (("weights_immutable", 2), ("peer_wait_polls", 0), ("gemv_max_m", -1), ("gemv_max_m", 33)):
         with pytest.raises(_C.MetalNativeError, match="InvalidArgument"):
             _C.set_option(name, bad)
     with pytest.raises(_C.MetalNativeError):
         _C.set_option("nope", 1)
     assert _C._lib.mnq_get_option(77) == -1
-    # fp16 activations with bf16 scales above the decode threshold: the any-shape kernel, and it says so
+    # the threshold left to the library: by weight format and activation type
     import torch
+    sp = _C.select_path
+    assert _C.get_option("gemv_max_m") == 0
+    assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (8, 9)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (24, 25)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (24, 25)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33)] == ["gemv", "gemm"]
+    # fp16 activations with bf16 scales above the decode threshold: the any-shape kernel, and it says so
     assert _C.select_path(64, 4096, 4096, 128, "int4", torch.float16, scale_dtype=torch.bfloat16) == "generic"
     assert _C.select_path(64, 4096, 4096, 128, "int4", torch.float16, scale_dtype=torch.float16) == "gemm"
     assert _C.select_path(64, 4096, 4096, 128, "int4", torch.bfloat16, scale_dtype=torch.float16) == "gemm"
