@@ -776,7 +776,10 @@ struct StreamPlan {
     int resident_ctas;   // SMs x CTAs per SM the plan assumed
 };
 
-bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, StreamPlan* out)
+// One planning attempt for a given number of CTAs per SM; `smem_limit` is what one CTA may use so
+// that this many are resident together.
+bool plan_stream_at(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, int ctas_per_sm,
+                    size_t smem_limit, StreamPlan* out)
 {
     if (a.M < 1 || a.M > 32) return false;
     if (a.quant == MNQ_INT4 && (a.K & 1)) return false;
@@ -798,7 +801,8 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     // tile is compiled for 256 threads
     // Up to 8 tokens: CTAs of 8 warps, two per SM (measured 1 us per launch better than one CTA of 16 on
     // the Qwen2.5-7B shapes: a CTA of the next kernel starts its set-up while its neighbour still streams)
-    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta : (pl.nt == 2 ? 16 : 8);
+    int warps = (tuning && tuning->warps_per_cta > 0) ? tuning->warps_per_cta
+                                                       : ((pl.nt == 2 || (pl.nt == 1 && ctas_per_sm == 1)) ? 16 : 8);
     if (warps > 16) warps = 16;
     if (pl.nt >= 4 && warps > 8) warps = 8;
     while (warps > 1 && row_blocks < warps) warps >>= 1;
@@ -814,7 +818,6 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     pl.stages = (tuning && tuning->stages > 0) ? tuning->stages : (pl.nt >= 2 ? 4 : 2);
     if (pl.stages > 8) pl.stages = 8;
     if (pl.stages < 2) pl.stages = 2;
-    const int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : (pl.nt == 1 ? 2 : 1);
     const int64_t slots = static_cast<int64_t>(a.sm_count) * ctas_per_sm * warps;
 
     // K chunks.  A warp processes `rbw` units (row block x chunk) one after the other, so the
@@ -855,6 +858,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
     if (chunks > pl.total_steps) chunks = pl.total_steps;
     if (chunks < 1 || row_blocks > kMaxCounters) chunks = 1;
 
+    bool grew_for_smem = false;
     for (;;) {
         pl.steps_per_chunk = (pl.total_steps + chunks - 1) / chunks;
         if (chunks > 1) pl.steps_per_chunk = (pl.steps_per_chunk + 3) & ~3;
@@ -882,17 +886,26 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
                    ~size_t(1023)) + static_cast<size_t>(warps) * (ring + 128);
         size_t need_ws = 0;
         if (pl.num_chunks > 1) need_ws = kCounterBytes + static_cast<size_t>(pl.num_chunks) * a.M * a.N * 4;
-        const bool smem_ok = pl.smem <= kMaxSmem;
+        const bool smem_ok = pl.smem <= smem_limit;
         const bool ws_ok = need_ws <= workspace_bytes;
+        const bool may_split = !swiglu && chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
+                               !(tuning && tuning->split_k > 0);
+        // up to 8 tokens: the compact kernel stages at most kLeanMaxStaged activations per CTA; shorter
+        // chunks, if the workspace has room for one more plane, keep the problem on it
+        if (smem_ok && ws_ok && pl.nt == 1 && may_split && a.M * chunk_k > kLeanMaxStaged &&
+            kCounterBytes + static_cast<size_t>(pl.num_chunks + 1) * a.M * a.N * 4 <= workspace_bytes) {
+            ++chunks;
+            continue;
+        }
         if (smem_ok && ws_ok) break;
         if (!smem_ok) {
             // too much shared memory: fewer stages, then shorter chunks (less staged
             // activation), then fewer warps
             if (pl.stages > 2) { --pl.stages; continue; }
-            if (rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap >>= 1; continue; }
-            if (!swiglu && chunks < pl.total_steps && chunks < kMaxSplitK && row_blocks <= kMaxCounters &&
-                !(tuning && tuning->split_k > 0)) {
+            if (many_tokens && rbw_cap > 1 && !(tuning && tuning->row_blocks_per_warp > 0)) { rbw_cap >>= 1; continue; }
+            if (may_split) {
                 ++chunks;
+                grew_for_smem = true;
                 continue;
             }
             if (warps > 4 && !(tuning && tuning->warps_per_cta > 0)) {
@@ -902,7 +915,7 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
             }
             return false;
         }
-        if (chunks == 1) return false;
+        if (chunks == 1 || grew_for_smem) return false;   // (shorter chunks were needed for shared memory)
         --chunks;
     }
     pl.resident_ctas = a.sm_count * ctas_per_sm;
@@ -910,6 +923,17 @@ bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace
                                       (static_cast<int64_t>(pl.warps) * rbw));
     *out = pl;
     return true;
+}
+
+// Up to 8 tokens the kernels run two CTAs per SM: the plan must then leave room for both (an SM has
+// 227 KB, of which every resident CTA reserves 1 KB), which with several tokens' activations staged
+// means shorter K chunks; only if no such plan exists does a single CTA per SM take everything.
+bool plan_stream(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, StreamPlan* out)
+{
+    int ctas_per_sm = (tuning && tuning->ctas_per_sm > 0) ? tuning->ctas_per_sm : (a.M <= 8 ? 2 : 1);
+    if (ctas_per_sm > 2) ctas_per_sm = 2;
+    if (ctas_per_sm == 2 && plan_stream_at(a, tuning, workspace_bytes, 2, (227 * 1024) / 2 - 1024, out)) return true;
+    return plan_stream_at(a, tuning, workspace_bytes, 1, kMaxSmem, out);
 }
 
 template <int QUANT, typename T, int NT, int CH>

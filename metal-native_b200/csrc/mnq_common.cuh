@@ -296,6 +296,8 @@ int encode_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType
                          CUtensorMapSwizzle swizzle);
 #endif
 // The streaming plan's figures the compact decode kernel (gemv_lean.cu) needs.
+// Activations (tokens x chunk length) a CTA of 8 warps of that kernel stages: 8 blocks of 8 per thread.
+constexpr int64_t kLeanMaxStaged = 8 * 256 * 8;
 struct LeanShape {
     int warps, num_chunks, steps_per_chunk, total_steps, stages;
     int resident_ctas;   // CTAs the plan expects to be resident on the GPU at once
