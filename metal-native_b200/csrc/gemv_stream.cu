@@ -1071,6 +1071,10 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
         LeanShape ls{pl.warps, pl.num_chunks, pl.steps_per_chunk, pl.total_steps, pl.stages, pl.resident_ctas};
         if (gemv_lean_supported(a, ls)) return launch_gemv_lean(a, ls, wmap);
     }
+    // 9 to 32 tokens: the kernel that reads activations prepared once per call (see gemv_mid.cu);
+    // variant 3 forces this one
+    if (pl.nt >= 2 && !(tuning && tuning->gemv_variant == 3) && gemv_mid_supported(a, tuning))
+        return launch_gemv_mid(a, tuning, wmap);
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
 #define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, wmap8, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)
@@ -1099,12 +1103,14 @@ int read_device_status(unsigned int* out, bool clear)
         rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &zero, sizeof zero), "cudaMemcpyToSymbol(status)");
         if (rc) return rc;
     }
-    unsigned int g = 0, l = 0;
+    unsigned int g = 0, l = 0, md = 0;
     rc = read_gemm_status(&g, clear);
     if (rc) return rc;
     rc = read_lean_status(&l, clear);
     if (rc) return rc;
-    *out = v | g | l;
+    rc = read_mid_status(&md, clear);
+    if (rc) return rc;
+    *out = v | g | l | md;
     return MNQ_SUCCESS;
 }
 

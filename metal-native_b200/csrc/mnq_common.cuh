@@ -307,6 +307,13 @@ bool gemv_lean_supported(const MatmulArgs& a, const LeanShape& s);
 int launch_gemv_lean(const MatmulArgs& a, const LeanShape& s, const CUtensorMap& wmap);
 #endif
 int read_lean_status(unsigned int* out, bool clear);
+// Batched decode, 9 to 32 tokens (gemv_mid.cu): activations prepared once per call in the workspace.
+bool gemv_mid_supported(const MatmulArgs& a, const mnq_tuning* tuning);
+size_t gemv_mid_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant);
+#ifdef CUDA_VERSION
+int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtensorMap& wmap);
+#endif
+int read_mid_status(unsigned int* out, bool clear);
 int launch_generic(const MatmulArgs& a);
 bool gemv_supported(const MatmulArgs& a);
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning);
