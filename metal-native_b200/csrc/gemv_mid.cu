@@ -12,10 +12,11 @@
 // into pieces of four steps: per piece the fp16 fragments of every token (rows padded so that
 // the eight token rows of a fragment load fall on different banks), then the fp32 sum of every
 // (step, token).  bf16 activations become fp16 times a per-token power of two.  The main kernel
-// walks K piece by piece: a producer thread brings image pieces into a small ring with one bulk
-// copy each, every consumer warp multiplies the piece against the weight pieces of its row blocks
-// and releases it, so a CTA holds a few pieces of activations, whatever K is, and the copies
-// overlap the arithmetic.  A warp keeps the accumulators of one or two row blocks (NB) in
+// walks K piece by piece: image pieces come into a small ring with one bulk copy each, every warp
+// multiplies the piece against the weight pieces of its row blocks and releases it, and the last
+// warp to release a ring slot requests the piece that will reuse it, so a CTA holds a few pieces
+// of activations, whatever K is, and the copies overlap the arithmetic.  (The copies hit L2, but
+// they queue behind every SM's outstanding weight requests, so the ring is as deep as fits.)  A warp keeps the accumulators of one or two row blocks (NB) in
 // registers over a sweep of K; with two, every activation fragment loaded from shared memory
 // feeds both, which is what keeps four token tiles within the shared-memory bandwidth.
 //
@@ -276,16 +277,11 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // GROUPED: every step is one quantisation group; otherwise one group per row.
 // NB: row blocks a warp carries through one sweep of K.
-// blockDim.x = 32 x (consumer warps + 1): the last warp's first lane is the producer of activation pieces.
 template <int QUANT, typename T, int NT, bool GROUPED, int NB>
-__global__ void __launch_bounds__(NT >= 4 ? 256 : 416)
+__global__ void __launch_bounds__((NT >= 4 && NB >= 2) ? 256 : 512)
 gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUtensorMap wmap)
 {
     using MT = __half;
@@ -297,17 +293,17 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int wc = (blockDim.x >> 5) - 1;                  // consumer warps
+    const int wc = blockDim.x >> 5;
     const int r = lane >> 2;
     const int t = lane & 3;
 
-    // shared memory: activation ring, weight rings (one per consumer warp), barriers
+    // shared memory: activation ring, weight rings (one per warp), barriers, release counters
     unsigned char* xring = smem;
     unsigned char* wring0 = smem + p.xstages * XSTAGE;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(wring0 + wc * p.stages * kStageBytes);
-    unsigned long long* xfull = bars;                      // [xstages]
-    unsigned long long* xempty = bars + p.xstages;         // [xstages]
-    unsigned long long* wbars = bars + 2 * p.xstages + (warp < wc ? warp : 0) * p.stages;   // [stages] of this warp
+    unsigned long long* xfull = bars;                                  // [xstages]
+    unsigned long long* wbars = bars + p.xstages + warp * p.stages;    // [stages] of this warp
+    unsigned int* xreleased = reinterpret_cast<unsigned int*>(bars + p.xstages + wc * p.stages);   // [xstages] warps done with the slot
 
     // this CTA's K pieces and row blocks; the row blocks are dealt evenly to CTAs, then to warps
     const int j0 = blockIdx.y * p.pieces_per_chunk;
@@ -320,34 +316,21 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
     if (tid == 0) {
         for (int s = 0; s < p.xstages; ++s) {
             mbar_init(smem_u32(&xfull[s]), 1);
-            mbar_init(smem_u32(&xempty[s]), wc);
+            xreleased[s] = 0u;
         }
-        for (int i = 0; i < wc * p.stages; ++i) mbar_init(smem_u32(&bars[2 * p.xstages + i]), 1);
+        for (int i = 0; i < wc * p.stages; ++i) mbar_init(smem_u32(&bars[p.xstages + i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == wc) {
-        // ---- producer of activation pieces ------------------------------------------------------
-        asm volatile("griddepcontrol.wait;" ::: "memory");   // the image is written by the kernel before this one
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        if (lane == 0) {
-            int s = 0, jj = 0;
-            uint32_t ph = 0;
-            for (int it = 0; it < x_total; ++it) {
-                if (it >= p.xstages && !mbar_wait(smem_u32(&xempty[s]), ph ^ 1u)) { atomicOr(&g_mid_status, 1u); break; }
-                const uint32_t bar = smem_u32(&xfull[s]);
-                mbar_expect_tx(bar, static_cast<uint32_t>(Img::BYTES));
-                bulk_copy_g2s(smem_u32(xring + s * XSTAGE), p.image + (size_t)(j0 + jj) * Img::BYTES,
-                              static_cast<uint32_t>(Img::BYTES), bar);
-                if (++jj == nj) jj = 0;
-                if (++s == p.xstages) { s = 0; ph ^= 1u; }
-            }
-        }
-        return;
-    }
+    // activation piece number `it` of this CTA (sweep-major, then K) into ring slot s
+    auto request_x = [&](int it, int s) {
+        const uint32_t bar = smem_u32(&xfull[s]);
+        mbar_expect_tx(bar, static_cast<uint32_t>(Img::BYTES));
+        bulk_copy_g2s(smem_u32(xring + s * XSTAGE), p.image + (size_t)(j0 + it % nj) * Img::BYTES,
+                      static_cast<uint32_t>(Img::BYTES), bar);
+    };
 
-    // ---- consumer warps ---------------------------------------------------------------------------
     const int wb0 = cb0 + static_cast<int>((long long)warp * ncb / wc);
     const int nrb = cb0 + static_cast<int>(((long long)warp + 1) * ncb / wc) - wb0;
     const int total_pieces = nrb * nj;
@@ -376,6 +359,9 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
     // and, if the caller declared them immutable, the weights.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // (the image is written by the kernel before this one)
+    if (tid == 0)
+        for (int it = 0; it < p.xstages && it < x_total; ++it) request_x(it, it);
     if (!p.weights_immutable)
         for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
 
@@ -502,7 +488,19 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
                     if (iss_count < total_pieces) issue_piece();
             }
             __syncwarp();       // ... and this activation piece
-            if (lane == 0) mbar_arrive(smem_u32(&xempty[xs]));
+            if (lane == 0) {
+                // the last warp to release the slot requests the piece that reuses it
+                __threadfence_block();
+                if (atomicAdd(&xreleased[xs], 1u) == static_cast<unsigned int>(wc - 1)) {
+                    xreleased[xs] = 0u;
+                    __threadfence_block();
+                    const int nxt = sweep * nj + jj + p.xstages;
+                    if (nxt < x_total) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        request_x(nxt, xs);
+                    }
+                }
+            }
             if (++xs == p.xstages) { xs = 0; xph ^= 1u; }
         }
         if (gave_up) break;
@@ -564,25 +562,28 @@ bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_by
 
     MidPlan pl{};
     pl.nt = a.M <= 16 ? 2 : 4;
-    pl.nb = pl.nt == 4 ? 2 : 1;
-    // consumer warps: with the producer warp, 256 threads (four token tiles need about 200 registers
-    // per thread) or 416
-    const int max_warps = pl.nt == 4 ? 7 : 12;
+    pl.nb = (pl.nt == 4 && tuning && tuning->gemv_variant == 6) ? 2 : 1;
+    // 8 warps where four token tiles of two row blocks need about 200 registers per thread, else 16
+    const int max_warps = pl.nb == 2 ? 8 : 16;
     pl.warps = max_warps;
     if (tuning && tuning->warps_per_cta > 0) pl.warps = tuning->warps_per_cta;
     if (pl.warps > max_warps) pl.warps = max_warps;
-    pl.stages = pl.nt == 4 ? 4 : 3;
+    // two weight pieces in flight per row block a warp carries keep HBM busy; whatever shared memory
+    // is left holds activation pieces
+    pl.stages = 2 * pl.nb;
     if (tuning && tuning->stages > 0) pl.stages = tuning->stages;
     if (pl.stages < 2 * pl.nb) pl.stages = 2 * pl.nb;
     if (pl.stages > 8) pl.stages = 8;
-    pl.xstages = pl.nt == 4 ? 2 : 3;
     pl.pieces = static_cast<int>(a.K / piece_k);
     pl.piece_bytes = image_piece_bytes(a.quant, pl.nt);
     const int xstage = (pl.piece_bytes + 127) & ~127;
     for (;;) {
-        pl.smem = static_cast<size_t>(pl.xstages) * xstage + static_cast<size_t>(pl.warps) * pl.stages * kStageBytes +
-                  8 * (2 * pl.xstages + pl.warps * pl.stages);
-        if (pl.smem <= static_cast<size_t>(kMidMaxSmem)) break;
+        const size_t fixed = static_cast<size_t>(pl.warps) * pl.stages * kStageBytes + 8 * (8 + pl.warps * pl.stages) + 64;
+        pl.xstages = fixed < static_cast<size_t>(kMidMaxSmem) ? static_cast<int>((kMidMaxSmem - fixed) / xstage) : 0;
+        if (pl.xstages > 8) pl.xstages = 8;
+        if (pl.xstages > pl.pieces) pl.xstages = pl.pieces;
+        pl.smem = static_cast<size_t>(pl.xstages) * xstage + fixed;
+        if (pl.xstages >= 2 || (pl.xstages >= 1 && pl.pieces == 1)) break;
         if (pl.stages > 2 * pl.nb) { --pl.stages; continue; }
         if (pl.warps > 4) { --pl.warps; continue; }
         return false;
@@ -643,7 +644,7 @@ int launch_mid_one(const MidParams& p, const CUtensorMap& wmap, const MidPlan& p
     int rc = check_cuda(cudaLaunchKernelEx(&cfg, prep, p), "prepare_image launch");
     if (rc) return rc;
     cfg.gridDim = dim3(static_cast<unsigned>(pl.grid_x), static_cast<unsigned>(pl.num_chunks), 1);
-    cfg.blockDim = dim3((pl.warps + 1) * 32);
+    cfg.blockDim = dim3(pl.warps * 32);
     cfg.dynamicSmemBytes = pl.smem;
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, wmap), "gemv_mid launch");
 }
@@ -695,8 +696,10 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
     const bool grouped = a.group_size < a.K;
     int rc;
 #define MNQ_MID(Q, T)                                                                                        \
-    rc = pl.nt == 4 ? (grouped ? launch_mid_one<Q, T, 4, true, 2>(p, wmap, pl, a.stream)                     \
-                               : launch_mid_one<Q, T, 4, false, 2>(p, wmap, pl, a.stream))                   \
+    rc = pl.nt == 4 ? (pl.nb == 2 ? (grouped ? launch_mid_one<Q, T, 4, true, 2>(p, wmap, pl, a.stream)       \
+                                             : launch_mid_one<Q, T, 4, false, 2>(p, wmap, pl, a.stream))     \
+                                  : (grouped ? launch_mid_one<Q, T, 4, true, 1>(p, wmap, pl, a.stream)       \
+                                             : launch_mid_one<Q, T, 4, false, 1>(p, wmap, pl, a.stream)))    \
                     : (grouped ? launch_mid_one<Q, T, 2, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 2, false, 1>(p, wmap, pl, a.stream))
     if (a.quant == MNQ_INT4) {
