@@ -219,17 +219,17 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
 }
 
 // Largest token count the decode kernels take.  MNQ_OPT_GEMV_MAX_M when set (1..32); otherwise by
-// what was measured on B200: the decode kernels' cost grows with every 8 tokens while the
-// tensor-core kernel's is flat up to 128, and where they cross depends on the tile mode.  int8
-// weights with one scale per row run raw-integer tiles, which win from 9 tokens; fp16 activations
-// use one fp16 tile per k-block and win from about 25; bf16 activations with group-wise scales
-// need two tiles per k-block and lose up to the decode kernels' limit of 32.
+// what was measured on B200.  The decode kernels feed warp MMAs, whose rate (one m16n8k16 per 8
+// cycles and SM sub-partition) bounds them from about 16 tokens on; the tensor-core kernel's cost is
+// flat up to 128 tokens but it has to expand every weight to 16 bits in shared memory.  int8 weights
+// with one scale per row run raw-integer tiles there, which draw level with the decode kernels at
+// 17 tokens; for every other format the decode kernels stay ahead up to their limit of 32.
 int64_t gemv_max_m_for(int64_t K, int32_t group_size, int32_t quant, int32_t act_dtype)
 {
+    (void)act_dtype;
     const int64_t set = option_value(MNQ_OPT_GEMV_MAX_M);
     if (set > 0) return set;
-    if (quant == MNQ_INT8 && group_size >= K) return 8;
-    if (act_dtype == MNQ_FP16) return 24;
+    if (quant == MNQ_INT8 && group_size >= K) return 16;
     return 32;
 }
 

@@ -16,9 +16,11 @@
 // multiplies the piece against the weight pieces of its row blocks and releases it, and the last
 // warp to release a ring slot requests the piece that will reuse it, so a CTA holds a few pieces
 // of activations, whatever K is, and the copies overlap the arithmetic.  (The copies hit L2, but
-// they queue behind every SM's outstanding weight requests, so the ring is as deep as fits.)  A warp keeps the accumulators of one or two row blocks (NB) in
-// registers over a sweep of K; with two, every activation fragment loaded from shared memory
-// feeds both, which is what keeps four token tiles within the shared-memory bandwidth.
+// they queue behind every SM's outstanding weight requests, so the ring is as deep as fits.)  A warp keeps the accumulators of its row block in registers
+// over a sweep of K.  (The kernel can also carry two row blocks per warp, NB = 2, so that every
+// activation fragment loaded from shared memory feeds both; that halves the warps a CTA can hold
+// and measured slower on B200, where these token counts are bound by the warp-MMA rate, one
+// m16n8k16 per 8 cycles and SM sub-partition, not by shared memory; it is not instantiated.)
 //
 // Row blocks are dealt out evenly over one CTA per SM and then over its warps; a layer with too
 // few row blocks is also cut along K (grid.y), each cut writing an fp32 plane that a second
@@ -43,8 +45,8 @@ constexpr int kPieceBytes = 256;                        // packed bytes of one r
 constexpr int kPieceSteps = kPieceBytes / kStepBytes;   // 4
 constexpr int kStageBytes = 16 * kPieceBytes;           // one weight-ring stage
 constexpr int kMidMaxSmem = 226 * 1024;
-constexpr int kPrepThreads = 256;
-constexpr int kPrepBatch = 8;
+constexpr int kPrepThreads = 1024;
+constexpr int kPrepBatch = 4;                           // 8-blocks a thread holds: K <= 8 * 4 * 1024
 
 // Geometry of one activation piece of the image, per weight format and token-tile count.
 template <int QUANT, int NT> struct Image {
@@ -119,22 +121,24 @@ prepare_image_kernel(const MidParams p)
     }
 
     const T* xg = static_cast<const T*>(p.x) + (size_t)m * p.lda;
+    // the whole token row in registers: one round trip to memory
+    uint4 xq[kPrepBatch];
+#pragma unroll
+    for (int u = 0; u < kPrepBatch; ++u) {
+        const int i = u * kPrepThreads + tid;
+        xq[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < blocks) xq[u] = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)i * 8));
+    }
     float x_down = 1.f;
     if (CONVERT_X) {
         // largest |x| of the token -> power-of-two scale that puts it just below 2^15
-        __syncthreads();
+        __syncthreads();   // x_max_bits is zero
         unsigned int mx = 0;
-        for (int base = tid; base < blocks; base += kPrepBatch * kPrepThreads) {
-            uint4 v[kPrepBatch];   // (a clamped index re-reads the last block, which leaves the maximum unchanged)
 #pragma unroll
-            for (int u = 0; u < kPrepBatch; ++u)
-                v[u] = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)min(base + u * kPrepThreads, blocks - 1) * 8));
+        for (int u = 0; u < kPrepBatch; ++u) {
+            const uint32_t w[4] = {xq[u].x, xq[u].y, xq[u].z, xq[u].w};
 #pragma unroll
-            for (int u = 0; u < kPrepBatch; ++u) {
-                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) mx = max(mx, max(w[e] & 0x7FFFu, (w[e] >> 16) & 0x7FFFu));
-            }
+            for (int e = 0; e < 4; ++e) mx = max(mx, max(w[e] & 0x7FFFu, (w[e] >> 16) & 0x7FFFu));
         }
         mx = __reduce_max_sync(0xffffffffu, mx);
         if (lane == 0 && mx) atomicMax(&x_max_bits, mx);
@@ -149,18 +153,11 @@ prepare_image_kernel(const MidParams p)
     }
 
     // whole warps walk the blocks together (the step sums are shuffle reductions over aligned lane runs)
-    // (kPrepBatch loads in flight per thread: the row costs a couple of round trips to L2, not one per block)
-    for (int base = 0; base < blocks; base += kPrepBatch * kPrepThreads) {
-        uint4 xq[kPrepBatch];
+    {
 #pragma unroll
         for (int u = 0; u < kPrepBatch; ++u) {
-            const int i = base + u * kPrepThreads + tid;
-            xq[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < blocks) xq[u] = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)i * 8));
-        }
-#pragma unroll
-        for (int u = 0; u < kPrepBatch; ++u) {
-        const int i = base + u * kPrepThreads + tid;
+        const int i = u * kPrepThreads + tid;
+        if (u * kPrepThreads + (tid & ~31) >= blocks) break;   // (warp-uniform)
         const bool valid = i < blocks;                      // blocks is a multiple of SEG: whole runs are valid or not
         uint32_t v[4] = {xq[u].x, xq[u].y, xq[u].z, xq[u].w};
         if (CONVERT_X) {   // bf16 -> fp16, times 2^-shift (exact unless the result is subnormal)
@@ -543,16 +540,16 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
 // Host side
 // ---------------------------------------------------------------------------------------------
 struct MidPlan {
-    int nt, nb, warps, stages, xstages, grid_x, num_chunks, pieces, pieces_per_chunk, piece_bytes;
+    int nt, nb, warps, stages, xstages, grid_x, num_chunks, pieces, pieces_per_chunk, piece_bytes, blocks_per_cta;
     size_t smem, planes_bytes, image_off, image_bytes, need_ws;
 };
 
-bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, MidPlan* out)
+bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, int want_warps, MidPlan* out)
 {
     if (a.M < 9 || a.M > 32 || a.swiglu_h > 0 || a.gather.world > 0) return false;
     const int step = a.quant == MNQ_INT4 ? 128 : 64;
     const int piece_k = step * kPieceSteps;
-    if (a.K < piece_k || a.K % piece_k || a.N < 1 || a.N > (1 << 30) || a.K > (1 << 28)) return false;
+    if (a.K < piece_k || a.K % piece_k || a.N < 1 || a.N > (1 << 30) || a.K > 8 * kPrepBatch * kPrepThreads) return false;
     const bool grouped = a.group_size < a.K;
     if (grouped) {
         if (a.group_size != step || a.G % kPieceSteps) return false;   // a step is a group; 8-byte scale loads
@@ -561,11 +558,10 @@ bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_by
     if (reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8 || reinterpret_cast<uintptr_t>(a.wq) % 16) return false;
 
     MidPlan pl{};
-    pl.nt = a.M <= 16 ? 2 : 4;
-    pl.nb = (pl.nt == 4 && tuning && tuning->gemv_variant == 6) ? 2 : 1;
-    // 8 warps where four token tiles of two row blocks need about 200 registers per thread, else 16
-    const int max_warps = pl.nb == 2 ? 8 : 16;
-    pl.warps = max_warps;
+    pl.nt = static_cast<int>((a.M + 7) / 8);   // 2, 3 or 4 token tiles
+    pl.nb = 1;
+    const int max_warps = 16;
+    pl.warps = want_warps;
     if (tuning && tuning->warps_per_cta > 0) pl.warps = tuning->warps_per_cta;
     if (pl.warps > max_warps) pl.warps = max_warps;
     // two weight pieces in flight per row block a warp carries keep HBM busy; whatever shared memory
@@ -615,7 +611,19 @@ bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_by
         if (pl.need_ws <= workspace_bytes) break;
         if (c == 1) return false;
     }
+    pl.blocks_per_cta = static_cast<int>((row_blocks + pl.grid_x - 1) / pl.grid_x);
     *out = pl;
+    return true;
+}
+
+// 16 warps per CTA when a CTA has more than 8 row blocks, else 8: with few row blocks the extra
+// warps only add weight requests in flight, behind which the activation pieces queue (measured).
+bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, MidPlan* out)
+{
+    if (!plan_mid_with(a, tuning, workspace_bytes, 16, out)) return false;
+    if (out->blocks_per_cta > 8 || (tuning && tuning->warps_per_cta > 0)) return true;
+    MidPlan small;
+    if (plan_mid_with(a, tuning, workspace_bytes, 8, &small)) *out = small;
     return true;
 }
 
@@ -696,10 +704,10 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
     const bool grouped = a.group_size < a.K;
     int rc;
 #define MNQ_MID(Q, T)                                                                                        \
-    rc = pl.nt == 4 ? (pl.nb == 2 ? (grouped ? launch_mid_one<Q, T, 4, true, 2>(p, wmap, pl, a.stream)       \
-                                             : launch_mid_one<Q, T, 4, false, 2>(p, wmap, pl, a.stream))     \
-                                  : (grouped ? launch_mid_one<Q, T, 4, true, 1>(p, wmap, pl, a.stream)       \
-                                             : launch_mid_one<Q, T, 4, false, 1>(p, wmap, pl, a.stream)))    \
+    rc = pl.nt == 4 ? (grouped ? launch_mid_one<Q, T, 4, true, 1>(p, wmap, pl, a.stream)                     \
+                               : launch_mid_one<Q, T, 4, false, 1>(p, wmap, pl, a.stream))                   \
+       : pl.nt == 3 ? (grouped ? launch_mid_one<Q, T, 3, true, 1>(p, wmap, pl, a.stream)                     \
+                               : launch_mid_one<Q, T, 3, false, 1>(p, wmap, pl, a.stream))                   \
                     : (grouped ? launch_mid_one<Q, T, 2, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 2, false, 1>(p, wmap, pl, a.stream))
     if (a.quant == MNQ_INT4) {
