@@ -103,7 +103,9 @@ typedef struct mnq_tuning {
     int32_t gemv_variant;        /* kernel variant, 0 auto.  GEMV path: 1 register-prefetch kernel, 2 shared-memory
                                     streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2),
                                     3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it, 5 no raw-integer
-                                    tiles.  Streaming GEMV: 3 the general kernel even where the compact one would run */
+                                    tiles.  Streaming GEMV: 3 the general kernel even where the compact or the batched one would
+                                    run, 4 no kernel that reads prepared activations (the compact kernel up to 8 tokens,
+                                    the general one above) */
     int32_t piece_bytes;         /* streaming GEMV: packed bytes per row per stage (multiple of 64) */
     int32_t stages;              /* streaming GEMV: stages per warp (2..8) */
     int32_t ctas_per_sm;         /* streaming GEMV: resident CTAs per SM the plan assumes */

@@ -538,7 +538,7 @@ size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size,
     size_t need = gemv_stream_workspace_bytes(M, N, K, group_size, quant, &streaming);
     const size_t two_way = kCounterBytes + static_cast<size_t>(2) * M * N * 4;
     if (need < two_way) need = two_way;
-    const size_t mid = gemv_mid_workspace_bytes(M, N, K, group_size, quant);   // 9-32 tokens: the prepared activations
+    const size_t mid = gemv_mid_workspace_bytes(M, N, K, group_size, quant);   // 5-32 tokens: the prepared activations
     if (need < mid) need = mid;
     if (streaming) return need;
     // shapes only the register-prefetch kernel takes: bound of the chunk count plan_gemv picks

@@ -1,4 +1,4 @@
-// Decode-shaped fused dequantise + matmul for 9 to 32 tokens (the batched-decode case; replaces,
+// Decode-shaped fused dequantise + matmul for 5 to 32 tokens (the batched-decode case; replaces,
 // for those token counts, the reference's tiled kernels dequant_matmul_int{4,8}_fp16,
 // shaders/matmul_dequant_kernel.metal:55-223, 351-479).  Same weight movement and arithmetic as
 // the other decode kernels (gemv_stream.cu, gemv_lean.cu): one TMA tile copy per 16-row x 256-byte
@@ -45,6 +45,9 @@ constexpr int kPieceBytes = 256;                        // packed bytes of one r
 constexpr int kPieceSteps = kPieceBytes / kStepBytes;   // 4
 constexpr int kStageBytes = 16 * kPieceBytes;           // one weight-ring stage
 constexpr int kMidMaxSmem = 226 * 1024;
+// Fewer tokens than this run the compact kernel: preparing the activations costs a launch and a
+// dependency (about 3.5 us), which five tokens' worth of per-CTA staging outweighs (measured).
+constexpr int kMidMinTokens = 5;
 constexpr int kPrepThreads = 1024;
 constexpr int kPrepBatch = 4;                           // 8-blocks a thread holds: K <= 8 * 4 * 1024
 
@@ -540,13 +543,13 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
 // Host side
 // ---------------------------------------------------------------------------------------------
 struct MidPlan {
-    int nt, nb, warps, stages, xstages, grid_x, num_chunks, pieces, pieces_per_chunk, piece_bytes, blocks_per_cta;
+    int nt, nb, warps, stages, xstages, grid_x, num_chunks, pieces, pieces_per_chunk, piece_bytes;
     size_t smem, planes_bytes, image_off, image_bytes, need_ws;
 };
 
 bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, int want_warps, MidPlan* out)
 {
-    if (a.M < 9 || a.M > 32 || a.swiglu_h > 0 || a.gather.world > 0) return false;
+    if (a.M < kMidMinTokens || a.M > 32 || a.swiglu_h > 0 || a.gather.world > 0) return false;
     const int step = a.quant == MNQ_INT4 ? 128 : 64;
     const int piece_k = step * kPieceSteps;
     if (a.K < piece_k || a.K % piece_k || a.N < 1 || a.N > (1 << 30) || a.K > 8 * kPrepBatch * kPrepThreads) return false;
@@ -558,7 +561,7 @@ bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspa
     if (reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8 || reinterpret_cast<uintptr_t>(a.wq) % 16) return false;
 
     MidPlan pl{};
-    pl.nt = static_cast<int>((a.M + 7) / 8);   // 2, 3 or 4 token tiles
+    pl.nt = static_cast<int>((a.M + 7) / 8);   // 1 to 4 token tiles
     pl.nb = 1;
     const int max_warps = 16;
     pl.warps = want_warps;
@@ -611,20 +614,17 @@ bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspa
         if (pl.need_ws <= workspace_bytes) break;
         if (c == 1) return false;
     }
-    pl.blocks_per_cta = static_cast<int>((row_blocks + pl.grid_x - 1) / pl.grid_x);
     *out = pl;
     return true;
 }
 
-// 16 warps per CTA when a CTA has more than 8 row blocks, else 8: with few row blocks the extra
-// warps only add weight requests in flight, behind which the activation pieces queue (measured).
+// 16 warps per CTA for big layers, 8 for small ones (under 48 MB of packed weights): a small layer
+// is over in a few microseconds, and the extra warps mostly add weight requests in flight, behind
+// which the activation pieces queue (measured on the Qwen2.5-7B, Llama-3-8B and Llama-3-70B shapes).
 bool plan_mid(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, MidPlan* out)
 {
-    if (!plan_mid_with(a, tuning, workspace_bytes, 16, out)) return false;
-    if (out->blocks_per_cta > 8 || (tuning && tuning->warps_per_cta > 0)) return true;
-    MidPlan small;
-    if (plan_mid_with(a, tuning, workspace_bytes, 8, &small)) *out = small;
-    return true;
+    const int64_t packed = a.N * (a.quant == MNQ_INT4 ? a.K / 2 : a.K);
+    return plan_mid_with(a, tuning, workspace_bytes, packed >= (int64_t(48) << 20) ? 16 : 8, out);
 }
 
 template <int QUANT, typename T, int NT, bool GROUPED, int NB>
@@ -704,7 +704,9 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
     const bool grouped = a.group_size < a.K;
     int rc;
 #define MNQ_MID(Q, T)                                                                                        \
-    rc = pl.nt == 4 ? (grouped ? launch_mid_one<Q, T, 4, true, 1>(p, wmap, pl, a.stream)                     \
+    rc = pl.nt == 1 ? (grouped ? launch_mid_one<Q, T, 1, true, 1>(p, wmap, pl, a.stream)                     \
+                               : launch_mid_one<Q, T, 1, false, 1>(p, wmap, pl, a.stream))                   \
+       : pl.nt == 4 ? (grouped ? launch_mid_one<Q, T, 4, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 4, false, 1>(p, wmap, pl, a.stream))                   \
        : pl.nt == 3 ? (grouped ? launch_mid_one<Q, T, 3, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 3, false, 1>(p, wmap, pl, a.stream))                   \

@@ -1,8 +1,9 @@
 // Decode-shaped fused dequantise + matmul, the general streaming kernel (M <= 32).  Replaces the
 // reference's dequant_matmul_int{4,8}_vecmat_fp16 (shaders/matmul_dequant_kernel.metal:229-345,
 // 485-576), computing every row m < M.  The common case of at most 8 tokens runs the compact
-// kernel of gemv_lean.cu, which shares this file's plan; this kernel takes 9-32 tokens, groups
-// that span several steps, ragged rows, the fused SwiGLU epilogue and the fused all-gather.
+// kernel of gemv_lean.cu, which shares this file's plan, and 5 to 32 tokens the batched kernel of
+// gemv_mid.cu; this kernel takes groups that span several steps, ragged rows, the fused SwiGLU
+// epilogue, the fused all-gather above 8 tokens and calls without a workspace.
 //
 // Data movement.  Every warp owns 16 consecutive weight rows at a time and a small
 // ring of stages in shared memory; one stage holds a piece of 256 consecutive packed
@@ -1066,15 +1067,15 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
                                              CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc8) return rc8;
     }
+    // 5 to 32 tokens: the kernel that reads activations prepared once per call (see gemv_mid.cu);
+    // variants 3 and 4 leave it out
+    if (!(tuning && (tuning->gemv_variant == 3 || tuning->gemv_variant == 4)) && gemv_mid_supported(a, tuning))
+        return launch_gemv_mid(a, tuning, wmap);
     // the compact kernel takes the common decode case (see gemv_lean.cu); variant 3 forces this one
     if (pl.nt == 1 && !(tuning && tuning->gemv_variant == 3)) {
         LeanShape ls{pl.warps, pl.num_chunks, pl.steps_per_chunk, pl.total_steps, pl.stages, pl.resident_ctas};
         if (gemv_lean_supported(a, ls)) return launch_gemv_lean(a, ls, wmap);
     }
-    // 9 to 32 tokens: the kernel that reads activations prepared once per call (see gemv_mid.cu);
-    // variant 3 forces this one
-    if (pl.nt >= 2 && !(tuning && tuning->gemv_variant == 3) && gemv_mid_supported(a, tuning))
-        return launch_gemv_mid(a, tuning, wmap);
     dim3 grid(pl.grid_x, static_cast<unsigned>(pl.num_chunks), 1);
     const int threads = pl.warps * 32;
 #define MNQ_GS(Q, T) rcl = launch_stream_nt<Q, T>(p, wmap, wmap8, pl.nt, pl.piece_bytes, grid, threads, pl.smem, a.stream)

@@ -1,4 +1,4 @@
-"""The batched-decode kernel (9 to 32 tokens, activations prepared once per call; gemv_mid.cu)
+"""The batched-decode kernel (5 to 32 tokens, activations prepared once per call; gemv_mid.cu)
 against the CPU oracle and against the general streaming kernel, through the C ABI.  Needs a B200."""
 import pytest
 import torch
@@ -24,6 +24,9 @@ def _tuning(mn, **kw):
 
 CASES = [
     # quant, M, N, K, group, asymmetric, activation dtype
+    ("int4", 5, 4096, 3584, 128, True, torch.float16),       # one token tile
+    ("int4", 8, 37888, 512, 128, False, torch.bfloat16),
+    ("int8", 7, 1040, 8192, 8192, True, torch.bfloat16),
     ("int4", 9, 4096, 3584, 128, True, torch.float16),       # two token tiles, one sweep
     ("int4", 16, 1000, 4096, 128, False, torch.bfloat16),    # ragged last row block, bf16 activations and scales
     ("int4", 16, 48, 512, 128, True, torch.float16),         # three row blocks, one K piece

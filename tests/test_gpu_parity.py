@@ -200,13 +200,16 @@ def test_compact_and_general_decode_kernels(mn, quant, M, N, K, g, asym, adt):
     ref = H.oracle_matmul(L)
     d = L.to("cuda")
     general = _tuning(mn, gemv_variant=3)
+    compact = _tuning(mn, gemv_variant=4)   # (from 5 tokens the default is the batched kernel)
     for call in range(2):
         a = C.dequant_matmul(*d.args())
         b = C.dequant_matmul(*d.args(), tuning=general)
+        c = C.dequant_matmul(*d.args(), tuning=compact)
         C.synchronize()
         assert C.device_status() == 0
-        H.assert_close_to_oracle(a, ref, f"compact {quant} {M}x{N}x{K} call {call}")
+        H.assert_close_to_oracle(a, ref, f"default {quant} {M}x{N}x{K} call {call}")
         H.assert_close_to_oracle(b, ref, f"general {quant} {M}x{N}x{K} call {call}")
+        H.assert_close_to_oracle(c, ref, f"compact {quant} {M}x{N}x{K} call {call}")
     a32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
     H.assert_fp32_gate(a32, ref, f"compact fp32 {quant} {M}x{N}x{K}")
 
