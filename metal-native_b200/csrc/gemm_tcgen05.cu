@@ -77,6 +77,7 @@ struct GemmParams {
     int stages;         // weight-tile (A) ring
     int b_stages;       // activation-tile (B) ring
     int tmem_cols;      // power of two >= max(32, tok)
+    int tmem_a_col;     // weight tiles in tensor memory (TA kernels): first column of their ring, 32 columns per slot
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
     int raw_stages;     // stages of the packed-weight ring
     int raw_segs;       // 128-byte-wide boxes per stage (consecutive along k)
@@ -203,6 +204,21 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the weight tile (A) read from tensor memory: 128 lanes = rows, the 16 k of one MMA in 8
+// consecutive 32-bit columns (two 16-bit values each) from a_tmem.
+__device__ __forceinline__ void umma_ta(uint32_t tmem_d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 8 columns of this thread's tensor-memory lane from 8 registers (two 16-byte chunks of a tile row)
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4& a, const uint4& b)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -499,7 +515,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
 // OCC2: tiles of at most 256 tokens leave half of the SM's shared memory, tensor memory and
 // registers unused, and a CTA of this kernel spends most of its time waiting (on loads, on the
 // MMA, on its own barriers): two CTAs per SM, each planned for half the shared memory.
-template <int QUANT, typename T, typename TT, bool PAIR, bool OCC2>
+// TA (tiles of at most 128 tokens, single CTAs, one tile per k-block): the dequantise warps write the
+// weight tile into TENSOR memory (tcgen05.st, a thread's row of 64 values = 32 columns of its lane) and
+// the MMA takes its A operand from there.  A 128 x 64 tile then never passes through shared memory
+// (16 KB written and 16 KB read per k-block otherwise, most of the shared-memory traffic of a CTA that
+// multiplies few tokens, which is what bounds such a CTA), and its ring lives in the tensor-memory
+// columns the accumulator leaves free.
+template <int QUANT, typename T, typename TT, bool PAIR, bool OCC2, bool TA = false>
 __global__ void __launch_bounds__(352, OCC2 ? 2 : 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                     const __grid_constant__ CUtensorMap wmap)
@@ -512,7 +534,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr bool SPLIT = std::is_same<TT, BSplit>::value;
     constexpr bool RAW = std::is_same<TT, RawInt>::value;      // fp16 tiles of raw integers, fp16 activations whatever T is
     constexpr bool MMA_BF16 = IS_BF16 && !RAW;
-    constexpr int A_STAGE = SPLIT ? 2 * A_BYTES : A_BYTES;   // bytes of one weight-ring slot
+    constexpr int A_STAGE = TA ? 0 : (SPLIT ? 2 * A_BYTES : A_BYTES);   // shared-memory bytes of one weight-ring slot
+    static_assert(!TA || (!PAIR && !SPLIT), "weight tiles in tensor memory: single CTAs, one tile per k-block");
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
@@ -647,7 +670,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     const uint32_t acc = tmem_base + (uint32_t)(h * p.tokh);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {   // 32 bytes along k = 2 descriptor address units
-                        if (PAIR) umma_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if (TA) umma_ta(acc, tmem_base + (uint32_t)(p.tmem_a_col + s * 32 + 8 * j), bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        else if (PAIR) umma_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         else umma(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         if (SPLIT) {   // the low halves of the weights, same activations, same accumulator
                             if (PAIR) umma_pair(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
@@ -775,6 +799,18 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                         sts128(a_row + xoff[c], hi);
                         sts128(a_row + A_BYTES + xoff[c], lo);
                     }
+                } else if constexpr (TA) {
+                    // this thread's row of the tile: 32 columns of its tensor-memory lane, 8 at a time
+                    using Chunk = TileChunk<QUANT, typename std::conditional<RAW, RawInt, T>::type>;
+                    const uint32_t a_t = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.tmem_a_col + s * 32);
+#pragma unroll
+                    for (int c = 0; c < 8; c += 2) {
+                        const uint4 o0 = Chunk::run(&w[c * Chunk::WORDS], s2, nz2);
+                        const uint4 o1 = Chunk::run(&w[(c + 1) * Chunk::WORDS], s2, nz2);
+                        tmem_st8(a_t + 4 * c, o0, o1);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 } else {
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
@@ -783,7 +819,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                         sts128(a_row + xoff[c], o);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (!TA) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
                     if (PAIR) bar_arrive_cluster(ready_at + 8 * d);   // the leader waits for both CTAs' tiles
@@ -991,6 +1027,8 @@ struct GemmPlan {
     int occ2;       // 1: planned for two CTAs per SM (at most half the shared memory, <= 256 tensor-memory columns)
     int tiles_n;    // CTAs along N (even when pair)
     int raw;        // 1: raw-integer tiles (int8, one scale per row): activations prepared in the workspace first
+    int ta;         // 1: weight tiles in tensor memory, from column tmem_a_col on
+    int tmem_a_col;
     size_t smem;
 };
 
@@ -1139,9 +1177,40 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     const size_t b_stage = static_cast<size_t>(pl.nh) * (pl.pair ? pl.tokh / 2 : pl.tokh) * 128;
     pl.raw_segs = 1;
     const size_t epilogue_min = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
-    auto size_rings = [&](size_t total) -> bool {
+    // weight tiles in tensor memory (see the kernel): tiles of at most 128 tokens (variant 6 forbids it)
+    const bool ta_ok = !pl.pair && !split_tiles && pl.nh == 1 && pl.tok <= 128 && !(tuning && tuning->gemv_variant == 6);
+    const int accum_cols = pl.tmem_cols;
+    auto size_rings = [&](size_t total, int tmem_budget) -> bool {
         size_t ring = 0, budget = 0;
         int bst = 0;
+        if (ta_ok) {
+            int slots = (tmem_budget - accum_cols) / 32;
+            if (slots > 8) slots = 8;
+            pl.raw_stages = 3;
+            ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
+            if (slots >= 2 && ring + 1024 + 2 * b_stage <= total) {
+                budget = total - 1024 - ring;
+                bst = static_cast<int>(budget / b_stage);
+                if (bst > 8) bst = 8;
+                int ast = slots;
+                pl.commit_every = 1;
+                if (bst >= 4 && ast >= 4) {
+                    pl.commit_every = 2;
+                    bst &= ~1;
+                    ast &= ~1;
+                }
+                pl.b_stages = bst;
+                pl.stages = ast;
+                pl.ta = 1;
+                pl.tmem_a_col = accum_cols;
+                pl.tmem_cols = tmem_budget;
+                pl.smem = 1024 + ring + b_stage * bst;
+                if (pl.smem < epilogue_min) pl.smem = epilogue_min;
+                return pl.smem <= total;
+            }
+        }
+        pl.ta = 0;
+        pl.tmem_cols = accum_cols;
         // big activation stages leave room for two packed stages (8 k-blocks of int4 ahead), small ones for three
         for (pl.raw_stages = b_stage >= 24 * 1024 ? 2 : 3; pl.raw_stages >= 1; --pl.raw_stages) {
             ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
@@ -1181,22 +1250,24 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
         return pl.smem <= total;
     };
     pl.occ2 = 0;
-    if (want_occ2 && size_rings(112 * 1024)) pl.occ2 = 1;
-    else if (!size_rings(226 * 1024)) return false;
+    if (want_occ2 && size_rings(112 * 1024, 256)) pl.occ2 = 1;
+    else if (!size_rings(226 * 1024, 512)) return false;
     *out = pl;
     return true;
 }
 
 template <int QUANT, typename T, typename TT>
 int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensorMap& wmap, dim3 grid, size_t smem,
-                    bool pair, bool occ2, cudaStream_t stream)
+                    bool pair, bool occ2, bool ta, cudaStream_t stream)
 {
     auto* kern = pair ? &gemm_tcgen05_kernel<QUANT, T, TT, true, false> : &gemm_tcgen05_kernel<QUANT, T, TT, false, false>;
     if constexpr (!std::is_same<TT, BSplit>::value) {
         if (occ2 && !pair) kern = &gemm_tcgen05_kernel<QUANT, T, TT, false, true>;
+        if (ta && !pair) kern = occ2 ? &gemm_tcgen05_kernel<QUANT, T, TT, false, true, true> : &gemm_tcgen05_kernel<QUANT, T, TT, false, false, true>;
     }
-    static std::atomic<uint64_t> attr_set[3];   // per kernel of this instantiation: CTA pairs, single CTAs, two CTAs per SM
-    std::atomic<uint64_t>& attr_flags = attr_set[pair ? 0 : (occ2 ? 2 : 1)];
+    // per kernel of this instantiation: CTA pairs, single CTAs, two CTAs per SM, and the two with weight tiles in tensor memory
+    static std::atomic<uint64_t> attr_set[5];
+    std::atomic<uint64_t>& attr_flags = attr_set[pair ? 0 : (ta ? (occ2 ? 4 : 3) : (occ2 ? 2 : 1))];
     if (smem > 48 * 1024 && !attribute_done_on_device(attr_flags)) {
         const int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024),
                                   "cudaFuncSetAttribute(gemm_tcgen05)");
@@ -1322,6 +1393,7 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.group_size = a.group_size; p.G = a.G; p.scale_dtype = a.scale_dtype;
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
     p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.commit_every = pl.commit_every; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
+    p.tmem_a_col = pl.tmem_a_col;
     const bool split_tiles = !pl.raw && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
     p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
@@ -1385,17 +1457,17 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
               static_cast<unsigned>(pl.splits));
     const bool pair = pl.pair != 0;
     if (pl.raw) {   // int8 only (plan_gemm)
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
-        return launch_gemm_one<MNQ_INT8, __nv_bfloat16, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+        return launch_gemm_one<MNQ_INT8, __nv_bfloat16, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
     }
     if (a.quant == MNQ_INT4) {
-        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
-        if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
-        return launch_gemm_one<MNQ_INT4, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+        if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+        if (split_tiles) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+        return launch_gemm_one<MNQ_INT4, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
     }
-    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
-    if (split_tiles) return launch_gemm_one<MNQ_INT8, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
-    return launch_gemm_one<MNQ_INT8, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, a.stream);
+    if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+    if (split_tiles) return launch_gemm_one<MNQ_INT8, __nv_bfloat16, BSplit>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+    return launch_gemm_one<MNQ_INT8, __nv_bfloat16, __nv_bfloat16>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
 }
 
 }  // namespace mnq

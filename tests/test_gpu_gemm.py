@@ -246,3 +246,37 @@ def test_config4_m64_int8_bf16_full_size(mn):
         assert torch.equal(out32.to(torch.bfloat16), out), "the 16-bit output is the rounded fp32 output"
         del d, out, out32
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("quant,M,N,K,g,adt", [
+    ("int4", 64, 384, 1024, 128, torch.float16),      # group-wise fp16: dequantised tiles
+    ("int4", 128, 200, 4096, 128, torch.float16),     # 128 tokens: four tensor-memory slots
+    ("int4", 40, 256, 2048, 2048, torch.bfloat16),    # bf16, one scale per row, no zeros: integer tiles
+    ("int8", 96, 272, 2048, 2048, torch.bfloat16),    # raw-integer tiles
+    ("int8", 33, 128, 512, 64, torch.float16),        # int8 group-wise
+])
+def test_weight_tiles_in_tensor_memory_match_shared_memory_tiles(mn, quant, M, N, K, g, adt):
+    """Tiles of at most 128 tokens keep the dequantised weight tile in tensor memory (the default);
+    kernel variant 6 sends it through shared memory.  Same arithmetic: the outputs are bit-identical,
+    and both meet the oracle gate; split K too."""
+    import mnq_workloads as workloads
+    C = mn._C
+    per_channel = g >= K
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             scale_dtype=torch.float16 if (quant == "int8" or adt == torch.float16) else adt,
+                             asymmetric=not (per_channel and quant == "int4"), seed=M + N + K)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    for split in (0, 2):
+        t = _gemm_tuning(mn)
+        t.split_k = split
+        a = C.dequant_matmul(*d.args(), tuning=t)
+        t6 = _gemm_tuning(mn)
+        t6.split_k = split
+        t6.gemv_variant = 6
+        b = C.dequant_matmul(*d.args(), tuning=t6)
+        C.synchronize()
+        assert C.device_status() == 0
+        H.assert_close_to_oracle(a, ref, f"tensor-memory tiles {quant} {M}x{N}x{K} split {split}")
+        H.assert_close_to_oracle(b, ref, f"shared-memory tiles {quant} {M}x{N}x{K} split {split}")
+        assert torch.equal(a, b), "the two tile paths differ"
