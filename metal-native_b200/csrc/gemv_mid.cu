@@ -353,6 +353,8 @@ gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUt
             if (++iss_jj == nj) { iss_jj = 0; ++iss_sweep; }
         }
     };
+    // (immutable weights: the whole ring before the dependency wait; holding part of it back until the
+    // first activation pieces are requested, as the compact kernel does, measured slightly slower here)
     if (p.weights_immutable)
         for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
     // Launched programmatically dependent: everything above touched only this CTA's shared memory

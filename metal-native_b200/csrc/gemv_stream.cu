@@ -357,10 +357,10 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
     ScaleRegs sc_cur, sc_nxt;
     sc_cur.s0 = sc_cur.s1 = sc_cur.z0 = sc_cur.z1 = make_uint2(0u, 0u);
     sc_nxt = sc_cur;
-    if (p.weights_immutable) {
-        for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
-        if (total_pieces > 0) load_scales(0, 0, sc_cur);
-    }
+    // (one stage only: every early weight request delays the activation loads issued after the wait)
+    const int early = p.weights_immutable ? 1 : 0;
+    for (int j = 0; j < early && j < total_pieces; ++j) issue_piece();
+    if (early > 0 && total_pieces > 0) load_scales(0, 0, sc_cur);
     // With a programmatic dependent launch this CTA may have started while the previous kernel
     // in the stream was still running.  Everything above touched only this CTA's shared memory
     // (and, if the caller declared them immutable, weights, scales and zeros); every other global
@@ -398,10 +398,8 @@ gemv_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wma
 
     // The activation loads go out ahead of the weight stream: a request issued behind a full ring
     // of weight tiles waits in the memory system until those tiles have been fetched.
-    if (!p.weights_immutable) {
-        for (int j = 0; j < p.stages && j < total_pieces; ++j) issue_piece();
-        if (total_pieces > 0) load_scales(0, 0, sc_cur);
-    }
+    for (int j = early; j < p.stages && j < total_pieces; ++j) issue_piece();
+    if (early == 0 && total_pieces > 0) load_scales(0, 0, sc_cur);
     __syncthreads();   // xsum (and x_max_bits) are zeroed
 
     if (CONVERT_X) {
