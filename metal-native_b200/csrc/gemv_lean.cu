@@ -9,8 +9,9 @@
 // Why a second kernel.  A launch on a Qwen2.5-7B projection lasts 12-16 microseconds, of which
 // the weights stream for 6-12; the rest is what a freshly started SM spends between entry and its
 // first MMA, and the last piece's arithmetic after the last byte has arrived.  This kernel keeps
-// the path to the first MMA short: the ring is requested by the first instructions (before the
-// dependency wait if the weights are declared immutable), the activation block is staged by
+// the path to the first MMA short: the first ring stage is requested by the first instructions
+// (before the dependency wait if the weights are declared immutable; the second stage goes out
+// behind the activation loads, which would otherwise wait for it), the activation block is staged by
 // straight-line code without atomics (a group's activation sum is a shuffle reduction inside an
 // aligned run of lanes), and the scales and zeros of a piece are four aligned 8-byte loads through
 // pointers advanced per piece.  CTAs are small (8 warps, two per SM) so that a CTA of the next
