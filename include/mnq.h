@@ -268,6 +268,19 @@ MNQ_API int mnq_dequant_matmul_swiglu(const void* activations, const void* weigh
                                       int64_t ldc, int32_t group_size, int32_t quant_type, int32_t act_dtype,
                                       int32_t scale_dtype, void* stream);
 
+/* Fused residual addition + RMSNorm, the operator that produces the activations of the MLP these
+ * projections belong to: out = rms_norm(input + residual) * weight, row by row.  Replaces the
+ * reference's fast::fused_residual_norm (include/metal_native/future/fast_ops.h:99-107) and keeps the
+ * arithmetic of its kernels (shaders/fused_residual_norm.metal:43-76): the sum is rounded to the
+ * 16-bit type and that rounded value is normalised, the mean of squares is taken over the unrounded
+ * sums in fp32, rms_inv = rsqrt(mean + eps), one rounding at the store.  input, residual, out:
+ * [rows, hidden] with row strides ld_* (elements); weight: [hidden]; all of `dtype` (MNQ_FP16 or
+ * MNQ_BF16; the reference has fp16 and fp32).  sum_out, if not NULL, receives the rounded sums (the
+ * block's new residual stream; the reference discards them).  out may alias input or residual. */
+MNQ_API int mnq_residual_rmsnorm(const void* input, const void* residual, const void* weight, void* out,
+                                 void* sum_out, int64_t rows, int64_t hidden, int64_t ld_in, int64_t ld_res,
+                                 int64_t ld_out, int64_t ld_sum, float eps, int32_t dtype, void* stream);
+
 /* The fused operator for activations and output in HOST memory (pinned for the copies to be
  * asynchronous), weights, scales and zeros resident on the device.  The reference's tensors live in
  * memory both the CPU and the GPU address (MTLStorageModeShared, src/core/tensor_helpers.mm:13-48), so

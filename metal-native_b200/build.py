@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "metal_native" / "lib"
 LIB = LIB_DIR / "libmnq.so"
-SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemv_stream.cu", "gemv_lean.cu", "gemv_mid.cu", "gemm_tcgen05.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "dequantize.cu", "gemv.cu", "gemv_stream.cu", "gemv_lean.cu", "gemv_mid.cu", "gemm_tcgen05.cu", "no_alloc.cu", "residual_norm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

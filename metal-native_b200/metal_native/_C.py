@@ -73,6 +73,8 @@ def _load() -> ctypes.CDLL:
     L.mnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), i32]
     L.mnq_dequant_matmul_swiglu.restype = ctypes.c_int
     L.mnq_dequant_matmul_swiglu.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32, i32, vp]
+    L.mnq_residual_rmsnorm.restype = ctypes.c_int
+    L.mnq_residual_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, ctypes.c_float, i32, vp]
     L.mnq_host_workspace_bytes.restype = sz
     L.mnq_host_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.mnq_dequant_matmul_host.restype = ctypes.c_int
@@ -429,6 +431,52 @@ def dequant_matmul_fused(activations, weights_packed, scales, zeros, group_size,
     return out
 
 
+def fused_residual_norm(input, residual, weight, eps: float = 1e-6, *, out=None, sum_out=None):
+    """``rms_norm(input + residual) * weight`` over the last dimension: the reference's
+    ``fast::fused_residual_norm`` (``include/metal_native/future/fast_ops.h:99-107``, bound at
+    ``bindings/bind_ops.cpp:107-112``) with the arithmetic of its kernels
+    (``shaders/fused_residual_norm.metal:43-76``).  ``input`` and ``residual``: CUDA tensors of one shape
+    and dtype (fp16, or bf16 by extension) whose rows are contiguous; ``weight``: [hidden].  Returns the
+    normalised tensor; ``sum_out`` (same shape), if given, receives ``input + residual`` rounded to the
+    tensors' dtype, i.e. the block's new residual stream.  ``out`` / ``sum_out`` may be ``input`` or
+    ``residual`` themselves."""
+    for name, t in (("input", input), ("residual", residual), ("weight", weight)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise _invalid(f"fused_residual_norm: {name} must be a CUDA tensor")
+    if input.dtype not in _DT or input.dtype == torch.float32:
+        raise _invalid("fused_residual_norm: input must be float16 or bfloat16")
+    if residual.shape != input.shape or residual.dtype != input.dtype:
+        raise _invalid("fused_residual_norm: residual must have the shape and dtype of input")
+    if input.dim() < 1:
+        raise _invalid("fused_residual_norm: input must have at least one dimension")
+    hidden = input.shape[-1]
+    if weight.dim() != 1 or weight.shape[0] != hidden or weight.dtype != input.dtype or not weight.is_contiguous():
+        raise _invalid("fused_residual_norm: weight must be a contiguous [hidden] tensor in the dtype of input")
+
+    def rows_of(t, what):
+        v = t.reshape(-1, hidden) if t.is_contiguous() else (t if t.dim() == 2 else None)
+        if v is None or (hidden > 1 and v.stride(1) != 1):
+            raise _invalid(f"fused_residual_norm: {what} must be contiguous, or 2-D with contiguous rows")
+        return v
+
+    x2, r2 = rows_of(input, "input"), rows_of(residual, "residual")
+    if out is None:
+        out = torch.empty(input.shape, dtype=input.dtype, device=input.device)
+    for name, t in (("out", out), ("sum_out", sum_out)):
+        if t is not None and (not isinstance(t, torch.Tensor) or not t.is_cuda or t.shape != input.shape or t.dtype != input.dtype):
+            raise _invalid(f"fused_residual_norm: {name} must be a CUDA tensor with the shape and dtype of input")
+    o2 = rows_of(out, "out")
+    s2 = rows_of(sum_out, "sum_out") if sum_out is not None else None
+    rows = x2.shape[0]
+    ld = lambda v: v.stride(0) if rows > 1 else max(hidden, 1)
+    with torch.cuda.device(input.device):
+        _check(_lib.mnq_residual_rmsnorm(x2.data_ptr(), r2.data_ptr(), weight.data_ptr(), o2.data_ptr(),
+                                         s2.data_ptr() if s2 is not None else None, rows, hidden, ld(x2), ld(r2), ld(o2),
+                                         ld(s2) if s2 is not None else 0, float(eps), _DT[input.dtype],
+                                         torch.cuda.current_stream(input.device).cuda_stream))
+    return out
+
+
 STATIC_SCRATCH_BYTES = 4 << 20   # MNQ_STATIC_SCRATCH_BYTES of include/mnq.h
 
 
@@ -616,4 +664,4 @@ def exported_symbols() -> list[str]:
             "mnq_dequant_matmul", "mnq_dequant_matmul_ex", "mnq_select_path", "mnq_dequantize",
             "mnq_dequantize_flat", "mnq_device_status", "mnq_dequant_matmul_gather", "mnq_host_workspace_bytes",
             "mnq_dequant_matmul_host", "mnq_dequant_matmul_swiglu", "mnq_select_path_ex", "mnq_set_option",
-            "mnq_get_option", "mnq_dequant_matmul_fused", "mnq_dequant_matmul_static"]
+            "mnq_get_option", "mnq_dequant_matmul_fused", "mnq_dequant_matmul_static", "mnq_residual_rmsnorm"]

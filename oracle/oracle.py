@@ -239,3 +239,26 @@ def host_threads() -> int:
         return len(os.sched_getaffinity(0))
     except AttributeError:  # pragma: no cover
         return os.cpu_count() or 1
+
+
+def residual_rms_norm(inp: np.ndarray, residual: np.ndarray, weight: np.ndarray, eps: float, kind: str):
+    """CPU restatement of the reference's fused residual + RMSNorm kernel
+    (``shaders/fused_residual_norm.metal:43-76``, fp16 variant; the same steps for bf16): per row,
+    ``s = float(input) + float(residual)`` (``:62``), the sum is rounded to the 16-bit type and stored
+    (``:63``), the sum of squares is taken over the unrounded ``s`` in fp32 (``:64``),
+    ``rms_inv = rsqrt(sum_sq / n + eps)`` (``:68``), and the output is the rounded sum times ``rms_inv``
+    times the weight, rounded (``:70-73``).  The reference adds the squares lane by lane and then
+    across the SIMD group; here they are added in float64 and rounded once, so a comparison has to
+    allow the output's last bit.
+
+    ``inp``, ``residual`` [rows, n] and ``weight`` [n] as fp32 arrays holding fp16 / bf16 values
+    (``kind``).  Returns (normalised, rounded sums), both fp32 arrays of values exact in ``kind``."""
+    to_bits, from_bits = ((fp32_to_fp16_bits, fp16_bits_to_fp32) if kind == "fp16"
+                          else (fp32_to_bf16_bits, bf16_bits_to_fp32))
+    s = np.asarray(inp, np.float32) + np.asarray(residual, np.float32)
+    h = from_bits(to_bits(s))
+    n = s.shape[-1]
+    mean = (s.astype(np.float64) ** 2).sum(axis=-1, keepdims=True) / n
+    rms_inv = (1.0 / np.sqrt(mean.astype(np.float32) + np.float32(eps))).astype(np.float32)
+    out = (h * rms_inv).astype(np.float32) * np.asarray(weight, np.float32)
+    return from_bits(to_bits(out.astype(np.float32))), h
