@@ -103,3 +103,12 @@ class PeerGather:
         _C.dequant_matmul_gather(activations, weights_shard, scales_shard, zeros_shard, group_size, quant_type,
                                  self.out_ptrs, self.flag_ptrs, self.rank, self.rank * self.n_local, self.N)
         return self.out
+
+    def check(self) -> None:
+        """Synchronises this rank's stream and raises ``MetalNativeError`` (TimeoutError) if a kernel
+        gave up waiting for another rank since the last check: the gathered output is then
+        incomplete.  ``matmul`` itself never synchronises; call this where the caller synchronises
+        anyway (end of a step, before results leave the device)."""
+        from . import _C
+        _C.synchronize()
+        _C.check_device_status()

@@ -40,8 +40,7 @@ def main():
         pg = sharded.PeerGather(M, n_local, world, adt, dev)
         for call in range(5):
             got = pg.matmul(x, ws_, ss_, zs_, gs, q)
-            torch.cuda.synchronize()
-            assert _C.device_status() == 0, f"device status {_C.device_status()}"
+            pg.check()   # synchronises; raises if a kernel gave up waiting for the other rank
             assert torch.equal(got, want), f"rank {rank} case {(M, K, N)} call {call}: fused gather differs"
             x = x * 1.0   # a new activation tensor each call keeps the calls honest about stream order
         dist.barrier()
