@@ -251,6 +251,12 @@ def residual_rms_norm(inp: np.ndarray, residual: np.ndarray, weight: np.ndarray,
     across the SIMD group; here they are added in float64 and rounded once, so a comparison has to
     allow the output's last bit.
 
+    Parity unpinned: the reference holds no value test or golden vector for this operator (its
+    Metal kernels cannot run here).  What the reference's test suite does hold is the numpy formula
+    ``reference_rms_norm`` (``tests/test_numerical_accuracy.py:68-84``: ``x / sqrt(mean(x^2) + eps) *
+    weight``); tests/test_residual_norm.py checks this restatement against that formula applied to
+    ``input + residual``, to the precision of the 16-bit roundings.
+
     ``inp``, ``residual`` [rows, n] and ``weight`` [n] as fp32 arrays holding fp16 / bf16 values
     (``kind``).  Returns (normalised, rounded sums), both fp32 arrays of values exact in ``kind``."""
     to_bits, from_bits = ((fp32_to_fp16_bits, fp16_bits_to_fp32) if kind == "fp16"

@@ -28,6 +28,25 @@ def test_restatement_on_a_hand_checked_row():
     assert out[0, 0] == oracle.fp16_bits_to_fp32(oracle.fp32_to_fp16_bits(np.array([np.float32(2048.0) * inv], np.float32)))[0]
 
 
+def test_restatement_against_the_reference_test_suites_rms_norm_formula():
+    """x / sqrt(mean(x^2) + eps) * weight on x = input + residual, in float64 (the formula of the
+    reference's tests/test_numerical_accuracy.py:68-84): the restatement differs only by its
+    16-bit roundings (the sum, the output)."""
+    rng = np.random.default_rng(11)
+    for kind, ulp in (("fp16", 2.0 ** -10), ("bf16", 2.0 ** -7)):
+        to_bits, from_bits = ((oracle.fp32_to_fp16_bits, oracle.fp16_bits_to_fp32) if kind == "fp16"
+                              else (oracle.fp32_to_bf16_bits, oracle.bf16_bits_to_fp32))
+        q = lambda a: from_bits(to_bits(a.astype(np.float32)))
+        x, r = q(rng.standard_normal((5, 768)) * 3), q(rng.standard_normal((5, 768)))
+        w = q(1.0 + 0.2 * rng.standard_normal(768))
+        out, h = oracle.residual_rms_norm(x, r, w, 1e-5, kind)
+        s = x.astype(np.float64) + r.astype(np.float64)
+        want = s / np.sqrt((s ** 2).mean(axis=-1, keepdims=True) + 1e-5) * w.astype(np.float64)
+        # one rounding of the sum (relative ulp/2) and one of the output (ulp/2), plus slack
+        assert np.all(np.abs(out - want) <= 1.6 * ulp * np.abs(want) + 1e-6)
+        assert np.all(np.abs(h - s) <= 0.5 * ulp * np.abs(s) + 1e-12)
+
+
 def test_symbol_is_exported_and_validates_on_the_host():
     from metal_native import _C
     assert "mnq_residual_rmsnorm" in _C.exported_symbols()
