@@ -39,14 +39,15 @@ int fail(int status, const char* fmt, ...)
 // Process-wide options
 // ---------------------------------------------------------------------------
 namespace {
-constexpr int kNumOptions = 3;
-std::atomic<int64_t> g_options[kNumOptions] = {{0}, {int64_t(1) << 22}, {0}};
+constexpr int kNumOptions = 4;
+std::atomic<int64_t> g_options[kNumOptions] = {{0}, {int64_t(1) << 22}, {0}, {0}};
 std::once_flag g_options_env;
 
 bool option_in_range(int option, int64_t v)
 {
     switch (option) {
         case MNQ_OPT_WEIGHTS_IMMUTABLE: return v == 0 || v == 1;
+        case MNQ_OPT_BF16_FP16_TILES: return v == 0 || v == 1;
         case MNQ_OPT_PEER_WAIT_POLLS: return v >= 1 && v <= (int64_t(1) << 31) - 1;
         case MNQ_OPT_GEMV_MAX_M: return v >= 0 && v <= 32;   // 0: chosen per problem
         default: return false;

@@ -351,6 +351,17 @@ template <> struct TileChunk<MNQ_INT8, RawInt> {
 // two bf16 values, hi = RN(w) and lo = RN(w - hi) (together good to 2^-16 relative), kept as
 // two tiles, and every MMA is issued twice, once per tile, into the same accumulator.
 struct BSplit {};
+// bf16 activations with group-wise scales (or zeros), the faster and less exact way, for callers that opt in
+// (MNQ_OPT_BF16_FP16_TILES) and whose workspace has room: the
+// activations are converted once per call to fp16 times a per-token power of two (prep_activations_kernel,
+// as for raw-integer tiles) and the weight tile is ONE fp16 tile, as for fp16 activations.  The scales
+// and zeros of a row are divided by a power of two 2^E chosen per row and K split so that
+// max(8 |s|, |z|) lands in [1, 2) (whatever 16-bit type they come in, they then fit fp16's range and keep
+// their significand; groups 2^14 below the row's largest lose bits worth less than that), and the
+// epilogue multiplies the accumulator by 2^E and the token's power of two.  Every weight is then rounded to
+// fp16's 11 significant bits, as with fp16 activations (noise of about 2.8e-4 of the output RMS), where the
+// two-tile path keeps 16.
+struct HalfTile {};
 
 template <int QUANT> struct SplitChunk;
 template <> struct SplitChunk<MNQ_INT4> {
@@ -533,12 +544,15 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
     constexpr bool SPLIT = std::is_same<TT, BSplit>::value;
     constexpr bool RAW = std::is_same<TT, RawInt>::value;      // fp16 tiles of raw integers, fp16 activations whatever T is
-    constexpr bool MMA_BF16 = IS_BF16 && !RAW;
+    constexpr bool HALF_T = std::is_same<TT, HalfTile>::value; // fp16 tiles and fp16 copies of bf16 activations
+    constexpr bool MMA_BF16 = IS_BF16 && !RAW && !HALF_T;
+    using TileT = typename std::conditional<RAW, RawInt, typename std::conditional<HALF_T, __half, T>::type>::type;
     constexpr int A_STAGE = TA ? 0 : (SPLIT ? 2 * A_BYTES : A_BYTES);   // shared-memory bytes of one weight-ring slot
     static_assert(!TA || (!PAIR && !SPLIT), "weight tiles in tensor memory: single CTAs, one tile per k-block");
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
+    __shared__ float row_up[HALF_T ? BN : 1];   // HalfTile: 2^E of every weight row of the tile
     // ready[8], done[8], accum, raw_full[4], raw_empty[4]
     __shared__ __align__(8) unsigned long long bars[2 * 8 + 1 + 2 * 4];
 
@@ -725,6 +739,32 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             const int gbeg = hp * gh, gend = min(gc, gbeg + gh);
             const size_t rowsrc = (size_t)min(n0 + rr, p.N - 1) * p.G + g_first;
             const unsigned short* zsrc = zr16 ? zr16 : sc16;
+            float down = 1.f;   // HalfTile: 2^-E of this row
+            if (HALF_T) {
+                // largest of 8 |s| and |z| over the row's groups of this split (both threads of the row)
+                const bool sbf = p.scale_dtype == MNQ_BF16;
+                auto mag = [&](uint32_t bits) {
+                    return sbf ? fabsf(__uint_as_float(bits << 16)) : fabsf(__half2float(__ushort_as_half((unsigned short)bits)));
+                };
+                float mx = 0.f;
+                for (int g0 = gbeg; g0 < gend; g0 += TU) {
+                    uint32_t sv[TU], zv[TU];
+#pragma unroll
+                    for (int u = 0; u < TU; ++u) {
+                        const int g = min(g0 + u, gend - 1);
+                        sv[u] = __ldg(sc16 + rowsrc + g);
+                        zv[u] = __ldg(zsrc + rowsrc + g);
+                    }
+#pragma unroll
+                    for (int u = 0; u < TU; ++u) mx = fmaxf(mx, fmaxf(8.f * mag(sv[u]), zr16 ? mag(zv[u]) : 0.f));
+                }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                // E = floor(log2(mx)) from the exponent field (zero, subnormal, inf or nan rows: E = 0)
+                const int ex = static_cast<int>((__float_as_uint(mx) >> 23) & 0xFFu);
+                const int E = (ex == 0 || ex == 255) ? 0 : max(-100, min(100, ex - 127));
+                down = __int_as_float(static_cast<uint32_t>(127 - E) << 23);
+                if (hp == 0) row_up[rr] = __int_as_float(static_cast<uint32_t>(127 + E) << 23);
+            }
             for (int g0 = gbeg; g0 < gend; g0 += TU) {
                 uint32_t sv[TU], zv[TU];
 #pragma unroll
@@ -732,6 +772,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     const int g = min(g0 + u, gend - 1);
                     sv[u] = __ldg(sc16 + rowsrc + g);
                     zv[u] = __ldg(zsrc + rowsrc + g);
+                }
+                if (HALF_T) {   // to fp16 bits, divided by the row's power of two (exact unless the result is subnormal)
+                    const bool sbf = p.scale_dtype == MNQ_BF16;
+#pragma unroll
+                    for (int u = 0; u < TU; ++u) {
+                        const float sf = sbf ? __uint_as_float(sv[u] << 16) : __half2float(__ushort_as_half((unsigned short)sv[u]));
+                        const float zf = sbf ? __uint_as_float(zv[u] << 16) : __half2float(__ushort_as_half((unsigned short)zv[u]));
+                        sv[u] = __half_as_ushort(__float2half_rn(sf * down));
+                        zv[u] = __half_as_ushort(__float2half_rn(zf * down));
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < TU; ++u)
@@ -801,7 +851,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     }
                 } else if constexpr (TA) {
                     // this thread's row of the tile: 32 columns of its tensor-memory lane, 8 at a time
-                    using Chunk = TileChunk<QUANT, typename std::conditional<RAW, RawInt, T>::type>;
+                    using Chunk = TileChunk<QUANT, TileT>;
                     const uint32_t a_t = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.tmem_a_col + s * 32);
 #pragma unroll
                     for (int c = 0; c < 8; c += 2) {
@@ -814,7 +864,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 } else {
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
-                        using Chunk = TileChunk<QUANT, typename std::conditional<RAW, RawInt, T>::type>;
+                        using Chunk = TileChunk<QUANT, TileT>;
                         const uint4 o = Chunk::run(&w[c * Chunk::WORDS], s2, nz2);
                         sts128(a_row + xoff[c], o);
                     }
@@ -854,6 +904,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             float scale = 1.f, zterm = 0.f;
             if (p.epilogue_scale) scale = widen16(p.scales, sc_row, p.scale_dtype);
             const float* tscale = nullptr;
+            if (HALF_T) {   // the tile was built from scales and zeros divided by the row's 2^E
+                scale = row_up[row];
+                tscale = p.tok_scale;
+            }
             if (RAW) {
                 const float s_n = scale;
                 scale = s_n * 16777216.f;
@@ -1027,6 +1081,7 @@ struct GemmPlan {
     int occ2;       // 1: planned for two CTAs per SM (at most half the shared memory, <= 256 tensor-memory columns)
     int tiles_n;    // CTAs along N (even when pair)
     int raw;        // 1: raw-integer tiles (int8, one scale per row): activations prepared in the workspace first
+    int half;       // 1: bf16 activations through fp16 tiles (HalfTile): activations prepared in the workspace first
     int ta;         // 1: weight tiles in tensor memory, from column tmem_a_col on
     int tmem_a_col;
     size_t smem;
@@ -1135,6 +1190,12 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
                (a.act_dtype == MNQ_BF16 || a.scale_dtype == MNQ_FP16 || a.scale_dtype == MNQ_BF16);
     // bf16 activations otherwise: integer tile when one scale per row and no zeros, else two bf16 tiles per k-block
     bool split_tiles = !raw && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    // ... or, if the caller opted in (MNQ_OPT_BF16_FP16_TILES) and the workspace can hold an fp16 copy of the
+    // activations, one fp16 tile (HalfTile; variant 8 forbids it); checked again once the K split is known
+    bool half_tiles = split_tiles && option_value(MNQ_OPT_BF16_FP16_TILES) != 0 && !(tuning && tuning->gemv_variant == 8) &&
+                      a.workspace &&
+                      a.workspace_bytes >= raw_region_offset(1, a.M, a.N) + raw_region_bytes(a.M, a.K, true);
+    if (half_tiles) split_tiles = false;
     size_t a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
     GemmPlan pl{};
     if (!tile_plan(a.M, a.N, tuning ? tuning->gemv_variant : 0, &pl)) return false;
@@ -1167,7 +1228,15 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
         split_tiles = a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
         a_stage = split_tiles ? 2 * A_BYTES : A_BYTES;
     }
+    if (half_tiles && raw_region_offset(pl.splits, a.M, a.N) + raw_region_bytes(a.M, a.K, true) > a.workspace_bytes) {
+        // the K split's planes left no room for the fp16 copy: two bf16 tiles per k-block after all
+        half_tiles = false;
+        split_tiles = true;
+        a_stage = 2 * A_BYTES;
+        want_occ2 = 0;
+    }
     pl.raw = raw ? 1 : 0;
+    pl.half = half_tiles ? 1 : 0;
     pl.table_groups = a.group_size >= a.K
                           ? 1
                           : static_cast<int>((static_cast<int64_t>(pl.kb_per_split) * BK + a.group_size - 1) / a.group_size + 1);
@@ -1354,8 +1423,10 @@ bool gemm_supported(const MatmulArgs& a)
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant)
 {
     const size_t base = gemm_split_workspace_bytes(M, N, K, group_size);
-    if (M < 1 || N < 1 || K < BK || K % BK || !raw_applicable(M, K, group_size, quant)) return base;
-    // room for the prepared activations (sized for bf16 ones, which need the fp16 copy)
+    if (M < 1 || N < 1 || K < BK || K % BK) return base;
+    // room for the prepared activations (raw-integer tiles; fp16 tiles for bf16 activations if the caller opted
+    // in): per-token factor and sum and, sized for bf16 activations, their fp16 copy
+    if (!raw_applicable(M, K, group_size, quant) && option_value(MNQ_OPT_BF16_FP16_TILES) == 0) return base;
     const int splits = base > kCounterBytes ? static_cast<int>((base - kCounterBytes) / (static_cast<size_t>(M) * N * 4)) : 1;
     return raw_region_offset(splits, M, N) + raw_region_bytes(M, K, true);
 }
@@ -1394,8 +1465,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.tok = pl.tok; p.tokh = pl.tokh; p.nh = pl.nh; p.stages = pl.stages; p.b_stages = pl.b_stages;
     p.raw_stages = pl.raw_stages; p.raw_segs = pl.raw_segs; p.commit_every = pl.commit_every; p.table_groups = pl.table_groups; p.tmem_cols = pl.tmem_cols;
     p.tmem_a_col = pl.tmem_a_col;
-    const bool split_tiles = !pl.raw && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
-    p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles) ? 1 : 0;
+    const bool split_tiles = !pl.raw && !pl.half && a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr);
+    p.epilogue_scale = (a.act_dtype == MNQ_BF16 && !split_tiles && !pl.half) ? 1 : 0;
     p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
     p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0) |
                   ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 4 == 0) ? 4 : 0);
@@ -1405,11 +1476,12 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
     }
 
-    // raw-integer tiles: per-token factors and sums (and the fp16 copy of bf16 activations) first
+    // raw-integer tiles, fp16 tiles for bf16 activations: per-token factors and sums (and the fp16 copy of bf16
+    // activations) first
     const void* x_for_tiles = a.x;
     int64_t lda_tiles = a.lda;
     bool x_is_bf16 = a.act_dtype == MNQ_BF16;
-    if (pl.raw) {
+    if (pl.raw || pl.half) {
         unsigned char* region = static_cast<unsigned char*>(a.workspace) + raw_region_offset(pl.splits, a.M, a.N);
         float* tok_scale = reinterpret_cast<float*>(region);
         float* tok_sum = tok_scale + a.M;
@@ -1433,8 +1505,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
         if (rcp) return rcp;
         p.tok_scale = tok_scale;
         p.tok_sum = tok_sum;
-        p.offset_term = 1;
-        p.epilogue_scale = 1;
+        p.offset_term = pl.raw ? 1 : 0;
+        p.epilogue_scale = pl.raw ? 1 : 0;
         if (x_is_bf16) { x_for_tiles = x16; lda_tiles = a.K; x_is_bf16 = false; }
     }
     // activations as a [M, K] tensor of 16-bit elements; box = 64 k x the tokens one CTA loads, 128-byte swizzle
@@ -1459,6 +1531,10 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     if (pl.raw) {   // int8 only (plan_gemm)
         if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
         return launch_gemm_one<MNQ_INT8, __nv_bfloat16, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+    }
+    if (pl.half) {   // bf16 activations only (plan_gemm)
+        if (a.quant == MNQ_INT4) return launch_gemm_one<MNQ_INT4, __nv_bfloat16, HalfTile>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
+        return launch_gemm_one<MNQ_INT8, __nv_bfloat16, HalfTile>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);
     }
     if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT4, __half, __half>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);

@@ -185,7 +185,7 @@ def release_workspaces(device=None) -> None:
             del _workspaces[key]
 
 
-OPTIONS = {"weights_immutable": 0, "peer_wait_polls": 1, "gemv_max_m": 2}   # mnq_option of include/mnq.h
+OPTIONS = {"weights_immutable": 0, "peer_wait_polls": 1, "gemv_max_m": 2, "bf16_fp16_tiles": 3}   # mnq_option of include/mnq.h
 
 
 def set_option(name: str, value) -> None:
@@ -197,10 +197,14 @@ def set_option(name: str, value) -> None:
     ``peer_wait_polls``    how long a sharded call waits for another rank before it gives up;
     ``gemv_max_m``         largest M that takes the decode kernels (1..32), or 0, the default, to
                            have it chosen per problem; the environment variable
-                           METAL_NATIVE_GEMV_MAX_M sets the initial value."""
+                           METAL_NATIVE_GEMV_MAX_M sets the initial value;
+    ``bf16_fp16_tiles``    bf16 activations with group-wise scales above the decode threshold use one fp16
+                           weight tile per k-block instead of two bf16 tiles: about twice as fast up to 128
+                           tokens, weights rounded to 11 significant bits instead of 16."""
     if name not in OPTIONS:
         raise _invalid(f"set_option: unknown option {name!r}")
     _check(_lib.mnq_set_option(OPTIONS[name], int(value)))
+    _replay.clear()   # remembered calls carry the workspace size the old setting asked for
 
 
 def get_option(name: str) -> int:

@@ -280,3 +280,55 @@ def test_weight_tiles_in_tensor_memory_match_shared_memory_tiles(mn, quant, M, N
         H.assert_close_to_oracle(a, ref, f"tensor-memory tiles {quant} {M}x{N}x{K} split {split}")
         H.assert_close_to_oracle(b, ref, f"shared-memory tiles {quant} {M}x{N}x{K} split {split}")
         assert torch.equal(a, b), "the two tile paths differ"
+
+
+@pytest.mark.parametrize("quant,M,N,K,g,asym,sdt", [
+    ("int4", 64, 384, 1024, 128, True, torch.bfloat16),
+    ("int4", 200, 272, 4096, 128, False, torch.bfloat16),     # two accumulators, no zeros
+    ("int4", 512, 512, 640, 128, True, torch.bfloat16),       # CTA pairs
+    ("int8", 96, 128, 512, 64, True, torch.float16),          # int8 group-wise, fp16 scales
+    ("int8", 300, 256, 2048, 2048, True, torch.bfloat16),     # one scale per row with zeros, more tokens than raw-integer tiles take
+])
+def test_bf16_activations_through_fp16_tiles_when_opted_in(mn, quant, M, N, K, g, asym, sdt):
+    """MNQ_OPT_BF16_FP16_TILES: one fp16 weight tile per k-block for bf16 activations.  The result meets
+    the north-star gate in the fp32 output mode (rel-L2 <= 1e-3, max-abs <= 2e-2) and the bf16 rounding
+    floor in rel-L2; element-wise it carries the fp16 tile's rounding noise, about 2.8e-4 of the output
+    RMS per element (the default two-tile path is held to one bf16 ulp + 1e-4 RMS).  Scales and zeros far outside fp16's range (2^30 and
+    2^-30 times the usual) are normalised per row, so they change nothing."""
+    import numpy as np
+    import mnq_workloads as workloads
+    C = mn._C
+    for factor in (1.0, 2.0 ** 30, 2.0 ** -30) if sdt == torch.bfloat16 else (1.0,):
+        L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=torch.bfloat16,
+                                 scale_dtype=sdt, asymmetric=asym, seed=M + N + K)
+        if factor != 1.0:
+            L.scales = (L.scales.float() * factor).to(sdt)
+            if L.zeros is not None:
+                L.zeros = (L.zeros.float() * factor).to(sdt)
+        ref = H.oracle_matmul(L)
+        d = L.to("cuda")
+        exact = C.dequant_matmul(*d.args(), tuning=_gemm_tuning(mn))
+        try:
+            C.set_option("bf16_fp16_tiles", 1)
+            fast = C.dequant_matmul(*d.args(), tuning=_gemm_tuning(mn))
+            fast32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32) if M > 32 else None
+            again = C.dequant_matmul(*d.args(), tuning=_gemm_tuning(mn))
+            forced = _gemm_tuning(mn)
+            forced.gemv_variant = 8
+            two_tiles = C.dequant_matmul(*d.args(), tuning=forced)
+        finally:
+            C.set_option("bf16_fp16_tiles", 0)
+        C.synchronize()
+        assert C.device_status() == 0
+        H.assert_close_to_oracle(exact, ref, f"two tiles {quant} {M}x{N}x{K} x{factor:g}")
+        assert torch.equal(two_tiles, exact), "variant 8 must keep the two-tile path"
+        assert torch.equal(fast, again), "not deterministic"
+        if fast32 is not None and factor == 1.0:   # (the gate's max-abs is absolute: unscaled outputs only)
+            H.assert_fp32_gate(fast32, ref, f"fp16 tiles, fp32 output {quant} {M}x{N}x{K}")
+        got = fast.float().cpu().numpy()
+        rel, _ = H.errors(got, ref)
+        rel0, _ = H.errors(torch.from_numpy(ref).to(torch.bfloat16).float().numpy(), ref)
+        assert rel <= rel0 * 1.05 + 1e-6, f"rel-L2 {rel:.3e} vs bf16 rounding floor {rel0:.3e}"
+        rms = float(np.sqrt((ref.astype(np.float64) ** 2).mean()))
+        bound = np.abs(ref) * 2.0 ** -7 + 1.5e-3 * rms   # one bf16 ulp + five sigma of the tile noise
+        assert np.all(np.abs(got - ref) <= bound), f"element error {float(np.max(np.abs(got - ref) / bound)):.2f}x the bound"
