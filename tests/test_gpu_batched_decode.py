@@ -118,3 +118,31 @@ def test_batched_decode_strided_activations_and_bf16_range(mn):
     assert C.device_status() == 0
     for m in range(M):   # per token: the tokens' magnitudes differ too much for one norm
         H.assert_close_to_oracle(out[m:m + 1], ref[m:m + 1], f"token {m}")
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 2048), (24, 528, 14336)])
+def test_batched_decode_step_replayed_from_a_cuda_graph(mn, M, N, K):
+    """A batched-decode call is two or three launches (activation image, kernel, K-cut reduction);
+    recorded into a CUDA graph through PhasePipeline and replayed with new activations in the same
+    buffer, it must give the eager result every time."""
+    import mnq_workloads as workloads
+    C = mn._C
+    L = workloads.make_layer("t", M, K, N, act_dtype=torch.bfloat16, scale_dtype=torch.bfloat16, seed=M + N)
+    d = L.to("cuda")
+    out = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    pipe = mn.PhasePipeline()
+    pipe.set_phase(mn.InferencePhase.Decode)
+    step = pipe.capture_step(lambda: C.dequant_matmul(*d.args(), out=out))
+    for scale in (1.0, 0.5, -3.0):
+        d.x.copy_((L.x.float() * scale).to(torch.bfloat16))
+        want = C.dequant_matmul(*d.args()).clone()
+        out.zero_()
+        step()
+        torch.cuda.synchronize()
+        assert C.device_status() == 0
+        assert torch.equal(out, want), f"graph replay differs from the eager call at scale {scale}"
+    ref = H.oracle_matmul(L)
+    d.x.copy_(L.x)
+    step()
+    torch.cuda.synchronize()
+    H.assert_close_to_oracle(out, ref, f"replayed {M}x{N}x{K}")
