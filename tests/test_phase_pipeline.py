@@ -36,7 +36,7 @@ def test_configurations_and_fallback():
     assert p.active_config() == p.prefill_config()            # Unknown falls back to prefill
     assert p.decode_config().matmul_strategy == "gemv" and p.prefill_config().matmul_strategy == "gemm"
     assert p.prefill_config().gemv_max_m == 0                 # threshold left to the library
-    assert [p.strategy_for(m) for m in (16, 17, 32, 33)] == ["gemv", "auto", "auto", "gemm"]
+    assert [p.strategy_for(m) for m in (24, 25, 32, 33)] == ["gemv", "auto", "auto", "gemm"]
     p.set_decode_config(PhaseConfig("gemv", 16, True))
     p.set_prefill_config(PhaseConfig("gemm", 8, False))
     p.set_phase(InferencePhase.Decode)
@@ -59,7 +59,7 @@ def test_threshold_option_and_environment_override():
     code = ("import sys; sys.path.insert(0, r'%s'); from metal_native import _C; "
             "print(_C.get_option('gemv_max_m'), _C.select_path(12, 4096, 4096, 128, 'int4'), "
             "_C.select_path(4, 4096, 4096, 128, 'int4'), _C.select_path(33, 4096, 4096, 128, 'int4'), "
-            "_C.select_path(20, 4096, 4096, 4096, 'int8'))" % (ROOT / "metal-native_b200"))
+            "_C.select_path(28, 4096, 4096, 4096, 'int8'))" % (ROOT / "metal-native_b200"))
     for env_val, want in ((None, "0 gemv gemv gemm gemm"), ("0", "0 gemv gemv gemm gemm"), ("8", "8 gemm gemv gemm gemm"),
                           ("32", "32 gemv gemv gemm gemv"), ("99", "0 gemv gemv gemm gemm"), ("x", "0 gemv gemv gemm gemm")):
         env = dict(os.environ)
@@ -87,7 +87,7 @@ def test_options_validate_and_round_trip():
     import torch
     sp = _C.select_path
     assert _C.get_option("gemv_max_m") == 0
-    assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (16, 17)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (24, 25)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33)] == ["gemv", "gemm"]
