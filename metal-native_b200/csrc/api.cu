@@ -240,6 +240,13 @@ int choose_path(const MatmulArgs& a)
 {
     const int64_t gemv_max_m = gemv_max_m_for(a.K, a.group_size, a.quant, a.act_dtype);
     if (a.M <= gemv_max_m && gemv_supported(a)) return MNQ_PATH_GEMV;
+    // 33 to 64 tokens of bf16 activations where the tensor-core kernel would need two bf16 tiles per
+    // k-block (group-wise scales, the caller has not opted for fp16 tiles): the batched-decode
+    // kernel with six or eight token tiles is faster (measured: 31-50 against 70 us on the Llama-3-8B
+    // shapes).  Only while the threshold is left to the library.
+    if (a.M > 32 && a.M <= 64 && a.act_dtype == MNQ_BF16 && option_value(MNQ_OPT_GEMV_MAX_M) == 0 &&
+        option_value(MNQ_OPT_BF16_FP16_TILES) == 0 && a.group_size < a.K && gemv_supported(a))
+        return MNQ_PATH_GEMV;
     if (a.M > gemv_max_m && gemm_supported(a)) return MNQ_PATH_GEMM;
     if (a.M <= 32 && gemv_supported(a)) return MNQ_PATH_GEMV;   // e.g. K not a multiple of 64
     return MNQ_PATH_GENERIC;
@@ -293,7 +300,11 @@ int mnq_device_status(uint32_t* status, int32_t clear)
 
 size_t mnq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant_type)
 {
-    if (M > 32) return gemm_workspace_bytes(M, N, K, group_size, quant_type);
+    if (M > 32) {   // (33 to 64 tokens of bf16 activations may take the batched-decode kernel: enough for both)
+        const size_t g = gemm_workspace_bytes(M, N, K, group_size, quant_type);
+        const size_t d = M <= 64 ? gemv_workspace_bytes(M, N, K, group_size, quant_type) : 0;
+        return g > d ? g : d;
+    }
     // 9..32 tokens take either family, depending on MNQ_OPT_GEMV_MAX_M and the dtypes: enough for both
     const size_t a = gemv_workspace_bytes(M, N, K, group_size, quant_type);
     const size_t b = M > 8 ? gemm_workspace_bytes(M, N, K, group_size, quant_type) : 0;

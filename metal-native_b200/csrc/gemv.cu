@@ -522,6 +522,7 @@ int launch_lw(const GemvParams& p, int lw, int nt, dim3 grid, int threads, size_
 
 bool gemv_supported(const MatmulArgs& a)
 {
+    if (a.M > 32) return gemv_mid_supported(a, nullptr);   // 33 to 64 tokens: the batched-decode kernel, bf16 only
     if (gemv_stream_supported(a, nullptr)) return true;
     const int lw = pick_lane_width(a);
     if (!lw) return false;
@@ -531,7 +532,8 @@ bool gemv_supported(const MatmulArgs& a)
 
 size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size, int32_t quant)
 {
-    if (M < 1 || M > 32 || N < 1 || K < 1 || group_size < 1) return 0;
+    if (M > 32) return gemv_mid_workspace_bytes(M, N, K, group_size, quant);   // (0 where that kernel does not apply)
+    if (M < 1 || N < 1 || K < 1 || group_size < 1) return 0;
     // what the streaming kernel's plan asks for; at least room for a 2-way split so that a
     // caller can force one
     bool streaming = false;
@@ -558,6 +560,7 @@ size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size,
 int launch_gemv(const MatmulArgs& a, const mnq_tuning* tuning)
 {
     const int variant = tuning ? tuning->gemv_variant : 0;
+    if (a.M > 32) return launch_gemv_mid_wide(a, tuning);
     if (variant != 1 && gemv_stream_supported(a, tuning)) return launch_gemv_stream(a, tuning);
     if (variant == 2)
         return fail(MNQ_INVALID_ARGUMENT, "dequant_matmul: the streaming GEMV kernel cannot take this problem");

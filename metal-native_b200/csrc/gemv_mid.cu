@@ -1,4 +1,5 @@
-// Decode-shaped fused dequantise + matmul for 5 to 32 tokens (the batched-decode case; replaces,
+// Decode-shaped fused dequantise + matmul for 5 to 32 tokens, and up to 64 for bf16 activations (the
+// batched-decode case; replaces,
 // for those token counts, the reference's tiled kernels dequant_matmul_int{4,8}_fp16,
 // shaders/matmul_dequant_kernel.metal:55-223, 351-479).  Same weight movement and arithmetic as
 // the other decode kernels (gemv_stream.cu, gemv_lean.cu): one TMA tile copy per 16-row x 256-byte
@@ -48,6 +49,10 @@ constexpr int kMidMaxSmem = 226 * 1024;
 // Fewer tokens than this run the compact kernel: preparing the activations costs a launch and a
 // dependency (about 3.5 us), which five tokens' worth of per-CTA staging outweighs (measured).
 constexpr int kMidMinTokens = 5;
+// Above 32 tokens only bf16 activations come here (6 or 8 token tiles): with group-wise scales the
+// tensor-core kernel needs two bf16 tiles per k-block for them, and eight token tiles on the warp MMA
+// are still faster than that (measured on the Llama-3-8B shapes).
+constexpr int kMidMaxTokens = 64;
 constexpr int kPrepThreads = 1024;
 constexpr int kPrepBatch = 4;                           // 8-blocks a thread holds: K <= 8 * 4 * 1024
 
@@ -281,7 +286,7 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 // GROUPED: every step is one quantisation group; otherwise one group per row.
 // NB: row blocks a warp carries through one sweep of K.
 template <int QUANT, typename T, int NT, bool GROUPED, int NB>
-__global__ void __launch_bounds__((NT >= 4 && NB >= 2) ? 256 : 512)
+__global__ void __launch_bounds__((NT >= 5 || (NT >= 4 && NB >= 2)) ? 256 : 512)
 gemv_mid_kernel(const __grid_constant__ MidParams p, const __grid_constant__ CUtensorMap wmap)
 {
     using MT = __half;
@@ -551,7 +556,8 @@ struct MidPlan {
 
 bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspace_bytes, int want_warps, MidPlan* out)
 {
-    if (a.M < kMidMinTokens || a.M > 32 || a.swiglu_h > 0 || a.gather.world > 0) return false;
+    if (a.M < kMidMinTokens || a.M > kMidMaxTokens || a.swiglu_h > 0 || a.gather.world > 0) return false;
+    if (a.M > 32 && a.act_dtype != MNQ_BF16) return false;
     const int step = a.quant == MNQ_INT4 ? 128 : 64;
     const int piece_k = step * kPieceSteps;
     if (a.K < piece_k || a.K % piece_k || a.N < 1 || a.N > (1 << 30) || a.K > 8 * kPrepBatch * kPrepThreads) return false;
@@ -563,10 +569,10 @@ bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspa
     if (reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8 || reinterpret_cast<uintptr_t>(a.wq) % 16) return false;
 
     MidPlan pl{};
-    pl.nt = static_cast<int>((a.M + 7) / 8);   // 1 to 4 token tiles
+    pl.nt = a.M <= 32 ? static_cast<int>((a.M + 7) / 8) : (a.M <= 48 ? 6 : 8);   // 1 to 4 token tiles; 6 or 8 above 32 tokens
     pl.nb = 1;
-    const int max_warps = 16;
-    pl.warps = want_warps;
+    const int max_warps = pl.nt >= 5 ? 8 : 16;   // (six and eight token tiles need about 200 registers per thread)
+    pl.warps = std::min(want_warps, max_warps);
     if (tuning && tuning->warps_per_cta > 0) pl.warps = tuning->warps_per_cta;
     if (pl.warps > max_warps) pl.warps = max_warps;
     // two weight pieces in flight per row block a warp carries keep HBM busy; whatever shared memory
@@ -674,7 +680,7 @@ size_t gemv_mid_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_s
     a.M = M; a.N = N; a.K = K; a.lda = K; a.ldc = N;
     a.group_size = group_size;
     a.G = K > 0 ? static_cast<int32_t>((K + group_size - 1) / group_size) : 0;
-    a.quant = quant; a.act_dtype = MNQ_FP16; a.scale_dtype = MNQ_FP16;
+    a.quant = quant; a.act_dtype = M > 32 ? MNQ_BF16 : MNQ_FP16; a.scale_dtype = MNQ_FP16;
     a.sm_count = 148;
     MidPlan pl;
     if (!plan_mid(a, nullptr, ~size_t(0), &pl)) return 0;
@@ -705,6 +711,11 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
     p.epi = a.epi;
     const bool grouped = a.group_size < a.K;
     int rc;
+#define MNQ_MID_WIDE(Q)                                                                                      \
+    rc = pl.nt == 6 ? (grouped ? launch_mid_one<Q, __nv_bfloat16, 6, true, 1>(p, wmap, pl, a.stream)         \
+                               : launch_mid_one<Q, __nv_bfloat16, 6, false, 1>(p, wmap, pl, a.stream))       \
+                    : (grouped ? launch_mid_one<Q, __nv_bfloat16, 8, true, 1>(p, wmap, pl, a.stream)         \
+                               : launch_mid_one<Q, __nv_bfloat16, 8, false, 1>(p, wmap, pl, a.stream))
 #define MNQ_MID(Q, T)                                                                                        \
     rc = pl.nt == 1 ? (grouped ? launch_mid_one<Q, T, 1, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 1, false, 1>(p, wmap, pl, a.stream))                   \
@@ -714,7 +725,10 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
                                : launch_mid_one<Q, T, 3, false, 1>(p, wmap, pl, a.stream))                   \
                     : (grouped ? launch_mid_one<Q, T, 2, true, 1>(p, wmap, pl, a.stream)                     \
                                : launch_mid_one<Q, T, 2, false, 1>(p, wmap, pl, a.stream))
-    if (a.quant == MNQ_INT4) {
+    if (pl.nt > 4) {   // bf16 only (plan_mid)
+        if (a.quant == MNQ_INT4) MNQ_MID_WIDE(MNQ_INT4);
+        else MNQ_MID_WIDE(MNQ_INT8);
+    } else if (a.quant == MNQ_INT4) {
         if (a.act_dtype == MNQ_FP16) MNQ_MID(MNQ_INT4, __half);
         else MNQ_MID(MNQ_INT4, __nv_bfloat16);
     } else {
@@ -722,8 +736,21 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
         else MNQ_MID(MNQ_INT8, __nv_bfloat16);
     }
 #undef MNQ_MID
+#undef MNQ_MID_WIDE
     if (rc || pl.num_chunks == 1) return rc;
     return launch_splitk_reduce(p.partial, a.out, p.M, p.N, a.ldc, pl.num_chunks, a.act_dtype, a.epi, a.stream);
+}
+
+// More than 32 tokens: the streaming plan (and its tensor map) does not exist, so the weight map is made here.
+int launch_gemv_mid_wide(const MatmulArgs& a, const mnq_tuning* tuning)
+{
+    const int64_t row_bytes = a.quant == MNQ_INT4 ? a.K / 2 : a.K;
+    CUtensorMap wmap;
+    const int rc = encode_tensor_map_2d(&wmap, a.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(row_bytes) / 4,
+                                        static_cast<uint64_t>(a.N), static_cast<uint64_t>(row_bytes), kPieceBytes / 4, 16,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    return launch_gemv_mid(a, tuning, wmap);
 }
 
 int read_mid_status(unsigned int* out, bool clear)

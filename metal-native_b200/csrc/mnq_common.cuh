@@ -313,6 +313,7 @@ size_t gemv_mid_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_s
 #ifdef CUDA_VERSION
 int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtensorMap& wmap);
 #endif
+int launch_gemv_mid_wide(const MatmulArgs& a, const mnq_tuning* tuning);   // 33 to 64 tokens, bf16 activations
 int read_mid_status(unsigned int* out, bool clear);
 int launch_generic(const MatmulArgs& a);
 bool gemv_supported(const MatmulArgs& a);

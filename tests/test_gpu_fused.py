@@ -117,8 +117,8 @@ def test_residual_may_alias_a_strided_view_and_zero_K(mn):
 @pytest.mark.parametrize("M", [8, 24, 64])
 def test_select_path_names_the_kernel_that_runs(mn, adt, sdt, M):
     """For every activation / scale dtype pair the host-side answer is the family dispatch takes:
-    forcing that family succeeds, and where the answer is not the tensor-core kernel, forcing the
-    tensor-core kernel is refused (it is never silently replaced)."""
+    forcing that family succeeds, and where the tensor-core kernel cannot take the problem (the answer
+    is the any-shape kernel), forcing it is refused (it is never silently replaced)."""
     import mnq_workloads as workloads
     C = mn._C
     L = workloads.make_layer("t", M, 1024, 256, act_dtype=adt, scale_dtype=sdt, asymmetric=True, seed=M)
@@ -131,7 +131,7 @@ def test_select_path_names_the_kernel_that_runs(mn, adt, sdt, M):
     out = C.dequant_matmul(*d.args(), tuning=t)
     assert torch.equal(out, C.dequant_matmul(*d.args())), f"auto dispatch is not the '{said}' kernel"
     H.assert_close_to_oracle(out, ref, f"{said} {adt} {sdt}")
-    if M > 32 and said != "gemm":
+    if M > 32 and said == "generic":
         t.path = C.PATH_GEMM
         with pytest.raises(C.MetalNativeError, match="InvalidArgument"):
             C.dequant_matmul(*d.args(), tuning=t)

@@ -36,7 +36,7 @@ def test_configurations_and_fallback():
     assert p.active_config() == p.prefill_config()            # Unknown falls back to prefill
     assert p.decode_config().matmul_strategy == "gemv" and p.prefill_config().matmul_strategy == "gemm"
     assert p.prefill_config().gemv_max_m == 0                 # threshold left to the library
-    assert [p.strategy_for(m) for m in (24, 25, 32, 33)] == ["gemv", "auto", "auto", "gemm"]
+    assert [p.strategy_for(m) for m in (24, 25, 64, 65)] == ["gemv", "auto", "auto", "gemm"]
     p.set_decode_config(PhaseConfig("gemv", 16, True))
     p.set_prefill_config(PhaseConfig("gemm", 8, False))
     p.set_phase(InferencePhase.Decode)
@@ -90,8 +90,9 @@ def test_options_validate_and_round_trip():
     assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (24, 25)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
-    assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33, 64, 65)] == ["gemv", "gemv", "gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 4096, "int4", torch.bfloat16) for m in (32, 33)] == ["gemv", "gemm"]   # one scale per row, no zeros: integer tiles
     # fp16 activations with bf16 scales above the decode threshold: the any-shape kernel, and it says so
     assert _C.select_path(64, 4096, 4096, 128, "int4", torch.float16, scale_dtype=torch.bfloat16) == "generic"
     assert _C.select_path(64, 4096, 4096, 128, "int4", torch.float16, scale_dtype=torch.float16) == "gemm"
-    assert _C.select_path(64, 4096, 4096, 128, "int4", torch.bfloat16, scale_dtype=torch.float16) == "gemm"
+    assert _C.select_path(65, 4096, 4096, 128, "int4", torch.bfloat16, scale_dtype=torch.float16) == "gemm"
