@@ -49,7 +49,7 @@ constexpr int kMidMaxSmem = 226 * 1024;
 // Fewer tokens than this run the compact kernel: preparing the activations costs a launch and a
 // dependency (about 3.5 us), which five tokens' worth of per-CTA staging outweighs (measured).
 constexpr int kMidMinTokens = 5;
-// Above 32 tokens only bf16 activations come here (6 or 8 token tiles): with group-wise scales the
+// Above 32 tokens only bf16 activations come here (5 to 8 token tiles): with group-wise scales the
 // tensor-core kernel needs two bf16 tiles per k-block for them, and eight token tiles on the warp MMA
 // are still faster than that (measured on the Llama-3-8B shapes).
 constexpr int kMidMaxTokens = 64;
@@ -569,7 +569,7 @@ bool plan_mid_with(const MatmulArgs& a, const mnq_tuning* tuning, size_t workspa
     if (reinterpret_cast<uintptr_t>(a.x) % 16 || a.lda % 8 || reinterpret_cast<uintptr_t>(a.wq) % 16) return false;
 
     MidPlan pl{};
-    pl.nt = a.M <= 32 ? static_cast<int>((a.M + 7) / 8) : (a.M <= 48 ? 6 : 8);   // 1 to 4 token tiles; 6 or 8 above 32 tokens
+    pl.nt = static_cast<int>((a.M + 7) / 8);   // 1 to 8 token tiles (5 to 8: bf16 activations only)
     pl.nb = 1;
     const int max_warps = pl.nt >= 5 ? 8 : 16;   // (six and eight token tiles need about 200 registers per thread)
     pl.warps = std::min(want_warps, max_warps);
@@ -712,8 +712,12 @@ int launch_gemv_mid(const MatmulArgs& a, const mnq_tuning* tuning, const CUtenso
     const bool grouped = a.group_size < a.K;
     int rc;
 #define MNQ_MID_WIDE(Q)                                                                                      \
-    rc = pl.nt == 6 ? (grouped ? launch_mid_one<Q, __nv_bfloat16, 6, true, 1>(p, wmap, pl, a.stream)         \
+    rc = pl.nt == 5 ? (grouped ? launch_mid_one<Q, __nv_bfloat16, 5, true, 1>(p, wmap, pl, a.stream)         \
+                               : launch_mid_one<Q, __nv_bfloat16, 5, false, 1>(p, wmap, pl, a.stream))       \
+       : pl.nt == 6 ? (grouped ? launch_mid_one<Q, __nv_bfloat16, 6, true, 1>(p, wmap, pl, a.stream)         \
                                : launch_mid_one<Q, __nv_bfloat16, 6, false, 1>(p, wmap, pl, a.stream))       \
+       : pl.nt == 7 ? (grouped ? launch_mid_one<Q, __nv_bfloat16, 7, true, 1>(p, wmap, pl, a.stream)         \
+                               : launch_mid_one<Q, __nv_bfloat16, 7, false, 1>(p, wmap, pl, a.stream))       \
                     : (grouped ? launch_mid_one<Q, __nv_bfloat16, 8, true, 1>(p, wmap, pl, a.stream)         \
                                : launch_mid_one<Q, __nv_bfloat16, 8, false, 1>(p, wmap, pl, a.stream))
 #define MNQ_MID(Q, T)                                                                                        \
