@@ -849,8 +849,9 @@ bool plan_stream_at(const MatmulArgs& a, const mnq_tuning* tuning, size_t worksp
             } else {
                 const int64_t passes = (row_blocks * c + slots - 1) / slots;
                 // cutting K at all costs the planes, a fence, an atomic and the last arriver's reads, about as
-                // long as 12 steps take (Llama-3-8B gate/up, 896 row blocks: 10.8 us uncut, 11.6 us cut in two)
-                cost = static_cast<double>(passes) * (spc + 8) + (c > 1 ? 12.0 + 0.25 * c : 0.0);
+                // long as 20 steps take (Llama-3-8B gate/up, 896 row blocks and 32 steps: 10.8 us uncut, 11.6 us
+                // cut in two)
+                cost = static_cast<double>(passes) * (spc + 8) + (c > 1 ? 20.0 + 0.25 * c : 0.0);
             }
             if (cost < best_cost - 1e-9) { best_cost = cost; chunks = c; }
         }
