@@ -77,7 +77,7 @@ struct GemmParams {
     int stages;         // weight-tile (A) ring
     int b_stages;       // activation-tile (B) ring
     int tmem_cols;      // power of two >= max(32, tok)
-    int tmem_a_col;     // weight tiles in tensor memory (TA kernels): first column of their ring, 32 columns per slot
+    int tmem_a_col;     // weight tiles in tensor memory (TA kernels): first column of their ring, 32 columns per slot (64 with two tiles per k-block)
     int epilogue_scale; // 1: tile holds integers, scale applied to the accumulator
     int raw_stages;     // stages of the packed-weight ring
     int raw_segs;       // 128-byte-wide boxes per stage (consecutive along k)
@@ -526,9 +526,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, int quad, int 
 // OCC2: tiles of at most 256 tokens leave half of the SM's shared memory, tensor memory and
 // registers unused, and a CTA of this kernel spends most of its time waiting (on loads, on the
 // MMA, on its own barriers): two CTAs per SM, each planned for half the shared memory.
-// TA (tiles of at most 128 tokens, single CTAs, one tile per k-block): the dequantise warps write the
-// weight tile into TENSOR memory (tcgen05.st, a thread's row of 64 values = 32 columns of its lane) and
-// the MMA takes its A operand from there.  A 128 x 64 tile then never passes through shared memory
+// TA (tiles of at most 128 tokens, single CTAs): the dequantise warps write the weight tile into
+// TENSOR memory (tcgen05.st, a thread's row of 64 values = 32 columns of its lane; the two tiles of
+// BSplit side by side in a 64-column slot) and the MMA takes its A operand from there.  A 128 x 64 tile then never passes through shared memory
 // (16 KB written and 16 KB read per k-block otherwise, most of the shared-memory traffic of a CTA that
 // multiplies few tokens, which is what bounds such a CTA), and its ring lives in the tensor-memory
 // columns the accumulator leaves free.
@@ -548,7 +548,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr bool MMA_BF16 = IS_BF16 && !RAW && !HALF_T;
     using TileT = typename std::conditional<RAW, RawInt, typename std::conditional<HALF_T, __half, T>::type>::type;
     constexpr int A_STAGE = TA ? 0 : (SPLIT ? 2 * A_BYTES : A_BYTES);   // shared-memory bytes of one weight-ring slot
-    static_assert(!TA || (!PAIR && !SPLIT), "weight tiles in tensor memory: single CTAs, one tile per k-block");
+    static_assert(!TA || !PAIR, "weight tiles in tensor memory: single CTAs");
+    constexpr int A_COLS = SPLIT ? 64 : 32;   // tensor-memory columns of one weight-ring slot (TA): the high halves, then the low ones
 
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t tmem_base_slot;
@@ -684,11 +685,12 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     const uint32_t acc = tmem_base + (uint32_t)(h * p.tokh);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {   // 32 bytes along k = 2 descriptor address units
-                        if (TA) umma_ta(acc, tmem_base + (uint32_t)(p.tmem_a_col + s * 32 + 8 * j), bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if (TA) umma_ta(acc, tmem_base + (uint32_t)(p.tmem_a_col + s * A_COLS + 8 * j), bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         else if (PAIR) umma_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         else umma(acc, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                         if (SPLIT) {   // the low halves of the weights, same activations, same accumulator
-                            if (PAIR) umma_pair(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
+                            if (TA) umma_ta(acc, tmem_base + (uint32_t)(p.tmem_a_col + s * A_COLS + 32 + 8 * j), bdesc + 2 * j, idesc, 1u);
+                            else if (PAIR) umma_pair(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
                             else umma(acc, adesc_lo + 2 * j, bdesc + 2 * j, idesc, 1u);
                         }
                     }
@@ -842,17 +844,32 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                         s32 = __half2float(__ushort_as_half((unsigned short)(sz & 0xFFFFu)));
                         nz32 = -__half2float(__ushort_as_half((unsigned short)(sz >> 16)));
                     }
+                    if constexpr (TA) {
+                        // this thread's row of both tiles: 32 + 32 columns of its tensor-memory lane
+                        const uint32_t a_t = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.tmem_a_col + s * A_COLS);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint4 hi, lo;
-                        split_chunk<QUANT>(&w[c * SplitChunk<QUANT>::WORDS], s32, nz32, hi, lo);
-                        sts128(a_row + xoff[c], hi);
-                        sts128(a_row + A_BYTES + xoff[c], lo);
+                        for (int c = 0; c < 8; c += 2) {
+                            uint4 hi0, lo0, hi1, lo1;
+                            split_chunk<QUANT>(&w[c * SplitChunk<QUANT>::WORDS], s32, nz32, hi0, lo0);
+                            split_chunk<QUANT>(&w[(c + 1) * SplitChunk<QUANT>::WORDS], s32, nz32, hi1, lo1);
+                            tmem_st8(a_t + 4 * c, hi0, hi1);
+                            tmem_st8(a_t + 32 + 4 * c, lo0, lo1);
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            uint4 hi, lo;
+                            split_chunk<QUANT>(&w[c * SplitChunk<QUANT>::WORDS], s32, nz32, hi, lo);
+                            sts128(a_row + xoff[c], hi);
+                            sts128(a_row + A_BYTES + xoff[c], lo);
+                        }
                     }
                 } else if constexpr (TA) {
                     // this thread's row of the tile: 32 columns of its tensor-memory lane, 8 at a time
                     using Chunk = TileChunk<QUANT, TileT>;
-                    const uint32_t a_t = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.tmem_a_col + s * 32);
+                    const uint32_t a_t = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.tmem_a_col + s * A_COLS);
 #pragma unroll
                     for (int c = 0; c < 8; c += 2) {
                         const uint4 o0 = Chunk::run(&w[c * Chunk::WORDS], s2, nz2);
@@ -1247,13 +1264,15 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     pl.raw_segs = 1;
     const size_t epilogue_min = 1024 + 2 * 64 * BN * 4;   // the epilogue stages two 64-token slabs of fp32
     // weight tiles in tensor memory (see the kernel): tiles of at most 128 tokens (variant 6 forbids it)
-    const bool ta_ok = !pl.pair && !split_tiles && pl.nh == 1 && pl.tok <= 128 && !(tuning && tuning->gemv_variant == 6);
+    // (two bf16 tiles per k-block take a 64-column slot)
+    const bool ta_ok = !pl.pair && pl.nh == 1 && pl.tok <= 128 && !(tuning && tuning->gemv_variant == 6);
+    const int slot_cols = split_tiles ? 64 : 32;
     const int accum_cols = pl.tmem_cols;
     auto size_rings = [&](size_t total, int tmem_budget) -> bool {
         size_t ring = 0, budget = 0;
         int bst = 0;
         if (ta_ok) {
-            int slots = (tmem_budget - accum_cols) / 32;
+            int slots = (tmem_budget - accum_cols) / slot_cols;
             if (slots > 8) slots = 8;
             pl.raw_stages = 3;
             ring = static_cast<size_t>(pl.raw_stages) * pl.raw_segs * BN * 128 + static_cast<size_t>(pl.table_groups) * BN * 4;
@@ -1333,6 +1352,8 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
     if constexpr (!std::is_same<TT, BSplit>::value) {
         if (occ2 && !pair) kern = &gemm_tcgen05_kernel<QUANT, T, TT, false, true>;
         if (ta && !pair) kern = occ2 ? &gemm_tcgen05_kernel<QUANT, T, TT, false, true, true> : &gemm_tcgen05_kernel<QUANT, T, TT, false, false, true>;
+    } else {
+        if (ta && !pair) kern = &gemm_tcgen05_kernel<QUANT, T, TT, false, false, true>;
     }
     // per kernel of this instantiation: CTA pairs, single CTAs, two CTAs per SM, and the two with weight tiles in tensor memory
     static std::atomic<uint64_t> attr_set[5];

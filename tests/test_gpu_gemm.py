@@ -257,6 +257,8 @@ def test_config4_m64_int8_bf16_full_size(mn):
     ("int4", 40, 256, 2048, 2048, torch.bfloat16),    # bf16, one scale per row, no zeros: integer tiles
     ("int8", 96, 272, 2048, 2048, torch.bfloat16),    # raw-integer tiles
     ("int8", 33, 128, 512, 64, torch.float16),        # int8 group-wise
+    ("int4", 100, 400, 4096, 128, torch.bfloat16),    # bf16 group-wise: two tiles per k-block, 64-column slots
+    ("int8", 128, 256, 1024, 64, torch.bfloat16),
 ])
 def test_weight_tiles_in_tensor_memory_match_shared_memory_tiles(mn, quant, M, N, K, g, adt):
     """Tiles of at most 128 tokens keep the dequantised weight tile in tensor memory (the default);
