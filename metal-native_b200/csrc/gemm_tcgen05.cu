@@ -671,15 +671,24 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
-        if (lane == 0 && rank == 0) {
+        // The whole warp walks the k-blocks (uniform control flow and operand addresses) and one
+        // elected lane issues: with the loop inside an `if (lane == 0)` every tcgen05.mma cost the
+        // issuing thread about 47 cycles of its own (measured on static operands), ten times what
+        // it costs from convergent code, and at few tokens that thread sets the pace.
+        if (rank == 0) {
+            uint32_t elected;
+            asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
             const uint32_t idesc = instr_desc(p.tokh, MMA_BF16, PAIR ? 2 * BN : BN);
             int s = 0, sb = 0, d = 0; uint32_t dph = 0;
             int hp = 0;                             // pair barrier of this k-block
             for (int kb = 0; kb < num_kb; ++kb) {   // kb: position in this CTA's k order
-                if (!(PAIR ? bar_wait_cluster(ready0 + 8 * d, dph) : bar_wait(ready0 + 8 * d, dph))) { failed = true; break; }
+                const bool landed = PAIR ? bar_wait_cluster(ready0 + 8 * d, dph) : bar_wait(ready0 + 8 * d, dph);
+                if (!__all_sync(0xffffffffu, landed)) { failed = true; break; }   // the lanes leave together
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t adesc = smem_desc_sw128(tiles + s * A_STAGE);
                 const uint64_t adesc_lo = smem_desc_sw128(tiles + s * A_STAGE + A_BYTES);   // SPLIT only
+                const bool commit_now = CE == 1 || (kb & 1) || kb == num_kb - 1;
+                if (elected) {
                 for (int h = 0; h < p.nh; ++h) {
                     const uint64_t bdesc = smem_desc_sw128(btiles + (uint32_t)(sb * p.nh + h) * (uint32_t)b_bytes);
                     const uint32_t acc = tmem_base + (uint32_t)(h * p.tokh);
@@ -696,17 +705,22 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     }
                 }
                 // operands of this k-block are free once these MMAs have read them
-                if (CE == 1 || (kb & 1) || kb == num_kb - 1) {
+                if (commit_now) {
                     if (PAIR) umma_commit_pair(done0 + 8 * hp);
                     else umma_commit(done0 + 8 * hp);
-                    if (++hp == H) hp = 0;
                 }
+                }
+                __syncwarp();
+                if (commit_now && ++hp == H) hp = 0;
                 if (++s == S) s = 0;
                 if (++sb == SB) sb = 0;
                 if (++d == D) { d = 0; dph ^= 1u; }
             }
-            if (PAIR) umma_commit_pair(accum);   // accumulators complete, in both CTAs
-            else umma_commit(accum);
+            if (elected) {
+                if (PAIR) umma_commit_pair(accum);   // accumulators complete, in both CTAs
+                else umma_commit(accum);
+            }
+            __syncwarp();
         }
     } else {
         // ---------------- dequantise weight tiles, then epilogue ----------------
