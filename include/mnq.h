@@ -88,7 +88,7 @@ typedef enum mnq_option {
     MNQ_OPT_PEER_WAIT_POLLS = 1,
     /* Largest token count M that takes the decode (GEMV) kernels; above it the tensor-core
      * kernel runs.  0..32, initialised from the environment variable METAL_NATIVE_GEMV_MAX_M
-     * when set.  Default 0: chosen per problem from B200 measurements (24 for int8 weights with
+     * when set.  Default 0: chosen per problem from B200 measurements (16 for int8 weights with
      * one scale per row, 32 for every other format; bf16 activations with group-wise scales stay on
      * the decode kernels up to 64 tokens).  The
      * reference's counterpart is the fixed `use_vecmat = (M <= 8)` (src/ops/matmul.mm:946). */

@@ -224,13 +224,13 @@ void fill_args(MatmulArgs& a, const void* x, const void* wq, const void* scales,
 // cycles and SM sub-partition) bounds them from about 16 tokens on; the tensor-core kernel's cost is
 // flat up to 128 tokens but it has to expand every weight to 16 bits in shared memory.  int8 weights
 // with one scale per row run raw-integer tiles there, which overtake the decode kernels once those need
-// four token tiles (25 tokens); for every other format the decode kernels stay ahead up to their limit of 32.
+// three token tiles (17 tokens); for every other format the decode kernels stay ahead up to their limit of 32.
 int64_t gemv_max_m_for(int64_t K, int32_t group_size, int32_t quant, int32_t act_dtype)
 {
     (void)act_dtype;
     const int64_t set = option_value(MNQ_OPT_GEMV_MAX_M);
     if (set > 0) return set;
-    if (quant == MNQ_INT8 && group_size >= K) return 24;
+    if (quant == MNQ_INT8 && group_size >= K) return 16;
     return 32;
 }
 

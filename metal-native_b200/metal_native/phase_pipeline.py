@@ -35,7 +35,7 @@ class PhaseConfig:
     ``matmul_strategy``  ``"gemv"`` (the reference's "vecmat"), ``"gemm"`` (its "tiled64") or
                          ``"auto"``: advisory, as in the reference;
     ``gemv_max_m``       largest M that takes the decode kernels while this phase is active
-                         (1..32), or 0 to let the library choose per problem (24 or 32 by
+                         (1..32), or 0 to let the library choose per problem (16 or 32 by
                          weight format; up to 64 for bf16 activations with group-wise scales);
     ``capture_graph``    replay the step from a CUDA graph (the counterpart of the reference's
                          ``encoder_max_ops`` / ``auto_flush_threshold`` command batching)."""
@@ -132,7 +132,7 @@ class PhasePipeline:
         (``select_path`` answers for a concrete problem)."""
         limit = self.active_config().gemv_max_m
         if limit == 0:
-            return "gemv" if M <= 24 else "gemm" if M > 64 else "auto"
+            return "gemv" if M <= 16 else "gemm" if M > 64 else "auto"
         return "gemv" if M <= limit else "gemm"
 
     def capture_step(self, step, warmup: int = 2):

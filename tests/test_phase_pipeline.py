@@ -36,7 +36,7 @@ def test_configurations_and_fallback():
     assert p.active_config() == p.prefill_config()            # Unknown falls back to prefill
     assert p.decode_config().matmul_strategy == "gemv" and p.prefill_config().matmul_strategy == "gemm"
     assert p.prefill_config().gemv_max_m == 0                 # threshold left to the library
-    assert [p.strategy_for(m) for m in (24, 25, 64, 65)] == ["gemv", "auto", "auto", "gemm"]
+    assert [p.strategy_for(m) for m in (16, 17, 64, 65)] == ["gemv", "auto", "auto", "gemm"]
     p.set_decode_config(PhaseConfig("gemv", 16, True))
     p.set_prefill_config(PhaseConfig("gemm", 8, False))
     p.set_phase(InferencePhase.Decode)
@@ -87,7 +87,7 @@ def test_options_validate_and_round_trip():
     import torch
     sp = _C.select_path
     assert _C.get_option("gemv_max_m") == 0
-    assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (24, 25)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (16, 17)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
     assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33, 64, 65)] == ["gemv", "gemv", "gemv", "gemm"]
