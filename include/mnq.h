@@ -113,7 +113,7 @@ typedef struct mnq_tuning {
     int32_t gemv_variant;        /* kernel variant, 0 auto.  GEMV path: 1 register-prefetch kernel, 2 shared-memory
                                     streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2),
                                     3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it, 5 no raw-integer
-                                    tiles, 6 weight tiles always through shared memory (never tensor memory), 8 bf16 activations with
+                                    tiles, 6 weight tiles always through shared memory (never tensor memory), 7 no cut of the last round's tiles along K, 8 bf16 activations with
                                     group-wise scales: two bf16 tiles per k-block even with MNQ_OPT_BF16_FP16_TILES set.  Streaming GEMV: 3 the general kernel even where the compact or the batched one would
                                     run, 4 no kernel that reads prepared activations (the compact kernel up to 8 tokens,
                                     the general one above) */

@@ -37,6 +37,7 @@
 // and the CTA falls through to its teardown (tensor memory is always released).
 #include <cuda.h>
 
+#include <algorithm>
 #include <type_traits>
 
 #include "mnq_common.cuh"
@@ -92,6 +93,14 @@ struct GemmParams {
     const float* tok_scale;   // [M]: out column m is multiplied by it (undoes the activations' power-of-two rescale)
     const float* tok_sum;     // [M]: sum over k of the original activations of token m
     int offset_term;          // 1: this launch subtracts (128 s + z) * tok_sum (always; with K split, split 0 does)
+    // Tail cut (single CTAs, no K split otherwise): the tiles along N from tail_from on -- the ones that would
+    // run as a last, partly empty round of CTAs -- are cut tail_splits ways along K, tail_kb k-blocks each;
+    // CTA x >= tail_from is part (x - tail_from) % tail_splits of tile tail_from + (x - tail_from) / tail_splits
+    // and writes its fp32 result to plane [part][M][N - tail_from * 128] of tail_partial.  -1: none.
+    int tail_from;
+    int tail_splits;
+    int tail_kb;
+    float* tail_partial;
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -560,10 +569,20 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int n0 = blockIdx.x * BN;
+    int tile_x = blockIdx.x, part = blockIdx.z, kb_per_part = p.kb_per_split;
+    bool cut = p.splits > 1;   // this CTA's result is one of several partial sums over K
+    if (!PAIR && p.tail_from >= 0 && (int)blockIdx.x >= p.tail_from) {
+        const int t = (int)blockIdx.x - p.tail_from;
+        tile_x = p.tail_from + t / p.tail_splits;
+        part = t % p.tail_splits;
+        kb_per_part = p.tail_kb;
+        cut = true;
+    }
+    const bool in_tail = !PAIR && p.tail_from >= 0 && tile_x >= p.tail_from;
+    const int n0 = tile_x * BN;
     const int m0 = blockIdx.y * p.tok;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
-    const int num_kb = min(p.K / BK, kb_begin + p.kb_per_split) - kb_begin;   // k-blocks of this split
+    const int kb_begin = part * kb_per_part;
+    const int num_kb = min(p.K / BK, kb_begin + kb_per_part) - kb_begin;   // k-blocks of this part
     // Rings: S weight tiles, SB activation stages (one stage = the nh tiles of one k-block).
     // Synchronisation is per k-block, on D = max(S, SB) barrier pairs indexed kb % D:
     // ready[kb % D] completes when the k-block's weight tile is dequantised (one arrival per
@@ -942,15 +961,20 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             if (RAW) {
                 const float s_n = scale;
                 scale = s_n * 16777216.f;
-                if (p.offset_term && (p.splits == 1 || blockIdx.z == 0))
+                if (p.offset_term && (!cut || part == 0))
                     zterm = fmaf(128.f, s_n, p.zeros ? widen16(p.zeros, sc_row, p.scale_dtype) : 0.f);
                 tscale = p.tok_scale;
             }
             // with K split, this CTA's result goes to its [M][N] plane of the workspace instead;
             // the rings are idle now (every MMA has completed), so their memory stages the tile
-            if (p.splits > 1)
+            if (in_tail) {   // plane `part` of the tail's own planes, Nt = N - tail_from * 128 columns wide; indexed by the global n
+                const size_t Nt = (size_t)(p.N - p.tail_from * BN);
                 epilogue_tile<float, T, false>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
-                                               p.partial + (size_t)blockIdx.z * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
+                                               p.tail_partial + (size_t)part * p.M * Nt - (size_t)p.tail_from * BN, Nt, n0, p.N, m0, p.M,
+                                               (p.vec_store & 2) != 0, p.epi, tscale, p.tok_sum, zterm);
+            } else if (cut)
+                epilogue_tile<float, T, false>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
+                                               p.partial + (size_t)part * p.M * p.N, (size_t)p.N, n0, p.N, m0, p.M,
                                                (p.vec_store & 2) != 0, p.epi, tscale, p.tok_sum, zterm);
             else if (p.epi.out_f32)
                 epilogue_tile<float, T, true>(tmem_base, quad, half, row, tid - 64, p.tok, tiles, scale,
@@ -1115,6 +1139,8 @@ struct GemmPlan {
     int half;       // 1: bf16 activations through fp16 tiles (HalfTile): activations prepared in the workspace first
     int ta;         // 1: weight tiles in tensor memory, from column tmem_a_col on
     int tmem_a_col;
+    int tail_from, tail_splits, tail_kb;   // tail cut (see GemmParams): -1 / 1 / 0 when there is none
+    size_t tail_offset;                    // of the tail's planes in the workspace
     size_t smem;
 };
 
@@ -1177,6 +1203,32 @@ inline size_t raw_region_bytes(int64_t M, int64_t K, bool convert)
 {
     const size_t tok = ((static_cast<size_t>(M) * 8 + 255) & ~size_t(255));   // scale and sum per token
     return tok + (convert ? static_cast<size_t>(M) * static_cast<size_t>(K) * 2 : 0);
+}
+
+// Tail cut.  `tiles` CTAs on `slots` resident CTAs run as full rounds plus a last round of `rem` CTAs that
+// takes as long as a full one; cut `ts` ways along K, those tiles make ceil(rem * ts / slots) rounds of
+// 1 / ts the length (plus the fixed cost of a CTA, about 8 k-block times).  Returns the number of parts (1: no
+// cut) and the first tile of the tail.
+int choose_tail(int64_t tiles, int num_kb, int64_t slots, int64_t M, int* from)
+{
+    *from = -1;
+    if (tiles <= slots || num_kb < 32) return 1;
+    const int64_t rem = tiles % slots;
+    if (rem == 0) return 1;
+    int best_ts = 1;
+    double best = num_kb + 8.0;
+    for (int ts = 2; ts <= 4; ++ts) {
+        const int64_t rounds = (rem * ts + slots - 1) / slots;
+        // (+ the second launch and the planes' traffic, as for K splits)
+        const double cost = rounds * ((num_kb + ts - 1) / ts + 8.0) + 6.0 + ts * (4.0 * M * rem * BN) / 2.5e6;
+        if (cost < best * 0.9) { best = cost; best_ts = ts; }
+    }
+    if (best_ts > 1) *from = static_cast<int>(tiles - rem);
+    return best_ts;
+}
+inline size_t tail_bytes(int ts, int64_t M, int64_t N, int from)
+{
+    return static_cast<size_t>(ts) * static_cast<size_t>(M) * static_cast<size_t>(N - static_cast<int64_t>(from) * BN) * 4;
 }
 
 // Token tiling and CTA pairing: up to 512 tokens per CTA as two accumulators of up to 256;
@@ -1354,6 +1406,20 @@ bool plan_gemm(const MatmulArgs& a, const mnq_tuning* tuning, GemmPlan* out)
     pl.occ2 = 0;
     if (want_occ2 && size_rings(112 * 1024, 256)) pl.occ2 = 1;
     else if (!size_rings(226 * 1024, 512)) return false;
+    // a last, partly empty round of CTAs: cut those tiles along K (variant 7 forbids it)
+    pl.tail_from = -1; pl.tail_splits = 1; pl.tail_kb = 0; pl.tail_offset = 0;
+    if (!pl.pair && pl.splits == 1 && pl.tiles_m == 1 && !(tuning && tuning->gemv_variant == 7)) {
+        int from = -1;
+        const int ts = choose_tail(tiles, num_kb, static_cast<int64_t>(a.sm_count) * (pl.occ2 ? 2 : 1), a.M, &from);
+        if (ts > 1) {
+            const bool prepared = pl.raw || pl.half;
+            const size_t at = prepared ? ((raw_region_offset(1, a.M, a.N) + raw_region_bytes(a.M, a.K, a.act_dtype == MNQ_BF16) + 255) & ~size_t(255))
+                                       : ((kCounterBytes + 255) & ~size_t(255));
+            if (a.workspace && a.workspace_bytes >= at + tail_bytes(ts, a.M, a.N, from)) {
+                pl.tail_from = from; pl.tail_splits = ts; pl.tail_kb = (num_kb + ts - 1) / ts; pl.tail_offset = at;
+            }
+        }
+    }
     *out = pl;
     return true;
 }
@@ -1398,6 +1464,17 @@ int launch_gemm_one(const GemmParams& p, const CUtensorMap& xmap, const CUtensor
         if (rcl) return rcl;
     }
     const int rc = check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
+    if (!rc && p.tail_from >= 0) {
+        // second launch: add the tail's planes and write those columns of the output
+        const int64_t n_at = static_cast<int64_t>(p.tail_from) * BN;
+        Epilogue epi = p.epi;
+        const size_t esz = 2;   // bias and residual hold the activation type
+        if (epi.bias) epi.bias = static_cast<const unsigned char*>(epi.bias) + n_at * esz;
+        if (epi.residual) epi.residual = static_cast<const unsigned char*>(epi.residual) + n_at * esz;
+        void* out_at = static_cast<unsigned char*>(p.out) + n_at * (epi.out_f32 ? 4 : 2);
+        return launch_splitk_reduce(p.tail_partial, out_at, p.M, static_cast<int>(p.N - n_at), p.ldc, p.tail_splits,
+                                    std::is_same<T, __nv_bfloat16>::value ? MNQ_BF16 : MNQ_FP16, epi, stream);
+    }
     if (rc || p.splits <= 1) return rc;
     // second launch: add the splits' planes and write the output
     return launch_splitk_reduce(p.partial, p.out, p.M, p.N, p.ldc, p.splits,
@@ -1461,9 +1538,21 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size,
     if (M < 1 || N < 1 || K < BK || K % BK) return base;
     // room for the prepared activations (raw-integer tiles; fp16 tiles for bf16 activations if the caller opted
     // in): per-token factor and sum and, sized for bf16 activations, their fp16 copy
-    if (!raw_applicable(M, K, group_size, quant) && option_value(MNQ_OPT_BF16_FP16_TILES) == 0) return base;
+    // the tail cut's planes (whichever occupancy the plan ends up with), after the prepared activations if any
+    size_t tail = 0;
+    {
+        GemmPlan pl{};
+        if (base <= kCounterBytes && tile_plan(M, N, 0, &pl) && !pl.pair && pl.tiles_m == 1)
+            for (int per_sm = 1; per_sm <= 2; ++per_sm) {
+                int from = -1;
+                const int ts = choose_tail(pl.tiles_n, static_cast<int>(K / BK), 148 * per_sm, M, &from);
+                if (ts > 1) tail = std::max(tail, tail_bytes(ts, M, N, from) + 256);
+            }
+    }
+    if (!raw_applicable(M, K, group_size, quant) && option_value(MNQ_OPT_BF16_FP16_TILES) == 0)
+        return tail ? ((std::max(base, kCounterBytes) + 255) & ~size_t(255)) + tail : base;
     const int splits = base > kCounterBytes ? static_cast<int>((base - kCounterBytes) / (static_cast<size_t>(M) * N * 4)) : 1;
-    return raw_region_offset(splits, M, N) + raw_region_bytes(M, K, true);
+    return ((raw_region_offset(splits, M, N) + raw_region_bytes(M, K, true) + 255) & ~size_t(255)) + tail;
 }
 
 size_t gemm_split_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t group_size)
@@ -1506,6 +1595,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
     p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 8 == 0) ? 1 : 0) | ((a.N % 4 == 0) ? 2 : 0) |
                   ((reinterpret_cast<uintptr_t>(a.out) % 16 == 0 && a.ldc % 4 == 0) ? 4 : 0);
     p.epi = a.epi;
+    p.tail_from = pl.tail_from; p.tail_splits = pl.tail_splits; p.tail_kb = pl.tail_kb;
+    if (pl.tail_from >= 0) p.tail_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + pl.tail_offset);
     if (pl.splits > 1) {
         unsigned char* ws = static_cast<unsigned char*>(a.workspace);
         p.partial = reinterpret_cast<float*>(ws + kCounterBytes);
@@ -1560,8 +1651,8 @@ int launch_gemm(const MatmulArgs& a, const mnq_tuning* tuning)
                                          static_cast<uint64_t>(p.row_bytes) / 4, static_cast<uint64_t>(a.N),
                                          static_cast<uint64_t>(p.row_bytes), 32, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc2) return rc2;
-    dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m),
-              static_cast<unsigned>(pl.splits));
+    dim3 grid(static_cast<unsigned>(pl.tail_from >= 0 ? pl.tail_from + (pl.tiles_n - pl.tail_from) * pl.tail_splits : pl.tiles_n),
+              static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
     const bool pair = pl.pair != 0;
     if (pl.raw) {   // int8 only (plan_gemm)
         if (a.act_dtype == MNQ_FP16) return launch_gemm_one<MNQ_INT8, __half, RawInt>(p, xmap, wmap, grid, pl.smem, pair, pl.occ2 != 0, pl.ta != 0, a.stream);

@@ -337,3 +337,52 @@ def test_bf16_activations_through_fp16_tiles_when_opted_in(mn, quant, M, N, K, g
         rms = float(np.sqrt((ref.astype(np.float64) ** 2).mean()))
         bound = np.abs(ref) * 2.0 ** -7 + 1.5e-3 * rms   # one bf16 ulp + five sigma of the tile noise
         assert np.all(np.abs(got - ref) <= bound), f"element error {float(np.max(np.abs(got - ref) / bound)):.2f}x the bound"
+
+
+@pytest.mark.parametrize("quant,M,N,K,g,adt,epilogue", [
+    ("int8", 64, 300 * 128, 2048, 2048, torch.bfloat16, None),             # raw-integer tiles: 4 tiles past two full rounds
+    ("int8", 48, 301 * 128 - 88, 2048, 2048, torch.float16, "bias_relu"),  # ragged last tile, epilogue in the second launch
+    ("int4", 64, 300 * 128, 2048, 128, torch.float16, "residual"),         # dequantised tiles with a scale table per part
+    ("int4", 72, 150 * 128 + 64, 4096, 128, torch.bfloat16, None),         # two bf16 tiles per k-block: one CTA per SM
+])
+def test_last_round_of_tiles_cut_along_k(mn, quant, M, N, K, g, adt, epilogue):
+    """More tiles along N than CTAs that run at once: the tiles of the last, partly empty round are cut
+    along K (their partial sums added by a second launch).  Against the oracle, against the uncut kernel
+    (variant 7), with an epilogue and with the fp32 output; deterministic."""
+    import mnq_workloads as workloads
+    C = mn._C
+    per_channel = g >= K
+    L = workloads.make_layer("t", M, K, N, quant_type=quant, group_size=g, act_dtype=adt,
+                             scale_dtype=torch.float16 if (quant == "int8" or adt == torch.float16) else adt,
+                             asymmetric=not (per_channel and quant == "int4"), seed=M + K)
+    ref = H.oracle_matmul(L)
+    d = L.to("cuda")
+    t = _gemm_tuning(mn)
+    t7 = _gemm_tuning(mn)
+    t7.gemv_variant = 7
+    a = C.dequant_matmul(*d.args(), tuning=t)
+    a2 = C.dequant_matmul(*d.args(), tuning=t)
+    b = C.dequant_matmul(*d.args(), tuning=t7)
+    a32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)   # (these shapes take the tensor-core kernel by themselves)
+    C.synchronize()
+    assert C.device_status() == 0
+    H.assert_close_to_oracle(a, ref, f"cut tail {quant} {M}x{N}x{K}")
+    H.assert_close_to_oracle(b, ref, f"uncut {quant} {M}x{N}x{K}")
+    H.assert_fp32_gate(a32, ref, f"cut tail fp32 {quant} {M}x{N}x{K}")
+    assert torch.equal(a, a2), "result is not deterministic"
+    # the columns before the tail are computed exactly as without the cut
+    assert torch.equal(a[:, :128 * 148], b[:, :128 * 148])
+    if epilogue:
+        gen = torch.Generator(device="cpu").manual_seed(11)
+        ref_t = torch.from_numpy(ref)
+        if epilogue == "residual":
+            res = (torch.randn(M, N, generator=gen) * 0.5).to(adt)
+            want = ref_t + res.float()
+            out = C.dequant_matmul_fused(*d.args(), epilogue="residual", residual=res.cuda())
+        else:
+            bias = (torch.randn(N, generator=gen) * 0.5).to(adt)
+            want = torch.relu(ref_t + bias.float())
+            out = C.dequant_matmul_fused(*d.args(), epilogue="bias_relu", bias=bias.cuda())
+        C.synchronize()
+        assert C.device_status() == 0
+        H.assert_close_to_oracle(out, want.numpy(), f"cut tail with {epilogue}")
