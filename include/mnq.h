@@ -89,8 +89,8 @@ typedef enum mnq_option {
     /* Largest token count M that takes the decode (GEMV) kernels; above it the tensor-core
      * kernel runs.  0..32, initialised from the environment variable METAL_NATIVE_GEMV_MAX_M
      * when set.  Default 0: chosen per problem from B200 measurements (16 for int8 weights with
-     * one scale per row, 32 for every other format; bf16 activations with group-wise scales stay on
-     * the decode kernels up to 64 tokens).  The
+     * one scale per row and for layers of fewer than 8192 rows and less than 24 MB, 32 for every other
+     * format; bf16 activations with group-wise scales stay on the decode kernels up to 64 tokens).  The
      * reference's counterpart is the fixed `use_vecmat = (M <= 8)` (src/ops/matmul.mm:946). */
     MNQ_OPT_GEMV_MAX_M = 2,
     /* Non-zero: bf16 activations with group-wise scales (or zeros) above the decode threshold use ONE
@@ -114,7 +114,7 @@ typedef struct mnq_tuning {
                                     streaming kernel.  GEMM path: 1 single-CTA tiles, 2 CTA pairs (cta_group::2),
                                     3 never two CTAs per SM, 4 two CTAs per SM whenever a tile allows it, 5 no raw-integer
                                     tiles, 6 weight tiles always through shared memory (never tensor memory), 7 no cut of the last round's tiles along K, 8 bf16 activations with
-                                    group-wise scales: two bf16 tiles per k-block even with MNQ_OPT_BF16_FP16_TILES set.  Streaming GEMV: 3 the general kernel even where the compact or the batched one would
+                                    group-wise scales: two bf16 tiles per k-block even with MNQ_OPT_BF16_FP16_TILES set.  Streaming GEMV: 9 the batched-decode kernel even on small layers of few rows, 3 the general kernel even where the compact or the batched one would
                                     run, 4 no kernel that reads prepared activations (the compact kernel up to 8 tokens,
                                     the general one above) */
     int32_t piece_bytes;         /* streaming GEMV: packed bytes per row per stage (multiple of 64) */

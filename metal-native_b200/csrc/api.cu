@@ -238,7 +238,11 @@ int64_t gemv_max_m_for(int64_t K, int32_t group_size, int32_t quant, int32_t act
 // whatever neither takes.
 int choose_path(const MatmulArgs& a)
 {
-    const int64_t gemv_max_m = gemv_max_m_for(a.K, a.group_size, a.quant, a.act_dtype);
+    int64_t gemv_max_m = gemv_max_m_for(a.K, a.group_size, a.quant, a.act_dtype);
+    // small layers of few rows: the tensor-core kernel from 17 tokens (not where it needs two bf16 tiles per k-block)
+    if (option_value(MNQ_OPT_GEMV_MAX_M) == 0 && gemv_max_m > 16 && few_rows_small_layer(a) &&
+        !(a.act_dtype == MNQ_BF16 && (a.group_size < a.K || a.zeros != nullptr)))
+        gemv_max_m = 16;
     if (a.M <= gemv_max_m && gemv_supported(a)) return MNQ_PATH_GEMV;
     // 33 to 64 tokens of bf16 activations where the tensor-core kernel would need two bf16 tiles per
     // k-block (group-wise scales, the caller has not opted for fp16 tiles): the batched-decode

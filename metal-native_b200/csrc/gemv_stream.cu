@@ -1069,8 +1069,11 @@ int launch_gemv_stream(const MatmulArgs& a, const mnq_tuning* tuning)
         if (rc8) return rc8;
     }
     // 5 to 32 tokens: the kernel that reads activations prepared once per call (see gemv_mid.cu);
-    // variants 3 and 4 leave it out
-    if (!(tuning && (tuning->gemv_variant == 3 || tuning->gemv_variant == 4)) && gemv_mid_supported(a, tuning))
+    // variants 3 and 4 leave it out, and so do small layers of few rows (of at least 4 MB: below that
+    // every kernel takes the same 7-9 us) unless variant 9 asks for it
+    const bool mid_pays = !(few_rows_small_layer(a) && packed_weight_bytes(a) >= (int64_t(4) << 20)) ||
+                          (tuning && tuning->gemv_variant == 9);
+    if (!(tuning && (tuning->gemv_variant == 3 || tuning->gemv_variant == 4)) && mid_pays && gemv_mid_supported(a, tuning))
         return launch_gemv_mid(a, tuning, wmap);
     // the compact kernel takes the common decode case (see gemv_lean.cu); variant 3 forces this one
     if (pl.nt == 1 && !(tuning && tuning->gemv_variant == 3)) {

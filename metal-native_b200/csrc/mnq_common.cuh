@@ -275,6 +275,13 @@ struct MatmulArgs {
     Epilogue epi;         // kind NONE and out_f32 0 unless called through mnq_dequant_matmul_fused
 };
 
+// Few rows and little data.  The batched-decode path costs two launches more than the other decode kernels
+// (activation image, K-cut reduction), about 4 us, which layers like a 4096 x 4096 projection do not earn
+// back: measured on B200, the compact and general streaming kernels are ahead there up to 16 tokens
+// (8.6-10.2 against 12.9-16.6 us for 8 MB of int4) and the tensor-core kernel above (13.8 against 16.6-23 us).
+inline int64_t packed_weight_bytes(const MatmulArgs& a) { return a.N * (a.quant == MNQ_INT4 ? a.K / 2 : a.K); }
+inline bool few_rows_small_layer(const MatmulArgs& a) { return a.N < 8192 && packed_weight_bytes(a) < (int64_t(24) << 20); }
+
 // Process-wide options (mnq_set_option); defined in api.cu.
 int64_t option_value(int option);
 

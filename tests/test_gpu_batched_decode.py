@@ -1,5 +1,7 @@
 """The batched-decode kernel (5 to 32 tokens, activations prepared once per call; gemv_mid.cu)
-against the CPU oracle and against the general streaming kernel, through the C ABI.  Needs a B200."""
+against the CPU oracle and against the general streaming kernel, through the C ABI.  Needs a B200.
+(Kernel variant 9 asks for it on the small layers most of these cases are, which the default
+route gives to the other decode kernels.)"""
 import pytest
 import torch
 
@@ -52,7 +54,7 @@ CASES = [
 
 @pytest.mark.parametrize("quant,M,N,K,g,asym,adt", CASES)
 def test_batched_decode_kernel(mn, quant, M, N, K, g, asym, adt):
-    """Default route (the batched-decode kernel) and the general streaming kernel (variant 3), both
+    """The batched-decode kernel, the general streaming kernel (variant 3) and the default route, all
     against the oracle, twice in a row on one workspace; fp32 output against the tighter gate."""
     import mnq_workloads as workloads
     C = mn._C
@@ -65,15 +67,17 @@ def test_batched_decode_kernel(mn, quant, M, N, K, g, asym, adt):
         d = L.to("cuda")
         assert C.select_path(M, N, K, g, quant, adt) == "gemv"
         general = _tuning(mn, gemv_variant=3)
+        batched = _tuning(mn, gemv_variant=9)
         for call in range(2):
-            a = C.dequant_matmul(*d.args())
+            a = C.dequant_matmul(*d.args(), tuning=batched)
             b = C.dequant_matmul(*d.args(), tuning=general if M <= 32 else None)   # (no other decode kernel above 32 tokens)
             C.synchronize()
             assert C.device_status() == 0
             H.assert_close_to_oracle(a, ref, f"batched {quant} {M}x{N}x{K} call {call}")
             H.assert_close_to_oracle(b, ref, f"general {quant} {M}x{N}x{K} call {call}")
-        a2 = C.dequant_matmul(*d.args())
+        a2 = C.dequant_matmul(*d.args(), tuning=batched)
         assert torch.equal(a, a2), "result is not deterministic"
+        H.assert_close_to_oracle(C.dequant_matmul(*d.args()), ref, f"default route {quant} {M}x{N}x{K}")
         a32 = C.dequant_matmul_fused(*d.args(), out_dtype=torch.float32)
         H.assert_fp32_gate(a32, ref, f"batched fp32 {quant} {M}x{N}x{K}")
     finally:
@@ -93,7 +97,7 @@ def test_batched_decode_forced_k_cuts_and_epilogue(mn, split):
     want = torch.relu(torch.from_numpy(ref) + bias.float())
     try:
         C.set_option("gemv_max_m", 32)
-        t = _tuning(mn, path=C.PATH_GEMV, split_k=split)
+        t = _tuning(mn, path=C.PATH_GEMV, split_k=split, gemv_variant=9)
         out = C.dequant_matmul_fused(*d.args(), epilogue="bias_relu", bias=bias.cuda())
         plain = C.dequant_matmul(*d.args(), tuning=t)
         C.synchronize()
@@ -140,10 +144,11 @@ def test_batched_decode_step_replayed_from_a_cuda_graph(mn, M, N, K):
     out = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
     pipe = mn.PhasePipeline()
     pipe.set_phase(mn.InferencePhase.Decode)
-    step = pipe.capture_step(lambda: C.dequant_matmul(*d.args(), out=out))
+    batched = _tuning(mn, gemv_variant=9)
+    step = pipe.capture_step(lambda: C.dequant_matmul(*d.args(), out=out, tuning=batched))
     for scale in (1.0, 0.5, -3.0):
         d.x.copy_((L.x.float() * scale).to(torch.bfloat16))
-        want = C.dequant_matmul(*d.args()).clone()
+        want = C.dequant_matmul(*d.args(), tuning=batched).clone()
         out.zero_()
         step()
         torch.cuda.synchronize()

@@ -88,8 +88,12 @@ def test_options_validate_and_round_trip():
     sp = _C.select_path
     assert _C.get_option("gemv_max_m") == 0
     assert [sp(m, 4096, 4096, 4096, "int8", torch.bfloat16) for m in (16, 17)] == ["gemv", "gemm"]
-    assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
-    assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
+    assert [sp(m, 16384, 4096, 128, "int8", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
+    assert [sp(m, 16384, 4096, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]
+    # small layers of few rows (fewer than 8192, less than 24 MB): the tensor-core kernel from 17 tokens
+    assert [sp(m, 4096, 4096, 128, "int4", torch.float16) for m in (16, 17)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 4096, 128, "int8", torch.float16) for m in (16, 17)] == ["gemv", "gemm"]
+    assert [sp(m, 4096, 14336, 128, "int4", torch.float16) for m in (32, 33)] == ["gemv", "gemm"]   # 29 MB
     assert [sp(m, 4096, 4096, 128, "int4", torch.bfloat16) for m in (32, 33, 64, 65)] == ["gemv", "gemv", "gemv", "gemm"]
     assert [sp(m, 4096, 4096, 4096, "int4", torch.bfloat16) for m in (32, 33)] == ["gemv", "gemm"]   # one scale per row, no zeros: integer tiles
     # fp16 activations with bf16 scales above the decode threshold: the any-shape kernel, and it says so
